@@ -1,0 +1,308 @@
+"""CPU restatement of the reference attention arithmetic (luyanaa/flash-attn-triton).
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA kernels: only the
+test-suite, the smoke check and the benchmark's CPU-baseline leg may import it.  The
+product package never does; it fails loudly when its CUDA library is missing.
+
+Everything here is plain fp32 torch on the CPU (dense matrices, no tiling), written
+from the reference's own eager restatement and kernels:
+
+* score pipeline and mask alignment .......... flash_attn_triton/flash_attn_interface.py:15-49
+* rotary embedding ........................... flash_attn_triton/flash_attn_interface.py:52-66
+* KV-cache append + attend (intended form) ... flash_attn_triton/flash_attn_interface.py:409-525
+* packed variable-length batches ............. flash_attn_triton/triton_kernel/attention_kernel.py:27-104
+* base-2 LSE saved for the backward .......... flash_attn_triton/triton_kernel/attention_kernel.py:522-533
+* per-token INT8 K quantiser ................. flash_attn_triton/triton_kernel/attention_kernel_int8.py:27-30,58-79
+* INT8 QK^T forward .......................... flash_attn_triton/triton_kernel/attention_kernel_int8.py:82-141,167-217
+
+Parity pin: tests/golden/*.npz hold outputs of the unmodified reference kernels run
+under Triton's CPU interpreter (tests/golden/make_golden.py); tests/test_oracle_golden.py
+checks every function below against them.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+LOG2E = 1.4426950408889634
+
+
+# ----------------------------------------------------------------------------------------
+# score pipeline (flash_attn_interface.py:15-49)
+# ----------------------------------------------------------------------------------------
+def keep_mask(q_len, k_len, causal, window, q_pos_offset=0):
+    """Boolean (q_len, k_len) mask.  Query i sits at position i + q_pos_offset, key j at j;
+    causal keeps j <= pos, the window keeps pos-left <= j <= pos+right
+    (flash_attn_interface.py:27-35: upper-left alignment when the offset is 0)."""
+    q_pos = torch.arange(q_len)[:, None] + q_pos_offset
+    k_pos = torch.arange(k_len)[None, :]
+    keep = torch.ones(q_len, k_len, dtype=torch.bool)
+    if causal:
+        keep &= q_pos >= k_pos
+    if window[0] >= 0:
+        keep &= k_pos >= q_pos - window[0]
+    if window[1] >= 0:
+        keep &= k_pos <= q_pos + window[1]
+    return keep
+
+
+def scores_ref(q, k, softmax_scale=None, causal=False, window=(-1, -1), softcap=0.0,
+               alibi_slopes=None, attn_bias=None, q_pos_offset=0):
+    """Masked fp32 scores (B, Hq, Sq, Sk) in the natural-log domain.
+
+    Order of operations is the reference's contract (flash_attn_interface.py:26-43):
+    scale -> minus slope*|i-j| -> plus bias -> softcap*tanh(s/softcap) -> -inf mask.
+    q: (B, Sq, Hq, D), k: (B, Sk, Hkv, D)."""
+    q = q.float()
+    k = k.float()
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    if Hq != Hkv:
+        k = k.repeat_interleave(Hq // Hkv, dim=2)
+    scale = 1.0 / math.sqrt(D) if softmax_scale is None else softmax_scale
+    s = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
+    if alibi_slopes is not None:
+        slopes = torch.as_tensor(alibi_slopes, dtype=torch.float32)
+        slopes = slopes if slopes.ndim == 2 else slopes[None, :]
+        q_pos = torch.arange(Sq)[:, None] + q_pos_offset
+        k_pos = torch.arange(Sk)[None, :]
+        s = s - slopes[:, :, None, None] * (q_pos - k_pos).abs()
+    if attn_bias is not None:
+        s = s + attn_bias.float()
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    keep = keep_mask(Sq, Sk, causal, window, q_pos_offset)
+    return s.masked_fill(~keep[None, None], float("-inf"))
+
+
+def attention_ref(q, k, v, softmax_scale=None, causal=False, window=(-1, -1), softcap=0.0,
+                  alibi_slopes=None, attn_bias=None, q_pos_offset=0, p_dtype=None):
+    """Dense attention.  Returns (out fp32 (B,Sq,Hq,D), lse natural-log (B,Hq,Sq)).
+
+    Rows with no visible key give out = 0 and lse = -inf
+    (flash_attn_interface.py:43-45; attention_kernel.py:522-533).
+    p_dtype: when given, probabilities are rounded to that dtype before P@V, as the
+    kernels do (attention_kernel.py:366)."""
+    s = scores_ref(q, k, softmax_scale, causal, window, softcap, alibi_slopes, attn_bias,
+                   q_pos_offset)
+    probs = torch.nan_to_num(torch.softmax(s, dim=-1))
+    lse = torch.logsumexp(s, dim=-1)
+    vv = v.float()
+    if q.shape[2] != v.shape[2]:
+        vv = vv.repeat_interleave(q.shape[2] // v.shape[2], dim=2)
+    if p_dtype is not None:
+        probs = probs.to(p_dtype).float()
+    out = torch.einsum("bhqk,bkhd->bqhd", probs, vv)
+    return out, lse
+
+
+def attention_grads_ref(q, k, v, dout, **kw):
+    """(out, lse, dq, dk, dv) in fp32 by autograd through attention_ref.  GQA gradients of
+    a KV head are the sum over its query heads (attention_kernel.py:188-272)."""
+    q32 = q.detach().float().requires_grad_()
+    k32 = k.detach().float().requires_grad_()
+    v32 = v.detach().float().requires_grad_()
+    out, lse = attention_ref(q32, k32, v32, **kw)
+    dq, dk, dv = torch.autograd.grad((out * dout.float()).sum(), (q32, k32, v32))
+    return out.detach(), lse.detach(), dq, dk, dv
+
+
+def lse2_from_natural(lse):
+    """Natural-log LSE -> the base-2 LSE the kernels save (attention_kernel.py:524)."""
+    return lse * LOG2E
+
+
+# ----------------------------------------------------------------------------------------
+# packed variable-length batches (attention_kernel.py:27-104; interface.py:527-690)
+# ----------------------------------------------------------------------------------------
+def varlen_attention_ref(q, k, v, cu_q, cu_k, softmax_scale=None, causal=False,
+                         window=(-1, -1), softcap=0.0, alibi_slopes=None):
+    """q (Tq,Hq,D), k/v (Tk,Hkv,D); cu_* int (batch+1,).  Returns (out (Tq,Hq,D) fp32,
+    lse natural (Tq,Hq)).  Each sequence is attended on its own with upper-left
+    alignment (attention_kernel.py:47-48)."""
+    cu_q = [int(x) for x in cu_q]
+    cu_k = [int(x) for x in cu_k]
+    batch = len(cu_q) - 1
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    lse = torch.full((q.shape[0], q.shape[1]), float("-inf"))
+    slopes = None
+    if alibi_slopes is not None:
+        slopes = torch.as_tensor(alibi_slopes, dtype=torch.float32)
+        if slopes.ndim == 1:
+            slopes = slopes[None, :].expand(batch, -1)
+    for b in range(batch):
+        qs, qe, ks, ke = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
+        if qe == qs:
+            continue
+        if ke == ks:
+            continue
+        o, l = attention_ref(q[qs:qe][None], k[ks:ke][None], v[ks:ke][None], softmax_scale,
+                             causal, window, softcap,
+                             None if slopes is None else slopes[b:b + 1])
+        out[qs:qe] = o[0]
+        lse[qs:qe] = l[0].transpose(0, 1)
+    return out, lse
+
+
+def varlen_attention_grads_ref(q, k, v, dout, cu_q, cu_k, **kw):
+    q32 = q.detach().float().requires_grad_()
+    k32 = k.detach().float().requires_grad_()
+    v32 = v.detach().float().requires_grad_()
+    out, lse = varlen_attention_ref(q32, k32, v32, cu_q, cu_k, **kw)
+    dq, dk, dv = torch.autograd.grad((out * dout.float()).sum(), (q32, k32, v32),
+                                     allow_unused=True)
+    z = lambda g, t: torch.zeros_like(t) if g is None else g
+    return out.detach(), lse.detach(), z(dq, q32), z(dk, k32), z(dv, v32)
+
+
+# ----------------------------------------------------------------------------------------
+# rotary + KV cache (flash_attn_interface.py:52-66, 409-525)
+# ----------------------------------------------------------------------------------------
+def apply_rotary_ref(x, cos, sin, positions, interleaved):
+    """x (S,H,D) in its own dtype; cos/sin (seqlen_ro, rotary_dim/2); positions (S,) ints.
+    The arithmetic is carried out in x's dtype, like the reference
+    (flash_attn_interface.py:57-66)."""
+    rotary_dim = cos.shape[-1] * 2
+    c = cos[positions].to(x.dtype)[:, None, :]
+    s = sin[positions].to(x.dtype)[:, None, :]
+    part = x[..., :rotary_dim]
+    if interleaved:
+        even, odd = part[..., 0::2], part[..., 1::2]
+        rot = torch.stack((even * c - odd * s, even * s + odd * c), dim=-1).flatten(-2)
+    else:
+        h = rotary_dim // 2
+        a, b = part[..., :h], part[..., h:]
+        rot = torch.cat((a * c - b * s, a * s + b * c), dim=-1)
+    return torch.cat((rot, x[..., rotary_dim:]), dim=-1)
+
+
+def kvcache_ref(q, k_cache, v_cache, k_new=None, v_new=None, cos=None, sin=None,
+                cache_seqlens=None, cache_batch_idx=None, cache_leftpad=None,
+                block_table=None, softmax_scale=None, causal=False, window=(-1, -1),
+                rotary_interleaved=True, alibi_slopes=None):
+    """Append-then-attend against a contiguous or paged cache.
+
+    This is the behaviour the reference's code is written to have
+    (flash_attn_interface.py:468-525): rotate the new keys at positions
+    len+leftpad+i, write new k/v into the cache at those slots, rotate q at
+    len_after-Sq+leftpad+i and attend over the first len_after cached tokens.  (In the
+    reference the two `cache[idx, idx].copy_` lines at :487-492 write into a temporary,
+    so its cache stays stale; tests pin the reference by doing the append themselves.)
+    Query rows are bottom-right aligned for the causal mask (offset len_after-Sq, :523);
+    for window/ALiBi this oracle uses the same offset.
+    Returns (out fp32 (B,Sq,Hq,D), k_cache_after, v_cache_after)."""
+    kc = k_cache.clone()
+    vc = v_cache.clone()
+    B, Sq = q.shape[0], q.shape[1]
+    paged = block_table is not None
+    page = kc.shape[1]
+    lens = (torch.as_tensor(cache_seqlens).long().flatten() if cache_seqlens is not None else
+            torch.full((B,), (block_table.shape[1] * page) if paged else kc.shape[1]).long())
+    if cache_seqlens is None and k_new is not None:
+        lens = torch.zeros(B, dtype=torch.long)
+    pads = (torch.as_tensor(cache_leftpad).long().flatten() if cache_leftpad is not None
+            else torch.zeros(B, dtype=torch.long))
+    rows = (torch.as_tensor(cache_batch_idx).long().flatten() if cache_batch_idx is not None
+            else torch.arange(B))
+    outs = []
+    for b in range(B):
+        L, pad, row = int(lens[b]), int(pads[b]), int(rows[b])
+        if k_new is not None:
+            Sn = k_new.shape[1]
+            kn = k_new[b]
+            if cos is not None:
+                kn = apply_rotary_ref(kn, cos, sin, torch.arange(Sn) + L + pad, rotary_interleaved)
+            for i in range(Sn):
+                pos = L + pad + i
+                if paged:
+                    pg = int(block_table[b, pos // page])
+                    kc[pg, pos % page] = kn[i]
+                    vc[pg, pos % page] = v_new[b, i]
+                else:
+                    kc[row, pos] = kn[i]
+                    vc[row, pos] = v_new[b, i]
+            L += Sn
+        if paged:
+            npages = (pad + L + page - 1) // page
+            ids = block_table[b, :npages].long()
+            kb = kc[ids].reshape(-1, kc.shape[2], kc.shape[3])[pad:pad + L]
+            vb = vc[ids].reshape(-1, vc.shape[2], vc.shape[3])[pad:pad + L]
+        else:
+            kb = kc[row, pad:pad + L]
+            vb = vc[row, pad:pad + L]
+        qb = q[b]
+        if cos is not None:
+            qb = apply_rotary_ref(qb, cos, sin, torch.arange(Sq) + L - Sq + pad, rotary_interleaved)
+        sl = None
+        if alibi_slopes is not None:
+            sl = torch.as_tensor(alibi_slopes, dtype=torch.float32)
+            sl = sl[b:b + 1] if sl.ndim == 2 else sl[None]
+        o, _ = attention_ref(qb[None], kb[None], vb[None], softmax_scale, causal, window, 0.0,
+                             sl, q_pos_offset=L - Sq)
+        outs.append(o)
+    return torch.cat(outs, dim=0), kc, vc
+
+
+# ----------------------------------------------------------------------------------------
+# INT8 path (attention_kernel_int8.py)
+# ----------------------------------------------------------------------------------------
+def round_i8_np(x):
+    """floor(x+0.5) for x>=0, ceil(x-0.5) otherwise, in IEEE fp32
+    (attention_kernel_int8.py:27-30).  Not the same as rint or roundf at x=0.49999997."""
+    x = np.asarray(x, dtype=np.float32)
+    half = np.float32(0.5)
+    r = np.where(x >= 0, np.floor(x + half), np.ceil(x - half))
+    return r.astype(np.int8)
+
+
+def quantize_k_rows_ref(k):
+    """Per-key-token INT8 codes and fp32 scales (attention_kernel_int8.py:58-79).
+
+    k: fp16 array/tensor (..., S, D).  amax in fp16 (exact), s = fp32(max(amax,1))/127,
+    inv = 1/s, x = fp32(k)*inv, code = round_i8(x).  Every step is a single IEEE fp32
+    operation, so numpy reproduces the kernel bit for bit."""
+    kn = k.detach().cpu().numpy() if isinstance(k, torch.Tensor) else np.asarray(k)
+    assert kn.dtype == np.float16
+    amax = np.abs(kn).max(axis=-1).astype(np.float32)
+    s = (np.maximum(amax, np.float32(1.0)) / np.float32(127.0)).astype(np.float32)
+    inv = (np.float32(1.0) / s).astype(np.float32)
+    x = (kn.astype(np.float32) * inv[..., None]).astype(np.float32)
+    return round_i8_np(x), s
+
+
+def quantize_q_rows_ref(q):
+    """Per-query-row codes, division form q/s (attention_kernel_int8.py:33-39, :100)."""
+    qn = q.detach().cpu().numpy() if isinstance(q, torch.Tensor) else np.asarray(q)
+    amax = np.abs(qn).max(axis=-1).astype(np.float32)
+    s = (np.maximum(amax, np.float32(1.0)) / np.float32(127.0)).astype(np.float32)
+    x = (qn.astype(np.float32) / s[..., None]).astype(np.float32)
+    return round_i8_np(x), s
+
+
+def attention_int8_ref(q, k, v, causal=False, sm_scale=None):
+    """INT8-QK^T forward in the reference's arithmetic.  q,k,v: fp16 (B,H,S,D).
+
+    scores(log2) = float(int32 q8.k8) * (s_q*s_k) * (sm_scale*1.44269504)
+    (attention_kernel_int8.py:106-107, :200); masked entries get -1.0e6 added, not -inf
+    (:113); probabilities are rounded to fp16 before P@V (:135-137).
+    Returns (out fp32 (B,H,S,D), lse base-2 (B,H,S), k8 int8, s_k fp32)."""
+    B, H, S, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    k8, s_k = quantize_k_rows_ref(k)
+    q8, s_q = quantize_q_rows_ref(q)
+    acc = torch.einsum("bhqd,bhkd->bhqk", torch.from_numpy(q8.astype(np.float32)),
+                       torch.from_numpy(k8.astype(np.float32)))  # exact: |sum| < 2^24
+    qk = acc * (torch.from_numpy(s_q)[..., :, None] * torch.from_numpy(s_k)[..., None, :])
+    qk = qk * np.float32(sm_scale * 1.44269504)
+    if causal:
+        keep = keep_mask(S, S, True, (-1, -1))
+        qk = qk + torch.where(keep, 0.0, -1.0e6)[None, None]
+    m = qk.max(dim=-1, keepdim=True).values
+    p = torch.exp2(qk - m)
+    l = p.sum(dim=-1, keepdim=True)
+    out = torch.einsum("bhqk,bhkd->bhqd", p.half().float(), v.float()) / l
+    lse2 = (m + torch.log2(l)).squeeze(-1)
+    return out, lse2, k8, s_k

@@ -1,0 +1,122 @@
+"""The CPU oracle against the golden vectors produced by the unmodified reference
+(tests/golden/make_golden.py).  No GPU needed.
+
+Tolerances: the reference computes in fp16 with fp32 accumulation and its own measured
+error against fp32 SDPA is ~1e-3 (outputs) / ~2e-3 (gradients) at these sizes, so the
+oracle (exact fp32) must agree with it within 2e-3 / 1e-2, the bars the GPU kernels are
+held to.  Quantised K codes and scales are bit-exact.
+"""
+import ast
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import attention_oracle as orc
+
+FWD_TOL = 2e-3
+GRAD_TOL = 1e-2
+LN2 = 0.6931471805599453
+
+
+def maxdiff(a, b):
+    a = torch.as_tensor(np.asarray(a)).float()
+    b = torch.as_tensor(np.asarray(b)).float()
+    return (a - b).abs().max().item()
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+def test_dense_c1(golden, causal):
+    g = golden(f"dense_c1_causal{causal}")
+    q, k, v, do = cases.dense_case(0, 2, 128, 128, 4, 4, 64)
+    assert cases.checksum(q, k, v, do) == str(g["checksum"])
+    out, lse, dq, dk, dv = orc.attention_grads_ref(q, k, v, do, softmax_scale=0.125,
+                                                   causal=bool(causal))
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    assert maxdiff(lse, g["lse2"] * LN2) <= FWD_TOL
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t, g[name]) <= GRAD_TOL, name
+
+
+def test_dense_public(golden):
+    g = golden("dense_public")
+    specs = ast.literal_eval(str(g["_specs"]))
+    for i, (name, (B, Sq, Sk, Hq, Hkv, D, kw)) in enumerate(specs.items()):
+        q, k, v, do = cases.dense_case(100 + i, B, Sq, Sk, Hq, Hkv, D)
+        assert cases.checksum(q, k, v, do) == str(g[name + ".checksum"]), name
+        out, lse, dq, dk, dv = orc.attention_grads_ref(
+            q, k, v, do, softmax_scale=kw.get("softmax_scale"), causal=kw.get("causal", False),
+            window=kw.get("window_size", (-1, -1)), softcap=kw.get("softcap", 0.0),
+            alibi_slopes=kw.get("alibi_slopes"))
+        assert maxdiff(out, g[name + ".out"]) <= FWD_TOL, name
+        for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+            assert maxdiff(t, g[f"{name}.{n}"]) <= GRAD_TOL, (name, n)
+
+
+def test_varlen_all(golden):
+    g = golden("varlen_all")
+    ql, kl = g["q_lens"].tolist(), g["k_lens"].tolist()
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(7, ql, kl, 4, 2, 64)
+    assert cases.checksum(q, k, v, do) == str(g["checksum"])
+    out, lse, dq, dk, dv = orc.varlen_attention_grads_ref(
+        q, k, v, do, cu_q, cu_k, softmax_scale=0.125, causal=True, window=(48, 0),
+        softcap=30.0, alibi_slopes=torch.from_numpy(g["slopes"]))
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    assert maxdiff(lse, g["lse2"] * LN2) <= FWD_TOL
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t, g[name]) <= GRAD_TOL, name
+
+
+def test_varlen_rect(golden):
+    g = golden("varlen_rect")
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(8, [3, 5], [4, 6], 2, 2, 16)
+    out, _ = orc.varlen_attention_ref(q, k, v, cu_q, cu_k, causal=True)
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+
+
+def test_k_quantiser_bit_exact(golden):
+    g = golden("int8_kquant")
+    k = cases.k_with_outliers(21, 4, 192, 128)
+    assert cases.checksum(k) == str(g["checksum"])
+    k8, s_k = orc.quantize_k_rows_ref(k)
+    assert np.array_equal(k8, g["k8"])
+    assert np.array_equal(s_k.view(np.uint32), g["s_k"].view(np.uint32))
+
+
+def test_round_i8_is_not_rint():
+    x = np.array([0.49999997, 0.5, 1.5, 2.5, -0.5, -1.5, -0.49999997], dtype=np.float32)
+    assert orc.round_i8_np(x).tolist() == [1, 1, 2, 3, -1, -2, -1]
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+def test_int8_forward(golden, causal):
+    g = golden(f"int8_fwd_causal{causal}")
+    q, k, v = cases.int8_case(30, 1, 2, 256, 128)
+    assert cases.checksum(q, k, v) == str(g["checksum"])
+    out, lse2, _, _ = orc.attention_int8_ref(q, k, v, causal=bool(causal))
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    assert maxdiff(lse2, g["lse2"]) <= FWD_TOL
+
+
+def test_kvcache_paged(golden):
+    g = golden("kvcache_paged")
+    lens = g["lens"].tolist()
+    q, kc, vc, kn, vn, bt, cl = cases.paged_case(40, 3, 8, 2, 64, 64, 12, lens, 4)
+    assert cases.checksum(q, kc, vc, kn, vn, bt) == str(g["checksum"])
+    cos, sin = cases.rotary_tables(256, 64)
+    out, kc2, vc2 = orc.kvcache_ref(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl,
+                                    block_table=bt, causal=False, rotary_interleaved=False)
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    for i, (p, o) in enumerate(g["touched"].tolist()):
+        assert torch.equal(kc2[p, o], torch.from_numpy(g["k_rows"][i]))
+        assert torch.equal(vc2[p, o], torch.from_numpy(g["v_rows"][i]))
+    # nothing else in the cache moved
+    mask = torch.ones(kc.shape[:2], dtype=torch.bool)
+    for p, o in g["touched"].tolist():
+        mask[p, o] = False
+    assert torch.equal(kc2[mask], kc[mask]) and torch.equal(vc2[mask], vc[mask])
+    # causal=True is the same thing for one query row
+    out_c, _, _ = orc.kvcache_ref(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl,
+                                  block_table=bt, causal=True, rotary_interleaved=False)
+    assert maxdiff(out_c, out) == 0.0
