@@ -1,0 +1,75 @@
+"""Compile csrc/*.cu for sm_100a into libfa_b200.so next to this file.
+
+    python -m flash_attn_triton_b200.build [--force] [--verbose]
+
+nvcc cross-compiles without a GPU.  Objects are cached under build/ and rebuilt when a
+source or header is newer.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
+LIB = os.path.join(HERE, "libfa_b200.so")
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+# which tcgen05 families are present (each defines its FA_HAVE_* so the stubs step aside)
+HAVE = {"fwd_sm100.cu": "FA_HAVE_FWD_SM100", "bwd_sm100.cu": "FA_HAVE_BWD_SM100",
+        "int8_sm100.cu": "FA_HAVE_INT8_SM100"}
+
+
+def _sources():
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _newest_header():
+    t = 0.0
+    for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+        for f in os.listdir(root):
+            if f.endswith((".cuh", ".h")):
+                t = max(t, os.path.getmtime(os.path.join(root, f)))
+    return max(t, os.path.getmtime(__file__))
+
+
+def _compile(src, defs, force, verbose):
+    obj = os.path.join(OBJ, src[:-3] + ".o")
+    spath = os.path.join(CSRC, src)
+    if (not force and os.path.exists(obj)
+            and os.path.getmtime(obj) > max(os.path.getmtime(spath), _newest_header())):
+        return src, "", False
+    cmd = [NVCC, *FLAGS, *defs, "-c", spath, "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
+    with open(obj + ".ptxas.txt", "w") as f:
+        f.write(r.stderr)
+    return src, r.stderr if verbose else "", True
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    os.makedirs(OBJ, exist_ok=True)
+    srcs = _sources()
+    defs = [f"-D{HAVE[s]}" for s in srcs if s in HAVE]
+    rebuilt = False
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+        for src, log, did in ex.map(lambda s: _compile(s, defs, force, verbose), srcs):
+            rebuilt |= did
+            if log:
+                print(f"--- {src}\n{log}")
+    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in srcs]
+    if rebuilt or not os.path.exists(LIB):
+        cmd = [NVCC, "-shared", "-o", LIB, *objs, "-cudart", "static"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,255 @@
+// Shared device/host helpers for the sm_100a attention kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fa_b200.h"
+
+#define FA_LOG2E 1.4426950408889634f
+#define FA_LN2 0.6931471805599453f
+
+namespace fa {
+
+// ---------------------------------------------------------------------------------------
+// error plumbing (host)
+// ---------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+int ensure_device(int device);
+
+#define FA_REQUIRE(cond, ...)      \
+  do {                             \
+    if (!(cond)) {                 \
+      fa::set_error(__VA_ARGS__);  \
+      return FA_ERR_INVALID;       \
+    }                              \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------
+// Score pipeline shared by every kernel.  All fields are per launch except `slope`,
+// which kernels fetch per (batch, head).
+// ---------------------------------------------------------------------------------------
+struct ScoreCfg {
+  float scale;        // softmax_scale
+  float scale_log2;   // softmax_scale * log2(e)
+  float softcap;      // 0 = off
+  float inv_softcap;  // 1/softcap
+  int causal;
+  int wl, wr;         // window; -1 = open
+  int has_alibi;
+};
+
+__host__ __device__ inline ScoreCfg make_score_cfg(float scale, float softcap, int causal, int wl,
+                                                   int wr, bool alibi) {
+  ScoreCfg c;
+  c.scale = scale;
+  c.scale_log2 = scale * FA_LOG2E;
+  c.softcap = softcap;
+  c.inv_softcap = softcap > 0.f ? 1.f / softcap : 0.f;
+  c.causal = causal;
+  c.wl = wl;
+  c.wr = wr;
+  c.has_alibi = alibi ? 1 : 0;
+  return c;
+}
+
+// tanh through one exp2: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.
+__device__ __forceinline__ float fast_tanh(float x) {
+  float e = exp2f(x * (2.f * FA_LOG2E));
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+
+// Raw dot product -> score in the log2 domain (unmasked).  `th` returns tanh(s/softcap)
+// when softcap is on (needed by the backward), else 0.
+__device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
+                                            int kpos, float& th) {
+  th = 0.f;
+  if (!c.has_alibi && c.softcap == 0.f) return dot * c.scale_log2;
+  float s = dot * c.scale;
+  if (c.has_alibi) s -= slope * fabsf((float)(qpos - kpos));
+  if (c.softcap > 0.f) {
+    th = fast_tanh(s * c.inv_softcap);
+    s = c.softcap * th;
+  }
+  return s * FA_LOG2E;
+}
+
+__device__ __forceinline__ bool visible(const ScoreCfg& c, int qpos, int kpos, int k_len) {
+  bool ok = kpos < k_len;
+  if (c.causal) ok = ok && (kpos <= qpos);
+  if (c.wl >= 0) ok = ok && (kpos >= qpos - c.wl);
+  if (c.wr >= 0) ok = ok && (kpos <= qpos + c.wr);
+  return ok;
+}
+
+// Key range [lo, hi) any query position in [qpos_min, qpos_max] can see.
+__device__ __forceinline__ void visible_key_range(const ScoreCfg& c, int qpos_min, int qpos_max,
+                                                  int k_len, int& lo, int& hi) {
+  int right = c.wr;                      // -1 open
+  if (c.causal) right = (right >= 0) ? min(right, 0) : 0;
+  hi = k_len;
+  if (right >= 0) hi = min(k_len, qpos_max + right + 1);
+  lo = 0;
+  if (c.wl >= 0) lo = max(0, qpos_min - c.wl);
+  if (hi < 0) hi = 0;
+  if (lo > hi) lo = hi;
+}
+
+// Query-position range [lo, hi) that can see any key in [k_min, k_max].
+__device__ __forceinline__ void visible_query_range(const ScoreCfg& c, int k_min, int k_max,
+                                                    int qpos_begin, int qpos_end, int& lo,
+                                                    int& hi) {
+  int right = c.wr;
+  if (c.causal) right = (right >= 0) ? min(right, 0) : 0;
+  lo = qpos_begin;
+  hi = qpos_end;
+  if (right >= 0) lo = max(lo, k_min - right);  // kpos <= qpos + right
+  if (c.wl >= 0) hi = min(hi, k_max + c.wl + 1);  // kpos >= qpos - wl
+  if (lo > hi) lo = hi;
+}
+
+// ---------------------------------------------------------------------------------------
+// element types
+// ---------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+
+// ---------------------------------------------------------------------------------------
+// warp-level MMA toolkit (mma.sync m16n8k16, ldmatrix, cp.async)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4],
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4],
+                                                        uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 16-byte async copy; bytes = 0 zero-fills the destination.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// Tile of ROWS x D elements in shared memory with a 16-byte pad per row (row pitch D+8):
+// ldmatrix over 8 consecutive rows then touches 8 different bank groups.
+template <int D> struct TilePitch { static constexpr int value = D + 8; };
+
+// Async-load `ROWS` rows of D elements (2-byte type) starting at global row `row0`;
+// rows >= rows_valid are zero-filled.  `NT` threads cooperate.
+template <int ROWS, int D, int NT, typename T>
+__device__ __forceinline__ void load_tile_async(T* smem, const T* gbase, int64_t row_stride,
+                                                int row0, int rows_valid, int tid) {
+  constexpr int CPR = D / 8;  // 16-byte chunks per row
+  constexpr int P = TilePitch<D>::value;
+  for (int i = tid; i < ROWS * CPR; i += NT) {
+    int r = i / CPR, c = i % CPR;
+    int gr = row0 + r;
+    bool ok = gr < rows_valid;
+    const T* src = gbase + (int64_t)(ok ? gr : 0) * row_stride + c * 8;
+    cp_async16(smem_u32(smem + r * P + c * 8), src, ok ? 16 : 0);
+  }
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  return v;
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------
+// per-sequence geometry (dense or packed)
+// ---------------------------------------------------------------------------------------
+struct SeqInfo {
+  int q_len, k_len;
+  int64_t q_row0, k_row0;  // first row of this sequence in the row dimension
+  int64_t q_boff, k_boff;  // 1 for dense (multiply stride[0] by batch), 0 for packed
+};
+
+__device__ __forceinline__ SeqInfo seq_info(const fa_attn_args& p, int b) {
+  SeqInfo s;
+  if (p.cu_seqlens_q) {
+    int q0 = p.cu_seqlens_q[b], q1 = p.cu_seqlens_q[b + 1];
+    int k0 = p.cu_seqlens_k[b], k1 = p.cu_seqlens_k[b + 1];
+    s.q_len = q1 - q0;
+    s.k_len = k1 - k0;
+    s.q_row0 = q0;
+    s.k_row0 = k0;
+    s.q_boff = 0;
+    s.k_boff = 0;
+  } else {
+    s.q_len = p.seqlen_q;
+    s.k_len = p.seqlen_k;
+    s.q_row0 = 0;
+    s.k_row0 = 0;
+    s.q_boff = b;
+    s.k_boff = b;
+  }
+  return s;
+}
+
+}  // namespace fa

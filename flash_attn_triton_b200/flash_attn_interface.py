@@ -1,0 +1,567 @@
+"""Public API: the same functions, argument names, defaults and ValueErrors as the
+reference's flash_attn_triton/flash_attn_interface.py, on top of the sm_100a kernels.
+
+What is different underneath (results are the same within fp16 tolerance):
+* tensors are handed to the kernels in place -- no pad-to-64, no head-major transposes,
+  no repeat_interleave for GQA (reference: flash_attn_interface.py:168-212, :300-317);
+* `flash_attn_with_kvcache` really appends to the cache, in place, and runs as one launch
+  chain with no host synchronisation (reference loops over the batch in Python, :501-525,
+  and its append at :487-492 writes into a temporary);
+* bf16 is accepted as well as fp16;
+* `use_native_gqa` and `deterministic` are accepted and change nothing: GQA is always native
+  and the backward always has a single writer per element.
+The eager "materialise the probabilities" paths (`return_attn_probs`, `attn_bias`) are kept
+as torch code like the reference's (:15-49, :139-148); fp32 inputs and `dropout_p > 0` use
+that path too.
+"""
+from __future__ import annotations
+
+import math
+import os
+
+import torch
+
+from . import _native as N
+from . import _ops
+
+_VALIDATE = os.environ.get("FA_B200_VALIDATE", "1") != "0"
+
+
+def set_validation(enabled: bool) -> None:
+    """Turn the value checks that need a device->host sync (page indices in range, lengths
+    fit the cache, cu_seqlens monotone ...) on or off.  Shape/dtype checks always run."""
+    global _VALIDATE
+    _VALIDATE = bool(enabled)
+
+
+_KERNEL_DTYPES = (torch.float16, torch.bfloat16)
+_ALL_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+
+
+def _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
+                          alibi_slopes, attn_bias=None, causal_offset=0):
+    """Eager path that materialises the probabilities (reference: flash_attn_interface.py:15-49).
+    Returns (out, natural-log lse, probs)."""
+    batch, q_len, q_heads, head_dim = q.shape
+    k_len, kv_heads = k.shape[1], k.shape[2]
+    if q_heads != kv_heads:
+        k = k.repeat_interleave(q_heads // kv_heads, dim=2)
+        v = v.repeat_interleave(q_heads // kv_heads, dim=2)
+    scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else softmax_scale
+    scores = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
+    q_pos = torch.arange(q_len, device=q.device) + causal_offset
+    k_pos = torch.arange(k_len, device=q.device)
+    keep = torch.ones((q_len, k_len), dtype=torch.bool, device=q.device)
+    if causal:
+        keep &= q_pos[:, None] >= k_pos[None, :]
+    if window_size[0] >= 0:
+        keep &= k_pos[None, :] >= q_pos[:, None] - window_size[0]
+    if window_size[1] >= 0:
+        keep &= k_pos[None, :] <= q_pos[:, None] + window_size[1]
+    if alibi_slopes is not None:
+        slopes = alibi_slopes if alibi_slopes.ndim == 2 else alibi_slopes[None, :]
+        scores = scores - slopes[:, :, None, None] * (q_pos[:, None] - k_pos[None, :]).abs()
+    if attn_bias is not None:
+        scores = scores + attn_bias
+    if softcap > 0:
+        scores = softcap * torch.tanh(scores / softcap)
+    scores = scores.float().masked_fill(~keep[None, None], float("-inf"))
+    probs = torch.nan_to_num(torch.softmax(scores, dim=-1))
+    lse = torch.logsumexp(scores, dim=-1)
+    if dropout_p:
+        probs = torch.nn.functional.dropout(probs, p=dropout_p, training=True)
+    out = torch.einsum("bhqk,bkhd->bqhd", probs.to(q.dtype), v)
+    return out, lse, probs
+
+
+def _normalise_alibi(alibi_slopes, batch, heads, device):
+    """(nheads,) or (batch, nheads) -> contiguous fp32 (batch, nheads); None stays None."""
+    if alibi_slopes is None:
+        return None
+    alibi_slopes = torch.as_tensor(alibi_slopes, device=device, dtype=torch.float32)
+    if alibi_slopes.ndim == 1:
+        if alibi_slopes.shape[0] != heads:
+            raise ValueError("alibi_slopes must have one value per query head")
+        alibi_slopes = alibi_slopes.unsqueeze(0).expand(batch, -1)
+    elif alibi_slopes.shape != (batch, heads):
+        raise ValueError("alibi_slopes must have shape (nheads,) or (batch, nheads)")
+    return alibi_slopes.contiguous()
+
+
+def _check_head_dim(d):
+    if d not in (16, 32, 64, 128, 256):
+        raise ValueError("head dimension must be one of 16, 32, 64, 128, or 256")
+
+
+def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
+                    window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
+                    deterministic=False, return_attn_probs=False, use_native_gqa=False,
+                    attn_bias=None):
+    """Attention over (batch, seqlen, nheads, headdim) tensors; k/v may have fewer heads
+    (GQA/MQA) and a different sequence length (upper-left aligned masks).
+    Same contract as the reference's flash_attn_func (flash_attn_interface.py:68-246)."""
+    if q.dtype not in _ALL_DTYPES:
+        raise ValueError("This implementation supports FP16, BF16 and FP32 tensors")
+    if softcap < 0.0:
+        raise ValueError("softcap must be non-negative")
+    if dropout_p < 0.0 or dropout_p >= 1.0:
+        raise ValueError("dropout_p must be in the range [0, 1)")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("All attention tensors must be CUDA tensors")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k, and v must have shape (batch, seqlen, heads, headdim)")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise ValueError("q, k, and v must have the same dtype")
+    if q.device != k.device or q.device != v.device:
+        raise ValueError("q, k, and v must be on the same CUDA device")
+    batch_size, seq_len_q, n_heads_q, head_dim = q.shape
+    key_batch_size, seq_len_k, n_heads_k, key_head_dim = k.shape
+    value_batch_size, value_seq_len, value_heads, value_head_dim = v.shape
+    if key_batch_size != batch_size or value_batch_size != batch_size:
+        raise ValueError("q, k, and v must have the same batch size")
+    if value_seq_len != seq_len_k:
+        raise ValueError("k and v must have the same sequence length")
+    if key_head_dim != head_dim or value_head_dim != head_dim:
+        raise ValueError("q, k, and v must have the same head dimension")
+    if value_heads != n_heads_k:
+        raise ValueError("k and v must have the same number of heads")
+    if n_heads_k == 0 or n_heads_q % n_heads_k != 0:
+        raise ValueError(
+            f"Number of heads in Q ({n_heads_q}) must be divisible by number of heads in K/V ({n_heads_k})"
+        )
+    alibi_slopes = _normalise_alibi(alibi_slopes, batch_size, n_heads_q, q.device)
+
+    if return_attn_probs:
+        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
+                                     softcap, alibi_slopes, attn_bias)
+    if attn_bias is not None or dropout_p > 0.0 or q.dtype == torch.float32:
+        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
+                                     softcap, alibi_slopes, attn_bias)[0].to(q.dtype)
+    _check_head_dim(head_dim)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(head_dim)
+    return _ops.DenseAttention.apply(q, k, v, softmax_scale, causal, window_size[0],
+                                     window_size[1], softcap, alibi_slopes, 0, N.IMPL_AUTO, "bshd")
+
+
+def flash_attn_func_cross(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
+                          use_native_gqa=False, softcap=0.0, alibi_slopes=None,
+                          window_size=(-1, -1), deterministic=False,
+                          return_attn_probs=False, attn_bias=None, _causal_offset=0):
+    """Cross-attention for unequal query and KV lengths (flash_attn_interface.py:249-330).
+    Query row i sits at position i + _causal_offset (0 = upper-left alignment)."""
+    if q.dtype not in _ALL_DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("flash_attn_func_cross supports matching FP16, BF16 or FP32 tensors")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("All attention tensors must be CUDA tensors")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k, and v must have shape (batch, seqlen, heads, headdim)")
+    if q.device != k.device or q.device != v.device:
+        raise ValueError("q, k, and v must be on the same CUDA device")
+    if k.shape[0] != q.shape[0] or v.shape[:2] != k.shape[:2]:
+        raise ValueError("q, k, and v have incompatible batch or sequence dimensions")
+    if q.shape[-1] != k.shape[-1] or k.shape[-1] != v.shape[-1]:
+        raise ValueError("q, k, and v must have the same head dimension")
+    _check_head_dim(q.shape[-1])
+    if k.shape[2] == 0 or q.shape[2] % k.shape[2] != 0 or v.shape[2] != k.shape[2]:
+        raise ValueError("The number of query heads must be divisible by KV heads")
+    if dropout_p < 0.0 or dropout_p >= 1.0:
+        raise ValueError("dropout_p must be in the range [0, 1)")
+    if softcap < 0.0:
+        raise ValueError("softcap must be non-negative")
+    alibi_slopes = _normalise_alibi(alibi_slopes, q.shape[0], q.shape[2], q.device)
+    if return_attn_probs:
+        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
+                                     softcap, alibi_slopes, attn_bias, causal_offset=_causal_offset)
+    if attn_bias is not None or dropout_p > 0.0 or q.dtype == torch.float32:
+        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
+                                     softcap, alibi_slopes, attn_bias,
+                                     causal_offset=_causal_offset)[0].to(q.dtype)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    return _ops.DenseAttention.apply(q, k, v, softmax_scale, causal, window_size[0],
+                                     window_size[1], softcap, alibi_slopes, int(_causal_offset),
+                                     N.IMPL_AUTO, "bshd")
+
+
+def flash_attn_qkvpacked_func(qkv, dropout_p=0.0, softmax_scale=None, causal=False,
+                              window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
+                              deterministic=False, return_attn_probs=False, use_native_gqa=False,
+                              attn_bias=None):
+    """qkv: (batch, seqlen, 3, nheads, headdim).  The three slices are read in place through
+    their strides (flash_attn_interface.py:337-371 copies them)."""
+    if qkv.ndim != 5 or qkv.shape[2] != 3:
+        raise ValueError("qkv must have shape (batch, seqlen, 3, nheads, headdim)")
+    q, k, v = qkv.unbind(dim=2)
+    return flash_attn_func(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
+                           alibi_slopes, deterministic, return_attn_probs, use_native_gqa, attn_bias)
+
+
+def flash_attn_kvpacked_func(q, kv, dropout_p=0.0, softmax_scale=None, causal=False,
+                             window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
+                             deterministic=False, return_attn_probs=False, use_native_gqa=False,
+                             attn_bias=None):
+    """q: (batch, seqlen_q, nheads, headdim); kv: (batch, seqlen_k, 2, nheads_k, headdim)
+    (flash_attn_interface.py:374-406)."""
+    if kv.ndim != 5 or kv.shape[2] != 2:
+        raise ValueError("kv must have shape (batch, seqlen, 2, nheads_k, headdim)")
+    k, v = kv.unbind(dim=2)
+    return flash_attn_func(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
+                           alibi_slopes, deterministic, return_attn_probs, use_native_gqa, attn_bias)
+
+
+def _as_i32(x, device):
+    return torch.as_tensor(x, device=device).to(torch.int32).flatten().contiguous()
+
+
+def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None, rotary_sin=None,
+                            cache_seqlens=None, cache_batch_idx=None, cache_leftpad=None,
+                            block_table=None, softmax_scale=None, causal=False,
+                            window_size=(-1, -1), rotary_interleaved=True, alibi_slopes=None,
+                            num_splits=0):
+    """Attention against a KV cache, optionally appending new k/v first (in place) with
+    rotary embedding applied to the new keys and to q.
+
+    Contract of the reference's flash_attn_with_kvcache (flash_attn_interface.py:409-525):
+    q (batch, seqlen_q, nheads, d); cache (batch_cache, capacity, nheads_k, d) or paged
+    (num_pages, page_size, nheads_k, d) with block_table (batch, max_pages);
+    cache_seqlens = tokens already in the cache before this call.  The query rows are the
+    last seqlen_q positions of the sequence after the append; causal, window and ALiBi are
+    measured from there.  `num_splits` (0 = automatic) is an extra tuning knob."""
+    paged = block_table is not None
+    if (rotary_cos is None) != (rotary_sin is None):
+        raise ValueError("rotary_cos and rotary_sin must be supplied together")
+    if q.ndim != 4 or k_cache.ndim != 4 or v_cache.ndim != 4:
+        raise ValueError("q and KV caches must be rank-4 tensors")
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    if not (q.is_cuda and k_cache.is_cuda and v_cache.is_cuda):
+        raise ValueError("All attention tensors must be CUDA tensors")
+    B = q.shape[0]
+    dev = q.device
+    if paged:
+        if block_table.ndim != 2 or block_table.shape[0] != B:
+            raise ValueError("block_table must have shape (batch, max_num_pages)")
+        if block_table.dtype not in (torch.int32, torch.int64):
+            raise ValueError("block_table must contain integer page indices")
+        if cache_leftpad is not None:
+            raise ValueError("cache_leftpad cannot be combined with paged KV caches")
+        if cache_batch_idx is not None:
+            raise ValueError("cache_batch_idx cannot be combined with paged KV caches")
+        page_size = k_cache.shape[1]
+        cache_capacity = block_table.shape[1] * page_size
+        if _VALIDATE and (torch.any(block_table < 0) or torch.any(block_table >= k_cache.shape[0])):
+            raise ValueError("block_table contains an invalid physical page index")
+        block_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+    else:
+        cache_capacity = k_cache.shape[1]
+    if q.shape[-1] != k_cache.shape[-1]:
+        raise ValueError("q and KV cache dimensions are incompatible")
+    if q.device != k_cache.device or q.device != v_cache.device:
+        raise ValueError("q and KV caches must be on the same device")
+    if q.dtype != k_cache.dtype or q.dtype != v_cache.dtype:
+        raise ValueError("q and KV caches must have the same dtype")
+    if q.dtype not in _KERNEL_DTYPES:
+        raise ValueError("flash_attn_with_kvcache supports FP16 and BF16 tensors")
+    _check_head_dim(q.shape[-1])
+    if k_cache.shape[2] == 0 or q.shape[2] % k_cache.shape[2] != 0:
+        raise ValueError("The number of query heads must be divisible by KV heads")
+    if k_cache.stride(-1) != 1 or v_cache.stride(-1) != 1 or not (
+            N.kernel_ready(k_cache) and N.kernel_ready(v_cache)):
+        raise ValueError("KV caches must have a unit head-dim stride and 16-byte aligned rows")
+    rows = None
+    if cache_batch_idx is not None:
+        rows = _as_i32(cache_batch_idx, dev)
+        if rows.numel() != B or (_VALIDATE and (torch.any(rows < 0) or torch.any(rows >= k_cache.shape[0]))):
+            raise ValueError("cache_batch_idx must contain valid cache-row indices")
+    elif not paged and k_cache.shape[0] < B:
+        raise ValueError("cache_batch_idx must contain valid cache-row indices")
+    pads = None
+    if cache_leftpad is not None:
+        pads = _as_i32(cache_leftpad, dev)
+        if pads.numel() != B or (_VALIDATE and torch.any(pads < 0)):
+            raise ValueError("cache_leftpad must contain one non-negative value per query batch")
+    n_new = 0
+    if k is not None or v is not None:
+        if k is None or v is None or k.shape != v.shape:
+            raise ValueError("k and v must be supplied together with matching shapes")
+        if k.ndim != 4 or k.shape[0] != B or k.shape[2:] != k_cache.shape[2:]:
+            raise ValueError("new k/v tensors are incompatible with the cache")
+        if k.dtype != q.dtype or v.dtype != q.dtype:
+            raise ValueError("q and KV caches must have the same dtype")
+        n_new = k.shape[1]
+        if cache_seqlens is None:
+            cache_seqlens = torch.zeros(B, dtype=torch.int32, device=dev)
+        lengths = _as_i32(cache_seqlens, dev)
+        if lengths.numel() != B:
+            raise ValueError("new KV tensors do not fit in the cache")
+        if _VALIDATE:
+            total = lengths.long() + n_new + (pads.long() if pads is not None else 0)
+            if torch.any(lengths < 0) or torch.any(total > cache_capacity):
+                raise ValueError("new KV tensors do not fit in the cache")
+        if n_new == 0:
+            k = v = None
+    else:
+        if cache_seqlens is None:
+            lengths = torch.full((B,), cache_capacity, dtype=torch.int32, device=dev)
+        else:
+            lengths = _as_i32(cache_seqlens, dev)
+        if lengths.numel() != B:
+            raise ValueError("cache_seqlens must contain valid lengths for every batch item")
+        if _VALIDATE:
+            total = lengths.long() + (pads.long() if pads is not None else 0)
+            if torch.any(lengths < 0) or torch.any(total > cache_capacity):
+                raise ValueError("cache_seqlens must contain valid lengths for every batch item")
+    cos = sin = None
+    if rotary_cos is not None:
+        if rotary_cos.shape != rotary_sin.shape or rotary_cos.ndim != 2:
+            raise ValueError("rotary_cos and rotary_sin must be (seqlen_ro, rotary_dim / 2)")
+        if rotary_cos.shape[-1] * 2 > q.shape[-1]:
+            raise ValueError("rotary tables exceed the head dimension")
+        cos = rotary_cos.to(device=dev, dtype=q.dtype).contiguous()
+        sin = rotary_sin.to(device=dev, dtype=q.dtype).contiguous()
+    alibi = _normalise_alibi(alibi_slopes, B, q.shape[2], dev)
+    if B == 0 or q.shape[1] == 0:
+        return q.new_empty(q.shape)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    return _ops.kvcache_decode(q, k_cache, v_cache, k, v, cos, sin, lengths, rows, pads,
+                               block_table, softmax_scale, causal, window_size[0], window_size[1],
+                               rotary_interleaved, alibi, num_splits)
+
+
+def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                           dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                           softcap=0.0, alibi_slopes=None, deterministic=False,
+                           return_attn_probs=False, block_table=None, seqused_q=None,
+                           seqused_k=None, **kwargs):
+    """Attention over packed variable-length sequences (flash_attn_interface.py:527-690):
+    q (total_q, nheads, d), k/v (total_k, nheads_k, d), int32 cu_seqlens on the device.
+    Each sequence is masked with upper-left alignment."""
+    if block_table is not None:
+        if k.ndim != 4 or v.ndim != 4 or k.shape != v.shape:
+            raise ValueError("paged varlen k and v must have shape (pages, page_size, heads, dim)")
+        if block_table.ndim != 2 or block_table.shape[0] != cu_seqlens_k.numel() - 1:
+            raise ValueError("block_table must have shape (batch, max_num_pages)")
+        page_size = k.shape[1]
+        bounds = cu_seqlens_k.tolist()
+        page_parts, value_parts = [], []
+        for b in range(block_table.shape[0]):
+            length = bounds[b + 1] - bounds[b]
+            page_ids = block_table[b, :(length + page_size - 1) // page_size].to(torch.long)
+            if torch.any(page_ids < 0) or torch.any(page_ids >= k.shape[0]):
+                raise ValueError("block_table contains an invalid physical page index")
+            page_parts.append(k[page_ids].reshape(-1, k.shape[2], k.shape[3])[:length])
+            value_parts.append(v[page_ids].reshape(-1, v.shape[2], v.shape[3])[:length])
+        k = torch.cat(page_parts, dim=0) if page_parts else k.new_empty((0, k.shape[2], k.shape[3]))
+        v = torch.cat(value_parts, dim=0) if value_parts else v.new_empty((0, v.shape[2], v.shape[3]))
+    batch_size = cu_seqlens_q.numel() - 1
+    if seqused_q is not None:
+        used = torch.as_tensor(seqused_q).to(torch.int64).flatten().tolist()
+        if len(used) != batch_size:
+            raise ValueError("seqused_q must contain one value per sequence")
+        bounds = cu_seqlens_q.tolist()
+        parts = []
+        for b in range(batch_size):
+            if used[b] < 0 or used[b] > bounds[b + 1] - bounds[b]:
+                raise ValueError("seqused_q exceeds the packed query sequence")
+            parts.append(q[bounds[b]:bounds[b] + used[b]])
+        q = torch.cat(parts, dim=0) if parts else q[:0]
+        cu_seqlens_q = torch.tensor([0] + torch.tensor(used).cumsum(0).tolist(), device=q.device,
+                                    dtype=torch.int32)
+    if seqused_k is not None:
+        used = torch.as_tensor(seqused_k).to(torch.int64).flatten().tolist()
+        if len(used) != batch_size:
+            raise ValueError("seqused_k must contain one value per sequence")
+        bounds = cu_seqlens_k.tolist()
+        kp, vp = [], []
+        for b in range(batch_size):
+            if used[b] < 0 or used[b] > bounds[b + 1] - bounds[b]:
+                raise ValueError("seqused_k exceeds the packed KV sequence")
+            kp.append(k[bounds[b]:bounds[b] + used[b]])
+            vp.append(v[bounds[b]:bounds[b] + used[b]])
+        k = torch.cat(kp, dim=0) if kp else k[:0]
+        v = torch.cat(vp, dim=0) if vp else v[:0]
+        cu_seqlens_k = torch.tensor([0] + torch.tensor(used).cumsum(0).tolist(), device=k.device,
+                                    dtype=torch.int32)
+    if q.ndim != 3 or k.ndim != 3 or v.ndim != 3 or k.shape != v.shape:
+        raise ValueError("packed q, k, and v must be rank-3 tensors with matching KV shapes")
+    if cu_seqlens_q.ndim != 1 or cu_seqlens_k.ndim != 1:
+        raise ValueError("cu_seqlens arrays must be one-dimensional")
+    if cu_seqlens_q.numel() != cu_seqlens_k.numel():
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must describe the same batch size")
+    if cu_seqlens_q.numel() < 2:
+        raise ValueError("cu_seqlens arrays must describe at least one sequence")
+    if q.dtype not in _ALL_DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("flash_attn_varlen_func supports matching FP16, BF16 or FP32 tensors")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("All attention tensors must be CUDA tensors")
+    if q.device != k.device or q.device != v.device:
+        raise ValueError("q, k, and v must be on the same CUDA device")
+    if q.shape[-1] != k.shape[-1] or k.shape[-1] != v.shape[-1]:
+        raise ValueError("q, k, and v must have the same head dimension")
+    _check_head_dim(q.shape[-1])
+    if k.shape[1] == 0 or q.shape[1] % k.shape[1] != 0:
+        raise ValueError("The number of query heads must be divisible by KV heads")
+    if dropout_p < 0.0 or dropout_p >= 1.0:
+        raise ValueError("dropout_p must be in the range [0, 1)")
+    if softcap < 0.0:
+        raise ValueError("softcap must be non-negative")
+    if cu_seqlens_q.device != q.device or cu_seqlens_k.device != q.device:
+        raise ValueError("cu_seqlens arrays must be on the same CUDA device as q, k, and v")
+    if max_seqlen_q < 0 or max_seqlen_k < 0:
+        raise ValueError("max sequence lengths must be non-negative")
+    cu_seqlens_q = cu_seqlens_q.to(dtype=torch.int32).contiguous()
+    cu_seqlens_k = cu_seqlens_k.to(dtype=torch.int32).contiguous()
+    if _VALIDATE:
+        # one device->host transfer for every value check the reference makes (:588-626)
+        cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+        if cq[0] != 0 or ck[0] != 0:
+            raise ValueError("cu_seqlens arrays must start at zero and contain a batch boundary")
+        if any(b < a for a, b in zip(cq, cq[1:])) or any(b < a for a, b in zip(ck, ck[1:])):
+            raise ValueError("cu_seqlens arrays must be monotonically non-decreasing")
+        if cq[-1] != q.shape[0] or ck[-1] != k.shape[0]:
+            raise ValueError("cu_seqlens arrays must cover the packed q and KV tensors")
+        if max_seqlen_q < max(b - a for a, b in zip(cq, cq[1:])) or \
+                max_seqlen_k < max(b - a for a, b in zip(ck, ck[1:])):
+            raise ValueError("max sequence lengths must cover every packed sequence")
+    if max_seqlen_q == 0 or max_seqlen_k == 0:
+        return q.new_zeros((q.shape[0], q.shape[1], q.shape[2]))
+    alibi = _normalise_alibi(alibi_slopes, batch_size, q.shape[1], q.device)
+    eager = return_attn_probs or dropout_p > 0.0 or q.dtype == torch.float32
+    if eager:
+        cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+        outputs = []
+        lses = q.new_full((batch_size, q.shape[1], max_seqlen_q), float("-inf"), dtype=torch.float32)
+        probabilities = q.new_zeros((batch_size, q.shape[1], max_seqlen_q, max_seqlen_k),
+                                    dtype=torch.float32) if return_attn_probs else None
+        for b in range(batch_size):
+            out, lse, probs = _attention_with_probs(
+                q[cq[b]:cq[b + 1]].unsqueeze(0), k[ck[b]:ck[b + 1]].unsqueeze(0),
+                v[ck[b]:ck[b + 1]].unsqueeze(0), dropout_p, softmax_scale, causal, window_size,
+                softcap, None if alibi is None else alibi[b:b + 1])
+            outputs.append(out.squeeze(0))
+            if return_attn_probs:
+                lses[b, :, :cq[b + 1] - cq[b]] = lse[0]
+                probabilities[b, :, :cq[b + 1] - cq[b], :ck[b + 1] - ck[b]] = probs[0]
+        out = torch.cat(outputs, dim=0).to(q.dtype)
+        return (out, lses, probabilities) if return_attn_probs else out
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    return _ops.VarlenAttention.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q),
+                                      int(max_seqlen_k), softmax_scale, causal, window_size[0],
+                                      window_size[1], softcap, alibi, N.IMPL_AUTO)
+
+
+def flash_attn_varlen_kvpacked_func(q, kv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
+                                    max_seqlen_k, dropout_p=0.0, softmax_scale=None,
+                                    causal=False, **kwargs):
+    """kv: (total_k, 2, nheads_k, d) (flash_attn_interface.py:692-699)."""
+    k, v = kv.unbind(dim=1)
+    return flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                  dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                                  **kwargs)
+
+
+def flash_attn_varlen_qkvpacked_func(qkv, cu_seqlens, max_seqlen, dropout_p=0.0,
+                                     softmax_scale=None, causal=False, **kwargs):
+    """qkv: (total, 3, nheads, d) (flash_attn_interface.py:702-708)."""
+    q, k, v = qkv.unbind(dim=1)
+    return flash_attn_varlen_func(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen,
+                                  dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                                  **kwargs)
+
+
+def attention_int8(q, k, v, causal=False, sm_scale=None, seq_len_k=None, seq_len_q=None):
+    """INT8-QK^T attention on contiguous fp16 [B, H, S, D] tensors; fp16 backward.
+    Same contract as the reference's attention_int8 (attention_kernel_int8.py:270-299) minus
+    its Turing-only gate: this one runs on sm_100."""
+    head_dim = q.shape[-1]
+    if not q.is_cuda:
+        raise ValueError("The INT8 kernel requires CUDA tensors")
+    if q.dtype != torch.float16 or k.dtype != torch.float16 or v.dtype != torch.float16:
+        raise ValueError("The INT8 kernel requires FP16 tensors")
+    if head_dim < 32 or head_dim & (head_dim - 1):
+        raise ValueError("The INT8 kernel requires a power-of-two head dim of at least 32")
+    if q.shape[2] % 64:
+        raise ValueError("The INT8 kernel requires sequence lengths divisible by 64")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("The INT8 kernel requires contiguous inputs")
+    if q.shape[2] != k.shape[2] or k.shape[2] != v.shape[2]:
+        raise ValueError("The INT8 kernel requires equal sequence lengths")
+    if q.shape != k.shape or q.shape != v.shape:
+        raise ValueError("The INT8 kernel requires q, k and v of the same shape")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    return _ops.Int8Attention.apply(q, k, v, causal, sm_scale, N.IMPL_AUTO)
+
+
+class FlashSelfAttention(torch.nn.Module):
+    """Self-attention over packed qkv (flash_attn_interface.py:711-736)."""
+
+    def __init__(self, causal=False, softmax_scale=None, attention_dropout=0.0,
+                 window_size=(-1, -1), alibi_slopes=None, deterministic=False):
+        super().__init__()
+        self.causal = causal
+        self.softmax_scale = softmax_scale
+        self.drop = torch.nn.Dropout(attention_dropout)
+        self.window_size = window_size
+        self.alibi_slopes = alibi_slopes
+        self.deterministic = deterministic
+
+    def forward(self, qkv, causal=None, cu_seqlens=None, max_seqlen=None):
+        dropout_p = self.drop.p if self.training else 0.0
+        causal = self.causal if causal is None else causal
+        if cu_seqlens is None:
+            return flash_attn_qkvpacked_func(qkv, dropout_p, self.softmax_scale, causal,
+                                             self.window_size, 0.0, self.alibi_slopes,
+                                             self.deterministic)
+        return flash_attn_varlen_qkvpacked_func(qkv, cu_seqlens, max_seqlen, dropout_p,
+                                                self.softmax_scale, causal,
+                                                window_size=self.window_size,
+                                                alibi_slopes=self.alibi_slopes,
+                                                deterministic=self.deterministic)
+
+
+class FlashCrossAttention(torch.nn.Module):
+    """Cross-attention over q and packed kv (flash_attn_interface.py:739-770)."""
+
+    def __init__(self, causal=False, softmax_scale=None, attention_dropout=0.0,
+                 window_size=(-1, -1), alibi_slopes=None, deterministic=False):
+        super().__init__()
+        self.causal = causal
+        self.softmax_scale = softmax_scale
+        self.drop = torch.nn.Dropout(attention_dropout)
+        self.window_size = window_size
+        self.alibi_slopes = alibi_slopes
+        self.deterministic = deterministic
+
+    def forward(self, q, kv, causal=None, cu_seqlens=None, max_seqlen=None, cu_seqlens_k=None,
+                max_seqlen_k=None):
+        dropout_p = self.drop.p if self.training else 0.0
+        causal = self.causal if causal is None else causal
+        if cu_seqlens is None:
+            k, v = kv.unbind(dim=2)
+            return flash_attn_func_cross(q, k, v, dropout_p, self.softmax_scale, causal,
+                                         use_native_gqa=not self.training, softcap=0.0,
+                                         alibi_slopes=self.alibi_slopes,
+                                         window_size=self.window_size,
+                                         deterministic=self.deterministic)
+        k, v = kv.unbind(dim=1)
+        return flash_attn_varlen_func(q, k, v, cu_seqlens, cu_seqlens_k, max_seqlen, max_seqlen_k,
+                                      dropout_p, self.softmax_scale, causal,
+                                      window_size=self.window_size, alibi_slopes=self.alibi_slopes,
+                                      deterministic=self.deterministic)
+
+
+class FlashAttention(torch.nn.Module):
+    """Module form of flash_attn_func (flash_attn_interface.py:773-804)."""
+
+    def __init__(self, attention_dropout=0.0, softmax_scale=None):
+        super().__init__()
+        self.dropout_p = attention_dropout
+        self.softmax_scale = softmax_scale
+
+    def forward(self, q, k, v, causal=False, attn_bias=None):
+        return flash_attn_func(q, k, v, dropout_p=self.dropout_p if self.training else 0.0,
+                               softmax_scale=self.softmax_scale, causal=causal, attn_bias=attn_bias)

@@ -1,0 +1,217 @@
+/*
+ * fa_b200.h -- C ABI of the B200 (sm_100a) attention kernels.
+ *
+ * The reference (luyanaa/flash-attn-triton) has no FFI: its operator boundary is the
+ * Python layer that launches Triton kernels.  Each entry point below replaces one of
+ * those launch sites; the citation gives the reference file:line it stands in for.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller.  The library allocates
+ *     nothing and keeps no state between calls (besides a thread-local error string
+ *     and one-time function-attribute set-up per device).
+ *   - Strides are in ELEMENTS.  The innermost (head_dim) stride is always 1.
+ *   - All work is enqueued on `stream` (a cudaStream_t passed as void*); calls return
+ *     without synchronising.
+ *   - Return value: 0 on success, a negative fa_status otherwise; fa_last_error() gives
+ *     a message for the calling thread.
+ *   - Row-wise log-sum-exp values are BASE-2 (lse2 = log2(sum exp(score))), -inf for a
+ *     row with no visible key, as the reference saves them
+ *     (flash_attn_triton/triton_kernel/attention_kernel.py:522-533).
+ *   - Score pipeline, in this order (flash_attn_triton/flash_attn_interface.py:26-43):
+ *       s = q.k * softmax_scale;  s -= slope * |qpos - kpos|;  s = softcap*tanh(s/softcap);
+ *       mask (causal: kpos <= qpos; window: qpos-left <= kpos <= qpos+right) -> -inf
+ *     with qpos = row + q_pos_offset (0 = upper-left alignment) and kpos = column.
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fa_status {
+  FA_OK = 0,
+  FA_ERR_INVALID = -1,     /* bad argument (null pointer, bad shape, bad stride)       */
+  FA_ERR_UNSUPPORTED = -2, /* valid but no kernel is instantiated for it               */
+  FA_ERR_LAUNCH = -3,      /* CUDA reported an error at launch                         */
+  FA_ERR_WORKSPACE = -4,   /* caller's workspace is too small                          */
+  FA_ERR_DEVICE_WAIT = -5  /* a bounded device-side wait ran out (kernel set its flag) */
+} fa_status;
+
+typedef enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 } fa_dtype;
+
+/* Kernel family selector (fa_attn_args.impl). */
+typedef enum fa_impl {
+  FA_IMPL_AUTO = 0,   /* tcgen05/TMA kernel when the shape has one, else the mma.sync one */
+  FA_IMPL_MMA = 1,    /* warp-level mma.sync kernels (every head_dim, every feature)      */
+  FA_IMPL_TCGEN05 = 2 /* tcgen05 + TMEM + TMA kernels; FA_ERR_UNSUPPORTED if none fits    */
+} fa_impl;
+
+/*
+ * One argument block for dense and packed variable-length attention, forward and
+ * backward.  Tensors are addressed as  base + b*stride[0] + row*stride[1] + head*stride[2] + d.
+ * Dense:   q (batch, seqlen_q, heads_q, head_dim), k/v (batch, seqlen_k, heads_kv, head_dim).
+ * Varlen:  cu_seqlens_* non-null; sequence b owns rows [cu[b], cu[b+1]) of the packed
+ *          tensors, stride[0] is ignored, seqlen_q/seqlen_k are the MAXIMA over the batch.
+ * GQA:     query head h reads kv head h / (heads_q / heads_kv)
+ *          (attention_kernel.py:446, :49).
+ */
+typedef struct fa_attn_args {
+  int32_t dtype;  /* fa_dtype */
+  int32_t device; /* CUDA device ordinal that owns the pointers */
+  int32_t impl;   /* fa_impl */
+  int32_t batch, seqlen_q, seqlen_k, heads_q, heads_kv, head_dim;
+
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o; /* forward: output; backward: the forward's output (read only) */
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
+
+  float* lse2; /* forward: written when non-null; backward: read */
+  int64_t lse_stride[3]; /* (batch, row, head); varlen ignores [0] */
+
+  const int32_t* cu_seqlens_q; /* (batch+1) or NULL */
+  const int32_t* cu_seqlens_k;
+
+  float softmax_scale;
+  float softcap;             /* 0 = off */
+  const float* alibi_slopes; /* (batch, heads_q) fp32 or NULL */
+  int32_t causal;
+  int32_t window_left, window_right; /* -1 = unbounded */
+  int32_t q_pos_offset;              /* added to the query row index; dense only */
+
+  /* backward only */
+  const void* dout;
+  int64_t do_stride[3];
+  float* delta; /* rowsum(o * dout), same layout as lse2 */
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+} fa_attn_args;
+
+/* Forward: o and (optionally) lse2.
+ * Replaces _launch_dense_forward/_attn_fwd (attention_kernel.py:1057-1101, :419-533) and
+ * _attention_varlen.forward/_varlen_fwd (attention_kernel.py:1284-1320, :27-104). */
+int fa_fwd(const fa_attn_args* args, void* stream);
+
+/* delta[b,h,row] = sum_d o*dout in fp32.
+ * Replaces _attn_bwd_preprocess (attention_kernel.py:536-563, launched at :1127). */
+int fa_bwd_preprocess(const fa_attn_args* args, void* stream);
+
+/* dq from q,k,v,dout,lse2,delta; one writer per element, no atomics.
+ * Replaces the dQ half of _attn_bwd (attention_kernel.py:677-772, :975-1054) and
+ * _varlen_bwd (attention_kernel.py:107-186). */
+int fa_bwd_dq(const fa_attn_args* args, void* stream);
+
+/* dk, dv; a CTA owns a key block of one KV head and loops its query heads, so every
+ * element has one writer (deterministic).
+ * Replaces the dK/dV half of _attn_bwd (attention_kernel.py:567-673, :873-962) and
+ * _varlen_bwd_dkdv (attention_kernel.py:188-272). */
+int fa_bwd_dkdv(const fa_attn_args* args, void* stream);
+
+/* Same three operations, but cu_seqlens_q/k are mandatory (the packed layout). */
+int fa_varlen_fwd(const fa_attn_args* args, void* stream);
+int fa_varlen_bwd_dq(const fa_attn_args* args, void* stream);
+int fa_varlen_bwd_dkdv(const fa_attn_args* args, void* stream);
+
+/*
+ * KV-cache decode: append (optional) -> rotary (optional) -> attend, one launch chain.
+ * Replaces the Python per-batch loop of flash_attn_with_kvcache
+ * (flash_attn_interface.py:468-525) including _apply_rotary (:52-66), the cache append
+ * (:482-492, performed IN PLACE here) and the page gather (:510-512).
+ *
+ * Cache layout: (num_pages, page_size, heads_kv, head_dim); a contiguous cache is the same
+ * thing with page_size = capacity and block_table = NULL (sequence b uses "page"
+ * cache_batch_idx[b], or b).  Token t of sequence b lives in page
+ * block_table[b*block_table_stride + (t+leftpad)/page_size] at row (t+leftpad)%page_size.
+ * The query rows sit at the END of the sequence: row i has position len_after-seqlen_q+i
+ * (flash_attn_interface.py:517, :523).
+ */
+typedef struct fa_decode_args {
+  int32_t dtype, device;
+  int32_t batch, seqlen_q, heads_q, heads_kv, head_dim;
+  const void* q;
+  void* o;
+  int64_t q_stride[3], o_stride[3];
+
+  void* k_cache;
+  void* v_cache;
+  int64_t kc_stride[3], vc_stride[3]; /* (page, row, head) */
+  int32_t page_size, num_pages;
+  const int32_t* block_table; /* (batch, block_table_stride) or NULL */
+  int32_t block_table_stride;
+  const int32_t* cache_batch_idx; /* (batch) or NULL; contiguous cache only */
+  const int32_t* cache_seqlens;   /* (batch) tokens already cached, BEFORE the append  */
+  const int32_t* cache_leftpad;   /* (batch) or NULL */
+
+  const void* k_new; /* (batch, seqlen_new, heads_kv, head_dim) or NULL */
+  const void* v_new;
+  int64_t kn_stride[3], vn_stride[3];
+  int32_t seqlen_new;
+
+  const void* rotary_cos; /* (rotary_seqlen, rotary_dim/2), same dtype as q; or NULL */
+  const void* rotary_sin;
+  int32_t rotary_dim, rotary_seqlen, rotary_interleaved;
+
+  float softmax_scale;
+  const float* alibi_slopes; /* (batch, heads_q) or NULL */
+  int32_t causal, window_left, window_right;
+
+  void* workspace; /* split-KV partials; size from fa_decode_workspace_bytes */
+  size_t workspace_bytes;
+  int32_t num_splits; /* 0 = choose */
+} fa_decode_args;
+
+int fa_decode_paged(const fa_decode_args* args, void* stream);
+
+/* Bytes of workspace fa_decode_paged needs for this problem (host-only, no CUDA call). */
+size_t fa_decode_workspace_bytes(const fa_decode_args* args);
+
+/*
+ * Per-key-token INT8 quantisation: k (rows, head_dim) fp16 contiguous ->
+ * k8 (rows, head_dim) int8, s_k (rows) fp32, with
+ *   s = max(absmax, 1)/127;  code = round_half_away(k * (1/s))  in IEEE fp32,
+ * bit-exact with _quantize_k_rows (attention_kernel_int8.py:58-79, :27-30).
+ */
+int fa_quantize_k_int8(const void* k, int8_t* k8, float* s_k, int64_t rows, int32_t head_dim,
+                       int32_t device, void* stream);
+
+/*
+ * INT8-QK^T forward on contiguous (batch, heads, seqlen, head_dim) fp16 tensors:
+ * q is quantised per row in-kernel, k8/s_k come from fa_quantize_k_int8, P@V stays fp16.
+ * Replaces _attn_fwd_int8 (attention_kernel_int8.py:167-217, launched at :237).
+ */
+typedef struct fa_int8_args {
+  int32_t device, impl;
+  int32_t batch, heads, seqlen, head_dim;
+  const void* q;    /* fp16 */
+  const int8_t* k8; /* (batch*heads, seqlen, head_dim) */
+  const float* s_k; /* (batch*heads, seqlen) */
+  const void* v;    /* fp16 */
+  void* o;          /* fp16 */
+  float* lse2;      /* (batch, heads, seqlen) or NULL */
+  float softmax_scale;
+  int32_t causal;
+} fa_int8_args;
+
+int fa_fwd_int8(const fa_int8_args* args, void* stream);
+
+/* Host-only helpers. */
+const char* fa_version(void);
+const char* fa_last_error(void);
+/* 1 when fa_fwd with FA_IMPL_AUTO would pick the tcgen05 kernel for these arguments. */
+int fa_fwd_uses_tcgen05(const fa_attn_args* args);
+/* sizeof of an argument block as this library was compiled: 0 = fa_attn_args,
+ * 1 = fa_decode_args, 2 = fa_int8_args.  Lets a foreign-language binding check its
+ * struct layout before the first call. */
+size_t fa_sizeof_args(int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */

@@ -306,3 +306,28 @@ def attention_int8_ref(q, k, v, causal=False, sm_scale=None):
     out = torch.einsum("bhqk,bhkd->bhqd", p.half().float(), v.float()) / l
     lse2 = (m + torch.log2(l)).squeeze(-1)
     return out, lse2, k8, s_k
+
+
+def attention_int8_grads_ref(q, k, v, dout, causal=False, sm_scale=None):
+    """Gradients the INT8 path returns: the fp16 dense backward run on the ORIGINAL fp16
+    q,k,v with the base-2 LSE and the output saved by the INT8 forward
+    (attention_kernel_int8.py:256-267 -> attention_kernel.py:1104-1155).  So
+    P = exp2(q.k*scale*log2e - lse2_int8) is not exactly normalised, and
+    delta = rowsum(o_int8 * dout).  q,k,v,dout: (B,H,S,D).  Returns fp32 (dq, dk, dv)."""
+    B, H, S, D = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    out, lse2, _, _ = attention_int8_ref(q, k, v, causal, sm_scale)
+    o16 = out.half().float()
+    qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
+    s2 = torch.einsum("bhqd,bhkd->bhqk", qf, kf) * (sm_scale * LOG2E)
+    p = torch.exp2(s2 - lse2[..., None])
+    if causal:
+        p = p * keep_mask(S, S, True, (-1, -1))[None, None]
+    delta = (o16 * dof).sum(-1, keepdim=True)
+    dp = torch.einsum("bhqd,bhkd->bhqk", dof, vf)
+    ds = p * (dp - delta)
+    dv = torch.einsum("bhqk,bhqd->bhkd", p, dof)
+    dq = torch.einsum("bhqk,bhkd->bhqd", ds, kf) * sm_scale
+    dk = torch.einsum("bhqk,bhqd->bhkd", ds, qf) * sm_scale
+    return dq, dk, dv

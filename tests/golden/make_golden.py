@@ -145,6 +145,14 @@ def int8():
         out = AK8._attention_int8.forward(ctx, q, k, v, causal, 1.0 / 128 ** 0.5, 256, 256)
         save(f"int8_fwd_causal{int(causal)}", checksum=cases.checksum(q, k, v), out=out,
              lse2=ctx.saved[4])
+        # forward + backward at the shape of the reference's own INT8 test (:222-235)
+        q, k, v = cases.int8_case(31, 2, 2, 128, 64)
+        do = cases.randn16(np.random.default_rng(32), 2, 2, 128, 64)
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        out = AK8._attention_int8.apply(qg, kg, vg, causal, 0.125, 128, 128)
+        dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
+        save(f"int8_bwd_causal{int(causal)}", checksum=cases.checksum(q, k, v, do), out=out,
+             dq=dq, dk=dk, dv=dv)
 
 
 def kvcache():
@@ -175,8 +183,7 @@ def kvcache():
 
 if __name__ == "__main__":
     torch.manual_seed(0)
-    dense_lowlevel()
-    dense_public()
-    varlen()
-    int8()
-    kvcache()
+    only = sys.argv[2:]
+    for fn in (dense_lowlevel, dense_public, varlen, int8, kvcache):
+        if not only or fn.__name__ in only:
+            fn()

@@ -99,6 +99,19 @@ def test_int8_forward(golden, causal):
     assert maxdiff(lse2, g["lse2"]) <= FWD_TOL
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+def test_int8_backward(golden, causal):
+    g = golden(f"int8_bwd_causal{causal}")
+    q, k, v = cases.int8_case(31, 2, 2, 128, 64)
+    do = cases.randn16(np.random.default_rng(32), 2, 2, 128, 64)
+    assert cases.checksum(q, k, v, do) == str(g["checksum"])
+    out, _, _, _ = orc.attention_int8_ref(q, k, v, causal=bool(causal), sm_scale=0.125)
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    dq, dk, dv = orc.attention_int8_grads_ref(q, k, v, do, causal=bool(causal), sm_scale=0.125)
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t, g[name]) <= GRAD_TOL, name
+
+
 def test_kvcache_paged(golden):
     g = golden("kvcache_paged")
     lens = g["lens"].tolist()
