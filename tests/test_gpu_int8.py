@@ -63,8 +63,10 @@ def test_int8_forward_backward_vs_oracle(shape, causal):
     # backward = fp16 dense backward with the INT8 forward's LSE and output
     # (attention_kernel_int8.py:256-267), restated by attention_int8_grads_ref
     rdq, rdk, rdv = orc.attention_int8_grads_ref(q, k, v, do, causal=causal, sm_scale=0.125)
+    # K carries x8 outliers, so dq reaches magnitudes of 20-30 where one fp16 rounding step
+    # of the stored gradient is already 1.6e-2: allow that step on top of the 1e-2 bar
     for t, r in ((dq, rdq), (dk, rdk), (dv, rdv)):
-        assert maxdiff(t, r) <= util.GRAD_TOL
+        assert util.excess(t, r) <= util.GRAD_TOL
 
 
 @pytest.mark.parametrize("causal", [0, 1])
@@ -91,7 +93,7 @@ def test_golden_int8_backward(golden, causal):
                                                    causal=bool(causal))
     assert maxdiff(tr(out), ro) <= INT8_GRAD_TOL
     for t, r in zip(grads, (rdq, rdk, rdv)):
-        assert maxdiff(tr(t), r) <= INT8_GRAD_TOL
+        assert util.excess(tr(t), r, rel=2e-2) <= INT8_GRAD_TOL  # atol and rtol of the reference's test
 
 
 def test_int8_value_errors():

@@ -32,3 +32,11 @@ def run_dense(fn, q, k, v, do, **kw):
     out = fn(qd, kd, vd, **kw)
     dq, dk, dv = torch.autograd.grad((out.float() * do.to(DEV).float()).sum(), (qd, kd, vd))
     return out.detach().cpu(), dq.cpu(), dk.cpu(), dv.cpu()
+
+
+def excess(a, b, rel=2.0 ** -10):
+    """max(|a-b| - rel*|b|): the max-abs error left after allowing one fp16 rounding step
+    of the reference value (values of magnitude 16-32 have an fp16 spacing of 2^-6)."""
+    a = torch.as_tensor(a).float().cpu()
+    b = torch.as_tensor(b).float().cpu()
+    return ((a - b).abs() - rel * b.abs()).max().item()
