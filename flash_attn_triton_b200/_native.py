@@ -23,6 +23,7 @@ class AttnArgs(C.Structure):
         ("dtype", C.c_int32), ("device", C.c_int32), ("impl", C.c_int32),
         ("batch", C.c_int32), ("seqlen_q", C.c_int32), ("seqlen_k", C.c_int32),
         ("heads_q", C.c_int32), ("heads_kv", C.c_int32), ("head_dim", C.c_int32),
+        ("total_q", C.c_int32), ("total_k", C.c_int32),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
         ("q_stride", _I64x3), ("k_stride", _I64x3), ("v_stride", _I64x3), ("o_stride", _I64x3),
         ("lse2", C.c_void_p), ("lse_stride", _I64x3),
@@ -84,6 +85,7 @@ EXPORTS = {
     "fa_version": (C.c_char_p, []),
     "fa_last_error": (C.c_char_p, []),
     "fa_fwd_uses_tcgen05": (C.c_int, [C.POINTER(AttnArgs)]),
+    "fa_device_wait_status": (C.c_int, [C.c_int]),
     "fa_sizeof_args": (C.c_size_t, [C.c_int]),
 }
 

@@ -38,6 +38,8 @@ def _fill_common(a, q, k, v, o, dims_q, dims_k, *, batch, sq, sk, hq, hkv, d, sc
     a.o_stride = N.strides3(o, dims_q)
     a.cu_seqlens_q = N.ptr(cu_q)
     a.cu_seqlens_k = N.ptr(cu_k)
+    if cu_q is not None:
+        a.total_q, a.total_k = q.shape[0], k.shape[0]
     a.softmax_scale = float(scale)
     a.softcap = float(softcap)
     a.alibi_slopes = _alibi_ptr(alibi)

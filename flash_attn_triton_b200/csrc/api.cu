@@ -53,6 +53,7 @@ int quantize_k(const void*, int8_t*, float*, int64_t, int, cudaStream_t);
 int fwd_int8_mma(const fa_int8_args&, cudaStream_t);
 bool fwd_int8_sm100_supported(const fa_int8_args&);
 int fwd_int8_sm100(const fa_int8_args&, cudaStream_t);
+int fwd_sm100_status();
 
 static bool mult8(const int64_t* s, int n) {
   for (int i = 0; i < n; ++i)
@@ -74,7 +75,10 @@ static int validate_common(const fa_attn_args* a, bool need_cu) {
   FA_REQUIRE((a->cu_seqlens_q == nullptr) == (a->cu_seqlens_k == nullptr),
              "cu_seqlens_q and cu_seqlens_k must be given together");
   if (need_cu) FA_REQUIRE(a->cu_seqlens_q != nullptr, "packed layout needs cu_seqlens_q/k");
-  if (a->cu_seqlens_q) FA_REQUIRE(a->q_pos_offset == 0, "q_pos_offset is dense-only");
+  if (a->cu_seqlens_q) {
+    FA_REQUIRE(a->q_pos_offset == 0, "q_pos_offset is dense-only");
+    FA_REQUIRE(a->total_q >= 0 && a->total_k >= 0, "total_q/total_k must be the packed row counts");
+  }
   const bool empty = a->batch == 0 || a->seqlen_q == 0;
   if (!empty) {
     FA_REQUIRE(a->q && a->o, "q/o is NULL");
@@ -255,6 +259,16 @@ const char* fa_version(void) { return "fa_b200 0.1 (sm_100a)"; }
 const char* fa_last_error(void) { return g_err; }
 int fa_fwd_uses_tcgen05(const fa_attn_args* a) {
   return a != nullptr && a->impl != FA_IMPL_MMA && fwd_sm100_supported(*a) ? 1 : 0;
+}
+
+int fa_device_wait_status(int device) {
+  if (int r = ensure_device(device)) return r;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_error("cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    return FA_ERR_LAUNCH;
+  }
+  return fwd_sm100_status();
 }
 
 size_t fa_sizeof_args(int which) {

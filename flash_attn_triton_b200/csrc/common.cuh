@@ -55,6 +55,13 @@ __host__ __device__ inline ScoreCfg make_score_cfg(float scale, float softcap, i
   return c;
 }
 
+// ex2.approx without the denormal handling exp2f() adds
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // tanh through one exp2: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.
 __device__ __forceinline__ float fast_tanh(float x) {
   float e = exp2f(x * (2.f * FA_LOG2E));

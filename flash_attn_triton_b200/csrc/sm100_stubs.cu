@@ -5,6 +5,7 @@ namespace fa {
 #ifndef FA_HAVE_FWD_SM100
 bool fwd_sm100_supported(const fa_attn_args&) { return false; }
 int fwd_sm100(const fa_attn_args&, const ScoreCfg&, cudaStream_t) { set_error("not built"); return FA_ERR_UNSUPPORTED; }
+int fwd_sm100_status() { return 0; }
 #endif
 #ifndef FA_HAVE_BWD_SM100
 bool bwd_sm100_supported(const fa_attn_args&) { return false; }

@@ -64,6 +64,7 @@ typedef struct fa_attn_args {
   int32_t device; /* CUDA device ordinal that owns the pointers */
   int32_t impl;   /* fa_impl */
   int32_t batch, seqlen_q, seqlen_k, heads_q, heads_kv, head_dim;
+  int32_t total_q, total_k; /* packed layout only: rows of q and of k/v (= cu_seqlens[batch]) */
 
   const void* q;
   const void* k;
@@ -206,6 +207,10 @@ const char* fa_version(void);
 const char* fa_last_error(void);
 /* 1 when fa_fwd with FA_IMPL_AUTO would pick the tcgen05 kernel for these arguments. */
 int fa_fwd_uses_tcgen05(const fa_attn_args* args);
+/* Status word of the tcgen05 kernels' bounded waits on `device`: 0, or the code of the wait
+ * that ran out (the kernel then released its tensor memory and returned early, leaving its
+ * outputs incomplete).  Synchronises the device. */
+int fa_device_wait_status(int device);
 /* sizeof of an argument block as this library was compiled: 0 = fa_attn_args,
  * 1 = fa_decode_args, 2 = fa_int8_args.  Lets a foreign-language binding check its
  * struct layout before the first call. */
