@@ -8,6 +8,8 @@
 //   warps 4-7   softmax group of tile 1
 //   warp  8     TMA producer            : Q tiles once, then K/V tiles through a ring
 //   warp  9     MMA issuer (one thread) : S_t = Q_t K^T (SS), O_t += P_t V (A = P from TMEM)
+//   warps 10-11 idle; they complete the third warpgroup so that it can hand its registers
+//               to the softmax groups (setmaxnreg)
 //
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each (O uses head_dim columns).
 // P (fp16/bf16) overwrites the first 64 columns of its S.  The running row maximum is only
@@ -33,7 +35,7 @@ namespace {
 
 constexpr int kBM = 128;          // rows per Q tile
 constexpr int kBN = 128;          // keys per K/V tile
-constexpr int kThreads = 320;     // 8 softmax warps + producer + MMA
+constexpr int kThreads = 384;     // 8 softmax warps + a warpgroup holding producer and MMA warps
 constexpr float kRescaleThreshold = 8.0f;
 
 template <int D> struct Cfg {
@@ -131,8 +133,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tS[2] = {tmem, tmem + 128};
   const uint32_t tO[2] = {tmem + 256, tmem + 384};
 
-  if (warp == 8) {
+  if (warp >= 10) {
+    // idle warps of the producer/MMA warpgroup
+    reg_dealloc<56>();
+  } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
+    reg_dealloc<56>();
     if (lane == 0 && nsteps > 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
@@ -170,6 +176,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
+    reg_dealloc<56>();
     if (lane == 0 && nsteps > 0) {
       constexpr uint32_t idesc_qk = make_idesc(1, Fmt<T>::code, 0, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(1, Fmt<T>::code, 0, 1, kBM, D);
@@ -235,6 +242,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------- softmax groups -------------------------------------
+    reg_alloc<224>();
     const int t = warp >> 2;                        // Q tile of this group
     const int row_in_tile = (warp & 3) * 32 + lane; // TMEM lane
     const int row = m0 + t * kBM + row_in_tile;     // query row inside the sequence
@@ -258,26 +266,45 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
 
-      // ---- pass 1: row maximum (log2 domain) --------------------------------------------
-      float mx = -INFINITY;
+      // ---- all 128 scores of this row into registers (one wait for four loads) ----------
+      uint32_t r[4][32];
 #pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS[t] + lane_addr + c * 32, r);
-        tmem_wait_ld();
+      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS[t] + lane_addr + c * 32, r[c]);
+      tmem_wait_ld();
+
+      if (kExtras || masked) {
+        // score pipeline and mask applied once, in place; values end up in the log2 domain
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          const int col = k0 + c * 32 + i;
-          if (kExtras) {
-            float th;
-            v = score_log2(cfg, slope, v, qpos, col, th);
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(r[c][i]);
+            const int col = k0 + c * 32 + i;
+            if (kExtras) {
+              float th;
+              v = score_log2(cfg, slope, v, qpos, col, th);
+            } else {
+              v *= cfg.scale_log2;
+            }
+            if (masked && !visible(cfg, qpos, col, si.k_len)) v = -INFINITY;
+            r[c][i] = __float_as_uint(v);
           }
-          if (masked && !visible(cfg, qpos, col, si.k_len)) v = -INFINITY;
-          mx = fmaxf(mx, v);
         }
       }
-      if (!kExtras) mx *= cfg.scale_log2;  // scale >= 0 on this path
+      const bool prescaled = kExtras || masked;
+
+      // ---- row maximum: four independent chains ------------------------------------------
+      float mx4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float a = fmaxf(__uint_as_float(r[c][0]), __uint_as_float(r[c][1]));
+#pragma unroll
+        for (int i = 2; i < 32; i += 2)
+          a = fmaxf(a, fmaxf(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])));
+        mx4[c] = a;
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
 
       // ---- lazy rescale ----------------------------------------------------------------
       if (j == 0) {
@@ -295,48 +322,34 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO[t] + lane_addr + c * 32, r);
+            uint32_t ro[32];
+            tmem_ld32(tO[t] + lane_addr + c * 32, ro);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO[t] + lane_addr + c * 32, r);
+            for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+            tmem_st32(tO[t] + lane_addr + c * 32, ro);
           }
           tmem_wait_st();
         }
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      const float mul = prescaled ? 1.f : cfg.scale_log2;
 
-      // ---- pass 2: P = exp2(s - m), row sum, P -> TMEM (in place over S) ----------------
-      float psum = 0.f;
+      // ---- P = exp2(s - m), row sum (four chains), P -> TMEM in place over S -------------
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS[t] + lane_addr + c * 32, r);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
-          const int col = k0 + c * 32 + i;
-          if (kExtras) {
-            float th;
-            v0 = score_log2(cfg, slope, v0, qpos, col, th) - m_safe;
-            v1 = score_log2(cfg, slope, v1, qpos, col + 1, th) - m_safe;
-          } else {
-            v0 = fmaf(v0, cfg.scale_log2, -m_safe);
-            v1 = fmaf(v1, cfg.scale_log2, -m_safe);
-          }
-          float p0 = ex2(v0), p1 = ex2(v1);
-          if (masked) {
-            if (!visible(cfg, qpos, col, si.k_len)) p0 = 0.f;
-            if (!visible(cfg, qpos, col + 1, si.k_len)) p1 = 0.f;
-          }
-          psum += p0 + p1;
+          const float p0 = ex2(fmaf(__uint_as_float(r[c][i]), mul, -m_safe));
+          const float p1 = ex2(fmaf(__uint_as_float(r[c][i + 1]), mul, -m_safe));
+          ps[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = Elem<T>::pack(p0, p1);
         }
         tmem_st16(tS[t] + lane_addr + c * 16, pk);
       }
+      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       l += psum;
       tmem_wait_st();
       tc_fence_before();

@@ -232,6 +232,14 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// Register re-balancing between warpgroups (all 4 warps of the group execute it together).
+template <int N> __device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N));
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
