@@ -56,6 +56,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     srcs = _sources()
     defs = [f"-D{HAVE[s]}" for s in srcs if s in HAVE]
+    if os.environ.get("FA_TRACE"):
+        defs.append("-DFA_TRACE")
     rebuilt = False
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         for src, log, did in ex.map(lambda s: _compile(s, defs, force, verbose), srcs):

@@ -1,26 +1,29 @@
 // Forward attention on the 5th-generation tensor cores: TMA-staged tiles, tcgen05.mma with
 // accumulators in tensor memory, warp-specialised online softmax.
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles.  Keys are consumed
-// in half-steps of 64; every Q tile has TWO score buffers in tensor memory, so the MMA of
-// half-step i+1 is already queued while the softmax warps work on half-step i, and the
-// tensor pipe and the exp units overlap instead of waiting for each other:
+// One CTA owns 128 query rows of one (batch, head).  Keys arrive in tiles of 128; the score
+// tile S = Q K^T (128 x 128, one N=128 MMA chain) is DOUBLE-BUFFERED in tensor memory, so
+// the tensor pipe computes S(j+1) while the softmax warps are still working on S(j).
+// The two column halves of every score tile are two independent online-softmax streams,
+// each owned by one warpgroup with its own running maximum, row sum and output accumulator
+// (like a 2-way split over keys, merged in the epilogue):
 //
-//   warps 0-3   softmax group of tile 0 : one query row per thread (TMEM lane = row)
-//   warps 4-7   softmax group of tile 1
-//   warp  8     TMA producer            : Q tiles once, then K/V tiles through a ring
-//   warp  9     MMA issuer (one thread) : S_t = Q_t K^T (SS), O_t += P_t V (A = P from TMEM)
+//   warps 0-3   softmax group A : columns   0..63 of every score tile, accumulator O_a
+//   warps 4-7   softmax group B : columns 64..127 of every score tile, accumulator O_b
+//   warp  8     TMA producer    : Q once, then K/V tiles through a ring
+//   warp  9     MMA issuer      : S = Q K^T (SS);  O_x += P_x V[x-half] (A = P_x from TMEM)
 //   warps 10-11 idle; they complete the third warpgroup so that it can hand its registers
 //               to the softmax groups (setmaxnreg)
 //
-// TMEM (512 columns): S0a S0b | S1a S1b | O0 | O1 (score buffers 64 fp32 columns each,
-// O head_dim columns).  P (fp16/bf16) overwrites the first 32 columns of its score buffer.  The running row maximum is only
-// raised when it grows by more than 2^8 ("lazy rescale"), so the O accumulator in TMEM is
-// rarely touched by the softmax warps; exactness is kept because O and the row sum always
-// share the same reference maximum.
+// One thread owns one query row of its stream (TMEM lane = row).  P (fp16/bf16) overwrites
+// the first 32 columns of its half of S.  The running maximum is only raised when it grows
+// by more than 2^8 ("lazy rescale"), so O is rarely touched by the softmax warps; exactness
+// is kept because O and the row sum of a stream always share the same reference maximum.
 //
-// Shared memory: Q0,Q1 (128 x D each) + a ring of K/V tiles (128 keys x D), every tile
-// written by TMA with the 128-byte swizzle the MMA descriptors expect.
+// TMEM (512 columns): S[0] | S[1] | O_a | O_b, 128 fp32 columns each (O uses head_dim).
+// Shared memory: Q (128 x D) + a ring of K/V tiles (128 keys x D), written by TMA with the
+// 128-byte swizzle the MMA descriptors expect.  Ring order = order of use:
+// K0, K1, V0, K2, V1, K3, ...
 //
 // Every mbarrier wait is bounded; on timeout the CTA raises a device-side status word,
 // releases its TMEM and returns.
@@ -33,36 +36,50 @@ using namespace sm100;
 
 __device__ int g_fwd_sm100_status = 0;
 
+#ifdef FA_TRACE
+// Timeline of one CTA (blockIdx 0,0,0) for kernel tuning: clock64 stamps per role and step.
+__device__ long long g_fwd_trace[3][32][8];
+#define FA_TRACE_EV(role, step, ev)                                                          \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (step) < 32 &&              \
+        (threadIdx.x & 31) == 0)                                                             \
+      g_fwd_trace[role][step][ev] = clock64();                                               \
+  } while (0)
+#else
+#define FA_TRACE_EV(role, step, ev) do {} while (0)
+#endif
+
 namespace {
 
-constexpr int kBM = 128;          // rows per Q tile
+constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 128;          // keys per K/V tile
+constexpr int kHalf = 64;         // keys per softmax stream and tile
 constexpr int kThreads = 384;     // 8 softmax warps + a warpgroup holding producer and MMA warps
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kMaxStages = 8;
 
 template <int D> struct Cfg {
   static constexpr int kTileBytes = kBN * D * 2;                    // one Q/K/V tile
-  static constexpr int kStages = (D == 128) ? 4 : 6;                // K/V ring depth
+  static constexpr int kStages = (D == 128) ? 5 : 8;                // K/V ring depth
   static constexpr int kBoxes = D / 64;                             // TMA boxes per tile
-  static constexpr int kSmemTiles = (2 + kStages) * kTileBytes;
-  static constexpr int kSmemBytes = kSmemTiles + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemTiles = (1 + kStages) * kTileBytes;
+  static constexpr int kSmemBytes = kSmemTiles + 1024 /*align slack*/ + 4096 /*barriers, merge*/;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
-
-constexpr int kHalf = 64;         // keys per half-step
 
 struct Shared {
-  uint64_t q_full[2];
-  uint64_t kv_full[6];
-  uint64_t kv_empty[6];
-  uint64_t s_full[2][2];   // [tile][buffer]
-  uint64_t p_ready[2][2];  // [tile][buffer]
-  uint64_t o_ready[2][2];  // [tile][parity of the PV index]: see the note at the waits
+  uint64_t q_full;
+  uint64_t kv_full[kMaxStages];
+  uint64_t kv_empty[kMaxStages];
+  uint64_t s_full[2];      // [score buffer]
+  uint64_t p_ready[2][2];  // [stream][score buffer]
+  uint64_t o_ready[2][2];  // [stream][parity of the PV index]: see the note at the waits
   uint32_t tmem_base;
   volatile int abort_flag;
+  float2 ml[2][kBM];       // epilogue exchange: (reference max, row sum) of each stream
 };
 
-__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Shared* sh, int code) {
-  const uint32_t a = smem_u32(bar);
+__device__ __forceinline__ bool wait_bar_slow(uint32_t a, uint32_t parity, Shared* sh, int code) {
   const long long t0 = clock64();
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(a, parity)) return true;
@@ -76,10 +93,18 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Shared*
     }
   }
 }
+// Bounded wait on an mbarrier phase; the common "already complete" case costs one try_wait.
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Shared* sh, int code) {
+  const uint32_t a = smem_u32(bar);
+  if (mbar_try_wait(a, parity)) return true;
+  return wait_bar_slow(a, parity, sh, code);
+}
 
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> { static constexpr int code = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int code = 1; };
+
+static_assert(sizeof(Shared) <= 4096, "Shared must fit its reserve");
 
 }  // namespace
 
@@ -94,46 +119,30 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   Shared* sh = reinterpret_cast<Shared*>(tiles + C::kSmemTiles);
   const uint32_t sQ = smem_u32(tiles);
-  const uint32_t sKV = sQ + 2 * C::kTileBytes;
+  const uint32_t sKV = sQ + C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int mblk = cfg.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy blocks first
   const SeqInfo si = seq_info(p, b);
-  const int m0 = mblk * 2 * kBM;
+  const int m0 = mblk * kBM;
   if (m0 >= si.q_len) return;
   const int hk = h / (p.heads_q / p.heads_kv);
   const int off = p.q_pos_offset;
 
-  // Half-step ranges [glo_t, ghi_t) of the two Q tiles (half-step g covers keys
-  // [64g, 64g+64)), their union, and the K/V tiles (128 keys) the union touches.
-  int glo_t[2], ghi_t[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int r_first = m0 + t * kBM, r_last = min(r_first + kBM, si.q_len) - 1;
-    if (r_last < r_first) {
-      glo_t[t] = ghi_t[t] = 0;
-    } else {
-      int klo, khi;
-      visible_key_range(cfg, r_first + off, r_last + off, si.k_len, klo, khi);
-      glo_t[t] = klo / kHalf;
-      ghi_t[t] = (khi + kHalf - 1) / kHalf;
-      if (ghi_t[t] <= glo_t[t]) glo_t[t] = ghi_t[t] = 0;
-    }
-  }
-  const bool any0 = ghi_t[0] > glo_t[0], any1 = ghi_t[1] > glo_t[1];
-  const int glo = any0 ? (any1 ? min(glo_t[0], glo_t[1]) : glo_t[0]) : glo_t[1];
-  const int ghi = max(any0 ? ghi_t[0] : 0, any1 ? ghi_t[1] : 0);
-  const bool any = any0 || any1;
-  const int T0 = glo >> 1;                       // first K/V tile
-  const int T1 = any ? ((ghi - 1) >> 1) + 1 : T0;  // one past the last K/V tile
+  // K/V tiles [n_lo, n_hi) that any of this CTA's rows can see
+  int klo, khi;
+  visible_key_range(cfg, m0 + off, min(m0 + kBM, si.q_len) - 1 + off, si.k_len, klo, khi);
+  const int n_lo = klo / kBN;
+  const int n_hi = (khi + kBN - 1) / kBN;
+  const int nsteps = max(n_hi - n_lo, 0);
 
   if (tid == 0) {
+    mbar_init(smem_u32(&sh->q_full), 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&sh->q_full[i]), 1);
+      mbar_init(smem_u32(&sh->s_full[i]), 1);
       for (int k = 0; k < 2; ++k) {
         mbar_init(smem_u32(&sh->o_ready[i][k]), 1);
-        mbar_init(smem_u32(&sh->s_full[i][k]), 1);
         mbar_init(smem_u32(&sh->p_ready[i][k]), 128);
       }
     }
@@ -159,23 +168,21 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
     reg_dealloc<56>();
-    if (lane == 0 && any) {
+    if (lane == 0 && nsteps > 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
-      const int qrow = (int)si.q_row0 + m0;
       const int krow0 = (int)si.k_row0;
-      const int qb = (int)si.q_boff, kb = (int)si.k_boff;
-      auto load_q = [&](int t) {
-        const uint32_t bar = smem_u32(&sh->q_full[t]);
+      const int kb = (int)si.k_boff;
+      {
+        const uint32_t bar = smem_u32(&sh->q_full);
         mbar_expect_tx(bar, C::kTileBytes);
         for (int x = 0; x < C::kBoxes; ++x)
-          tma_load_4d(sQ + t * C::kTileBytes + x * (kBM * 128), &tmQ, bar, x * 64, h, qrow + t * kBM, qb);
-      };
+          tma_load_4d(sQ + x * (kBM * 128), &tmQ, bar, x * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      // ring order: K[T0], V[T0], K[T0+1], V[T0+1], ...
       auto load_kv = [&](const CUtensorMap* tm, int tile) {
         if (!ok) return;
         ok = wait_bar(&sh->kv_empty[stage], phase ^ 1, sh, 11);
@@ -187,133 +194,116 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       krow0 + tile * kBN, kb);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       };
-      load_q(0);
-      load_kv(&tmK, T0);
-      load_q(1);
-      for (int tl = T0; tl < T1; ++tl) {
-        load_kv(&tmV, tl);
-        if (tl + 1 < T1) load_kv(&tmK, tl + 1);
+      // order of use: K0, K1, then V_j, K_{j+2}
+      load_kv(&tmK, n_lo);
+      if (nsteps > 1) load_kv(&tmK, n_lo + 1);
+      for (int j = 0; j < nsteps; ++j) {
+        load_kv(&tmV, n_lo + j);
+        if (j + 2 < nsteps) load_kv(&tmK, n_lo + j + 2);
       }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
+    // The whole warp runs the control flow (so it stays warp-uniform and cheap); one elected
+    // lane issues the MMAs and commits.
     reg_dealloc<56>();
-    if (lane == 0 && any) {
-      constexpr uint32_t idesc_qk = make_idesc(1, Fmt<T>::code, 0, 0, kBM, kHalf);
+    if (nsteps > 0) {
+      constexpr uint32_t idesc_qk = make_idesc(1, Fmt<T>::code, 0, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(1, Fmt<T>::code, 0, 1, kBM, D);
+      int stage = 0;
+      uint32_t phase = 0;
       bool ok = true;
-      int waited = 0;  // ring slots [0, waited) are known to be full
-      // ring slot of K tile tl is 2*(tl-T0), of V tile tl 2*(tl-T0)+1
-      auto slot_addr = [&](int slot) { return sKV + (slot % C::kStages) * C::kTileBytes; };
-      auto wait_slot = [&](int slot) {
-        while (ok && waited <= slot) {
-          ok = wait_bar(&sh->kv_full[waited % C::kStages], (waited / C::kStages) & 1, sh, 22);
-          ++waited;
-        }
-        if (ok) tc_fence_after();
-      };
-      auto release_slot = [&](int slot) { mma_commit(smem_u32(&sh->kv_empty[slot % C::kStages])); };
-      int cqk[2] = {0, 0}, cpv[2] = {0, 0};
-      // S_t[buf] = Q_t K[g]^T for half-step g
-      auto issue_qk = [&](int t, int g) {
-        const int slot = 2 * ((g >> 1) - T0);
-        wait_slot(slot);
-        if (!ok) return;
-        const int buf = cqk[t] & 1;
-        const uint32_t kbase = slot_addr(slot) + (g & 1) * (kHalf * 128);
-        const uint32_t d = tmem + t * 128 + buf * kHalf;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t o = (kk / 4) * (kBM * 128) + (kk % 4) * 32;
-          mma_f16_ss(d, make_smem_desc(sQ + t * C::kTileBytes + o, 16, 1024),
-                     make_smem_desc(kbase + o, 16, 1024), idesc_qk, kk > 0);
-        }
-        mma_commit(smem_u32(&sh->s_full[t][buf]));
-        ++cqk[t];
-      };
-      // O_t += P_t[buf] V[g]
-      auto issue_pv = [&](int t, int g) {
-        const int slot = 2 * ((g >> 1) - T0) + 1;
-        wait_slot(slot);
-        if (!ok) return;
-        const int buf = cpv[t] & 1;
-        ok = wait_bar(&sh->p_ready[t][buf], (cpv[t] >> 1) & 1, sh, 25 + t);
-        if (!ok) return;
+      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
+        bool w = true;
+        if (lane == 0) w = wait_bar(bar, parity, sh, code);
+        ok = __all_sync(0xffffffffu, w) && ok;
         tc_fence_after();
-        const uint32_t vbase = slot_addr(slot) + (g & 1) * (kHalf * 128);
-        const uint32_t a = tmem + t * 128 + buf * kHalf;
+      };
+      auto advance = [&]() { if (++stage == C::kStages) { stage = 0; phase ^= 1; } };
+      auto issue_qk = [&](int buf) {
+        wwait(&sh->kv_full[stage], phase, 22);
+        if (!ok) return;
+        const uint32_t kbase = sKV + stage * C::kTileBytes;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < kHalf / 16; ++kk)
-          mma_f16_ts(tmem + 256 + t * 128, a + kk * 8, make_smem_desc(vbase + kk * 2048, kBN * 128, 1024),
-                     idesc_pv, (cpv[t] > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(smem_u32(&sh->o_ready[t][cpv[t] & 1]));
-        ++cpv[t];
-      };
-      auto in_range = [&](int t, int g) { return g >= glo_t[t] && g < ghi_t[t]; };
-      // A K (V) tile is free once both Q tiles have issued every QK (PV) that reads it; the
-      // commit then covers all MMAs issued so far.  Tiles are released in ring order.
-      int k_rel = T0, v_rel = T0;
-      auto done_upto = [&](const int (&cnt)[2], int tl) {
-        return glo_t[0] + cnt[0] >= min(ghi_t[0], 2 * tl + 2) &&
-               glo_t[1] + cnt[1] >= min(ghi_t[1], 2 * tl + 2);
-      };
-      auto release_ready = [&]() {
-        while (k_rel < T1 && done_upto(cqk, k_rel)) release_slot(2 * (k_rel++ - T0));
-        while (v_rel < T1 && done_upto(cpv, v_rel)) release_slot(2 * (v_rel++ - T0) + 1);
-      };
-
-      ok = wait_bar(&sh->q_full[0], 0, sh, 21);
-      // prologue: the first two half-steps of each tile
-      for (int t = 0; t < 2 && ok; ++t) {
-        if (t == 1) ok = wait_bar(&sh->q_full[1], 0, sh, 23);
-        for (int g = glo_t[t]; g < min(glo_t[t] + 2, ghi_t[t]) && ok; ++g) {
-          issue_qk(t, g);
-          if (ok) release_ready();
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t o = (kk / 4) * (kBM * 128) + (kk % 4) * 32;
+            mma_f16_ss(tmem + buf * kBN, make_smem_desc(sQ + o, 16, 1024),
+                       make_smem_desc(kbase + o, 16, 1024), idesc_qk, kk > 0);
+          }
+          mma_commit(smem_u32(&sh->s_full[buf]));
+          mma_commit(smem_u32(&sh->kv_empty[stage]));
         }
-      }
-      for (int g = glo; g < ghi && ok; ++g) {
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (!in_range(t, g)) continue;
-          issue_pv(t, g);
-          if (ok && in_range(t, g + 2)) issue_qk(t, g + 2);
-          if (ok) release_ready();
+        __syncwarp();
+        advance();
+      };
+      wwait(&sh->q_full, 0, 21);
+      if (ok) issue_qk(0);
+      if (ok && nsteps > 1) issue_qk(1);
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int buf = j & 1;
+        FA_TRACE_EV(2, j, 0);
+        wwait(&sh->kv_full[stage], phase, 24);
+        const uint32_t vbase = sKV + stage * C::kTileBytes;
+        FA_TRACE_EV(2, j, 1);
+        for (int x = 0; x < 2 && ok; ++x) {
+          wwait(&sh->p_ready[x][buf], (j >> 1) & 1, 25 + x);
+          if (!ok) break;
+          FA_TRACE_EV(2, j, 2 + x);
+          if (elect_one()) {
+            const uint32_t a = tmem + buf * kBN + x * kHalf;
+#pragma unroll
+            for (int kk = 0; kk < kHalf / 16; ++kk)
+              mma_f16_ts(tmem + 256 + x * 128, a + kk * 8,
+                         make_smem_desc(vbase + x * (kHalf * 128) + kk * 2048, kBN * 128, 1024), idesc_pv,
+                         (j > 0 || kk > 0) ? 1u : 0u);
+            mma_commit(smem_u32(&sh->o_ready[x][j & 1]));
+            if (x == 1) mma_commit(smem_u32(&sh->kv_empty[stage]));
+          }
+          __syncwarp();
         }
+        if (!ok) break;
+        advance();
+        FA_TRACE_EV(2, j, 4);
+        if (j + 2 < nsteps) issue_qk(buf);
+        FA_TRACE_EV(2, j, 5);
       }
     }
   } else {
     // ------------------------------- softmax groups -------------------------------------
     reg_alloc<224>();
-    const int t = warp >> 2;                        // Q tile of this group
-    const int row_in_tile = (warp & 3) * 32 + lane; // TMEM lane
-    const int row = m0 + t * kBM + row_in_tile;     // query row inside the sequence
+    const int x = warp >> 2;                         // stream: column half of every score tile
+    const int row_in_tile = (warp & 3) * 32 + lane;  // TMEM lane
+    const int row = m0 + row_in_tile;                // query row inside the sequence
     const int qpos = row + off;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tSb = tmem + t * 128 + lane_addr;
-    const uint32_t tOt = tmem + 256 + t * 128 + lane_addr;
+    const uint32_t tSx = tmem + lane_addr + x * kHalf;       // + buf * 128
+    const uint32_t tOx = tmem + lane_addr + 256 + x * 128;
     const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + h] : 0.f;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    const int tq_min = m0 + t * kBM + off, tq_max = tq_min + kBM - 1;
-    const int cnt = ghi_t[t] - glo_t[t];
+    const int tq_min = m0 + off, tq_max = tq_min + kBM - 1;
 
-    for (int c = 0; c < cnt && ok; ++c) {
-      const int g = glo_t[t] + c;
-      const int buf = c & 1;
-      const int k0 = g * kHalf;
+    for (int j = 0; j < nsteps && ok; ++j) {
+      const int buf = j & 1;
+      const int k0 = (n_lo + j) * kBN + x * kHalf;
       bool masked = (k0 + kHalf > si.k_len);
       if (cfg.causal) masked |= (k0 + kHalf - 1 > tq_min);
       if (cfg.wl >= 0) masked |= (k0 < tq_max - cfg.wl);
       if (cfg.wr >= 0) masked |= (k0 + kHalf - 1 > tq_min + cfg.wr);
 
-      ok = wait_bar(&sh->s_full[t][buf], (c >> 1) & 1, sh, 31 + t);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 0);
+      ok = wait_bar(&sh->s_full[buf], (j >> 1) & 1, sh, 31 + x);
       if (!ok) break;
       tc_fence_after();
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 1);
 
-      // ---- the 64 scores of this row into registers ---------------------------------------
+      // ---- the 64 scores of this row and stream into registers --------------------------
       uint32_t r[2][32];
-      tmem_ld32(tSb + buf * kHalf, r[0]);
-      tmem_ld32(tSb + buf * kHalf + 32, r[1]);
+      tmem_ld32(tSx + buf * kBN, r[0]);
+      tmem_ld32(tSx + buf * kBN + 32, r[1]);
       tmem_wait_ld();
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 2);
 
       const bool prescaled = kExtras || masked;
       if (prescaled) {
@@ -336,30 +326,29 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
 
-      // ---- row maximum: four independent chains ------------------------------------------
-      float mx4[4];
+      // ---- row maximum: balanced tree (depth 6) ------------------------------------------
+      float mt[32];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const int cc = q4 >> 1, base = (q4 & 1) * 16;
-        float a = fmaxf(__uint_as_float(r[cc][base]), __uint_as_float(r[cc][base + 1]));
+      for (int i = 0; i < 32; ++i) mt[i] = fmaxf(__uint_as_float(r[0][i]), __uint_as_float(r[1][i]));
 #pragma unroll
-        for (int i = 2; i < 16; i += 2)
-          a = fmaxf(a, fmaxf(__uint_as_float(r[cc][base + i]), __uint_as_float(r[cc][base + i + 1])));
-        mx4[q4] = a;
+      for (int w = 16; w >= 1; w >>= 1) {
+#pragma unroll
+        for (int i = 0; i < w; ++i) mt[i] = fmaxf(mt[i], mt[i + w]);
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = mt[0];
       if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
 
       // ---- lazy rescale ----------------------------------------------------------------
-      if (c == 0) {
+      if (j == 0) {
         m_used = mx;
       } else {
         const bool need = mx > m_used + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          // PV number c-1.  A parity wait cannot tell "k completions" from "k+2", and only
-          // PV c-3 is known to be complete here (QK c-1 was queued behind it), so PVs
-          // alternate between two barriers: on barrier (c-1)&1 at most one phase is open.
-          ok = wait_bar(&sh->o_ready[t][(c - 1) & 1], ((c - 1) >> 1) & 1, sh, 33 + t);
+          // PV number j-1 of this stream.  A parity wait cannot tell "k completions" from
+          // "k+2", and only PV j-3 is known to be complete here (QK j-1 was queued behind
+          // it), so PVs alternate between two barriers: on barrier (j-1)&1 at most one
+          // phase is open.
+          ok = wait_bar(&sh->o_ready[x][(j - 1) & 1], ((j - 1) >> 1) & 1, sh, 33 + x);
           if (!ok) break;
           tc_fence_after();
           const float alpha = need ? exp2f(m_used - mx) : 1.f;  // m_used = -inf -> 0
@@ -370,17 +359,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int cc = 0; cc < D / 32; ++cc) {
             uint32_t ro[32];
-            tmem_ld32(tOt + cc * 32, ro);
+            tmem_ld32(tOx + cc * 32, ro);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
-            tmem_st32(tOt + cc * 32, ro);
+            tmem_st32(tOx + cc * 32, ro);
           }
           tmem_wait_st();
         }
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       const float mul = prescaled ? 1.f : cfg.scale_log2;
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 3);
 
       // ---- P = exp2(s - m), row sum (four chains), P -> TMEM in place over S -------------
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
@@ -394,47 +384,67 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           ps[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = Elem<T>::pack(p0, p1);
         }
-        tmem_st16(tSb + buf * kHalf + cc * 16, pk);
+        tmem_st16(tSx + buf * kBN + cc * 16, pk);
       }
       l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 4);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->p_ready[t][buf]));
+      mbar_arrive(smem_u32(&sh->p_ready[x][buf]));
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 5);
     }
 
-    // ---- epilogue: O / l -> global, base-2 LSE ------------------------------------------
-    if (ok && cnt > 0) ok = wait_bar(&sh->o_ready[t][(cnt - 1) & 1], ((cnt - 1) >> 1) & 1, sh, 35 + t);
-    if (ok) {
-      tc_fence_after();
+    // ---- epilogue: merge the two streams, O / l -> global, base-2 LSE ---------------------
+    if (ok && nsteps > 0)
+      ok = wait_bar(&sh->o_ready[x][(nsteps - 1) & 1], ((nsteps - 1) >> 1) & 1, sh, 35 + x);
+    sh->ml[x][row_in_tile] = make_float2(m_used, l);
+    tc_fence_before();
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");  // the two softmax groups only
+    tc_fence_after();
+    if (ok && sh->abort_flag == 0) {
+      const float2 mine = make_float2(m_used, l), other = sh->ml[x ^ 1][row_in_tile];
+      const float mstar = fmaxf(mine.x, other.x);
+      const float w_me = (mstar == -INFINITY) ? 0.f : exp2f(mine.x - mstar);
+      const float w_ot = (mstar == -INFINITY) ? 0.f : exp2f(other.x - mstar);
+      const float lsum = mine.y * w_me + other.y * w_ot;
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      const float ca = (x == 0 ? w_me : w_ot) * inv, cb = (x == 0 ? w_ot : w_me) * inv;
       const bool row_ok = row < si.q_len;
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // this group writes head_dim columns [x*D/2, (x+1)*D/2) of the row
+      constexpr int DH = D / 2;
       T* og = reinterpret_cast<T*>(p.o) + si.q_boff * p.o_stride[0] +
-              (si.q_row0 + row) * p.o_stride[1] + (int64_t)h * p.o_stride[2];
+              (si.q_row0 + row) * p.o_stride[1] + (int64_t)h * p.o_stride[2] + x * DH;
+      const uint32_t tOa = tmem + lane_addr + 256 + x * DH, tOb = tOa + 128;
 #pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t ro[32];
-        if (cnt > 0) {
-          tmem_ld32(tOt + cc * 32, ro);
+      for (int cc = 0; cc < DH / 32; ++cc) {
+        uint32_t ra[32], rb[32];
+        if (nsteps > 0) {
+          tmem_ld32(tOa + cc * 32, ra);
+          tmem_ld32(tOb + cc * 32, rb);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ro[i] = 0u;
+          for (int i = 0; i < 32; ++i) ra[i] = rb[i] = 0u;
         }
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              f[e] = __uint_as_float(ra[i + e]) * ca + __uint_as_float(rb[i + e]) * cb;
             uint4 v;
-            v.x = Elem<T>::pack(__uint_as_float(ro[i]) * inv, __uint_as_float(ro[i + 1]) * inv);
-            v.y = Elem<T>::pack(__uint_as_float(ro[i + 2]) * inv, __uint_as_float(ro[i + 3]) * inv);
-            v.z = Elem<T>::pack(__uint_as_float(ro[i + 4]) * inv, __uint_as_float(ro[i + 5]) * inv);
-            v.w = Elem<T>::pack(__uint_as_float(ro[i + 6]) * inv, __uint_as_float(ro[i + 7]) * inv);
+            v.x = Elem<T>::pack(f[0], f[1]);
+            v.y = Elem<T>::pack(f[2], f[3]);
+            v.z = Elem<T>::pack(f[4], f[5]);
+            v.w = Elem<T>::pack(f[6], f[7]);
             *reinterpret_cast<uint4*>(og + cc * 32 + i) = v;
           }
         }
       }
-      if (row_ok && p.lse2 != nullptr)
+      if (x == 0 && row_ok && p.lse2 != nullptr)
         p.lse2[si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
-               (int64_t)h * p.lse_stride[2]] = l > 0.f ? m_used + log2f(l) : -INFINITY;
+               (int64_t)h * p.lse_stride[2]] = lsum > 0.f ? mstar + log2f(lsum) : -INFINITY;
     }
   }
 
@@ -483,7 +493,7 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
     set_error("fwd_sm100: cudaFuncSetAttribute(%d): %s", C::kSmemBytes, cudaGetErrorString(e));
     return FA_ERR_LAUNCH;
   }
-  dim3 grid((a.seqlen_q + 2 * kBM - 1) / (2 * kBM), a.heads_q, a.batch);
+  dim3 grid((a.seqlen_q + kBM - 1) / kBM, a.heads_q, a.batch);
   kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a, cfg);
   return check_launch("fwd_sm100");
 }
@@ -502,6 +512,12 @@ int fwd_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   return a.dtype == FA_BF16 ? launch<__nv_bfloat16, 64>(a, cfg, st, q_rows, k_rows)
                             : launch<__half, 64>(a, cfg, st, q_rows, k_rows);
 }
+
+#ifdef FA_TRACE
+extern "C" int fa_debug_fwd_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(long long) * 3 * 32 * 8);
+}
+#endif
 
 int fwd_sm100_status() {
   int v = 0;
