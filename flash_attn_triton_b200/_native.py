@@ -79,6 +79,8 @@ EXPORTS = {
     "fa_varlen_bwd_dkdv": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fa_decode_paged": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "fa_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
+    "fa_decode_paged_static": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "fa_decode_static_scratch_bytes": (C.c_size_t, []),
     "fa_quantize_k_int8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                      C.c_int32, C.c_void_p]),
     "fa_fwd_int8": (C.c_int, [C.POINTER(Int8Args), C.c_void_p]),

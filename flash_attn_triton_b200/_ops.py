@@ -323,3 +323,43 @@ def kvcache_decode(q, k_cache, v_cache, k_new, v_new, cos, sin, cache_seqlens, c
     with torch.cuda.device(q.device):
         N.check(L.fa_decode_paged(C.byref(a), N.stream_ptr(q.device)), "fa_decode_paged")
     return o
+
+
+def kvcache_decode_static(q, out, k_cache, v_cache, cache_seqlens, block_table=None, k_new=None,
+                          v_new=None, cos=None, sin=None, rotary_interleaved=True, scale=None,
+                          causal=False, num_splits=0):
+    """fa_decode_paged_static through ctypes: same decode, but the split-KV partials go to the
+    16 MiB array built into the library, so neither this function nor the C entry point
+    allocates anything -- `out` and every other tensor come from the caller.  For callers that
+    must not touch an allocator at call time (a frozen serving pool, a callback inside another
+    runtime).  q/out (B,Sq,Hq,D), caches (pages,page,Hkv,D), cache_seqlens int32 (B,),
+    block_table int32 (B,max_pages) or None, all already on the device and kernel-ready."""
+    B, Sq, Hq, D = q.shape
+    a = N.DecodeArgs()
+    a.dtype = N.dtype_code(q.dtype)
+    a.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    a.batch, a.seqlen_q, a.heads_q, a.heads_kv, a.head_dim = B, Sq, Hq, k_cache.shape[2], D
+    a.q, a.o = q.data_ptr(), out.data_ptr()
+    a.q_stride, a.o_stride = N.strides3(q, _BSHD), N.strides3(out, _BSHD)
+    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    a.kc_stride, a.vc_stride = N.strides3(k_cache, _BSHD), N.strides3(v_cache, _BSHD)
+    a.page_size, a.num_pages = k_cache.shape[1], k_cache.shape[0]
+    if block_table is not None:
+        a.block_table, a.block_table_stride = block_table.data_ptr(), block_table.stride(0)
+    a.cache_seqlens = cache_seqlens.data_ptr()
+    if k_new is not None:
+        a.k_new, a.v_new = k_new.data_ptr(), v_new.data_ptr()
+        a.kn_stride, a.vn_stride = N.strides3(k_new, _BSHD), N.strides3(v_new, _BSHD)
+        a.seqlen_new = k_new.shape[1]
+    if cos is not None:
+        a.rotary_cos, a.rotary_sin = cos.data_ptr(), sin.data_ptr()
+        a.rotary_dim, a.rotary_seqlen = cos.shape[-1] * 2, cos.shape[0]
+        a.rotary_interleaved = int(bool(rotary_interleaved))
+    a.softmax_scale = float(scale if scale is not None else D ** -0.5)
+    a.causal = int(bool(causal))
+    a.window_left = a.window_right = -1
+    a.num_splits = int(num_splits)
+    with torch.cuda.device(q.device):
+        N.check(N.lib().fa_decode_paged_static(C.byref(a), N.stream_ptr(q.device)),
+                "fa_decode_paged_static")
+    return out

@@ -49,6 +49,8 @@ int bwd_dq_sm100(const fa_attn_args&, const ScoreCfg&, cudaStream_t);
 int bwd_dkdv_sm100(const fa_attn_args&, const ScoreCfg&, cudaStream_t);
 int decode_paged(const fa_decode_args&, cudaStream_t);
 size_t decode_workspace_bytes(const fa_decode_args&);
+int decode_paged_static(const fa_decode_args&, cudaStream_t);
+size_t decode_static_scratch_bytes();
 int quantize_k(const void*, int8_t*, float*, int64_t, int, cudaStream_t);
 int fwd_int8_mma(const fa_int8_args&, cudaStream_t);
 bool fwd_int8_sm100_supported(const fa_int8_args&);
@@ -216,6 +218,14 @@ int fa_decode_paged(const fa_decode_args* a, void* stream) {
   if (int r = ensure_device(a->device)) return r;
   return decode_paged(*a, reinterpret_cast<cudaStream_t>(stream));
 }
+
+int fa_decode_paged_static(const fa_decode_args* a, void* stream) {
+  if (int r = validate_decode(a)) return r;
+  if (int r = ensure_device(a->device)) return r;
+  return decode_paged_static(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t fa_decode_static_scratch_bytes(void) { return decode_static_scratch_bytes(); }
 
 size_t fa_decode_workspace_bytes(const fa_decode_args* a) {
   if (a == nullptr || a->heads_kv <= 0 || a->heads_q <= 0 || a->page_size <= 0) return 0;

@@ -9,6 +9,8 @@
 //                      tiles of 64 keys arrive through a 3-stage cp.async ring of 16-byte
 //                      page-row gathers; 4 warps take 16 keys each and merge at the end.
 //   combine_kernel   : merges the per-split partial outputs with their base-2 LSEs.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fa {
@@ -468,6 +470,56 @@ int decode_paged(const fa_decode_args& a, cudaStream_t st) {
   ScoreCfg cfg = make_score_cfg(a.softmax_scale, 0.f, a.causal, a.window_left, a.window_right,
                                 a.alibi_slopes != nullptr);
   return a.dtype == FA_BF16 ? decode_t<__nv_bfloat16>(a, cfg, g, st) : decode_t<__half>(a, cfg, g, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation by anyone: the split-KV partials live in a fixed array
+// that is part of the library image.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle: the device address has to be asked for,
+// once per device, while that device is current.
+static void* static_scratch_ptr(int device) {
+  constexpr int kMaxDevices = 64;
+  static void* ptrs[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) {
+    set_error("device ordinal %d out of range for the static decode scratch", device);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[device] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("cudaGetSymbolAddress(static decode scratch) on device %d: %s", device,
+                cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[device] = p;
+  }
+  return ptrs[device];
+}
+
+size_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int decode_paged_static(const fa_decode_args& a, cudaStream_t st) {
+  if (a.batch == 0 || a.seqlen_q == 0 || a.heads_q == 0) return FA_OK;
+  const size_t need = decode_workspace_bytes(a);
+  if (need > kStaticScratchBytes) {
+    set_error("fa_decode_paged_static: this problem needs %zu bytes of split-KV scratch but the "
+              "built-in array holds %zu; pass a smaller num_splits or use fa_decode_paged with "
+              "your own workspace", need, kStaticScratchBytes);
+    return FA_ERR_WORKSPACE;
+  }
+  void* p = static_scratch_ptr(a.device);
+  if (p == nullptr) return FA_ERR_LAUNCH;
+  fa_decode_args b = a;
+  b.workspace = p;
+  b.workspace_bytes = kStaticScratchBytes;
+  return decode_paged(b, st);
 }
 
 }  // namespace fa

@@ -174,6 +174,31 @@ int fa_decode_paged(const fa_decode_args* args, void* stream);
 size_t fa_decode_workspace_bytes(const fa_decode_args* args);
 
 /*
+ * fa_decode_paged for callers that cannot allocate device memory and cannot get any from
+ * their host (no counterpart in the reference).  Think of a serving loop that has frozen
+ * its memory pool, a plugin running inside another runtime's callback where cudaMalloc is
+ * forbidden or would synchronise the device, or a process whose whole HBM budget is already
+ * spoken for by the KV cache.  The split-KV partial results go to a fixed 16 MiB array
+ * inside the library image (fa_decode_static_scratch_bytes() reports the size; every GPU
+ * that loads the library keeps those 16 MiB until the process exits).  args->workspace and
+ * args->workspace_bytes are ignored; q, o, the caches and every other buffer are still the
+ * caller's.  The call makes no cudaMalloc/cudaFree and calls no allocating library routine.
+ *
+ *  - A problem whose partials exceed the array (fa_decode_workspace_bytes(args) >
+ *    fa_decode_static_scratch_bytes()) is refused with FA_ERR_WORKSPACE and a message;
+ *    a smaller args->num_splits shrinks the need.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and keeps it; make that first call
+ *    outside any stream capture.
+ *  - All calls on one GPU share the array and it keeps whatever the last call left.  Nothing
+ *    in it has to start at zero (each call writes every partial it later reads), but two
+ *    calls that overlap on the GPU -- different streams, or different host threads --
+ *    overwrite each other's partials: serialise them.
+ */
+int fa_decode_paged_static(const fa_decode_args* args, void* stream);
+size_t fa_decode_static_scratch_bytes(void);
+
+/*
  * Per-key-token INT8 quantisation: k (rows, head_dim) fp16 contiguous ->
  * k8 (rows, head_dim) int8, s_k (rows) fp32, with
  *   s = max(absmax, 1)/127;  code = round_half_away(k * (1/s))  in IEEE fp32,
