@@ -56,6 +56,7 @@ int fwd_int8_mma(const fa_int8_args&, cudaStream_t);
 bool fwd_int8_sm100_supported(const fa_int8_args&);
 int fwd_int8_sm100(const fa_int8_args&, cudaStream_t);
 int fwd_sm100_status();
+int bwd_sm100_status();
 
 static bool mult8(const int64_t* s, int n) {
   for (int i = 0; i < n; ++i)
@@ -278,7 +279,8 @@ int fa_device_wait_status(int device) {
     set_error("cudaDeviceSynchronize: %s", cudaGetErrorString(e));
     return FA_ERR_LAUNCH;
   }
-  return fwd_sm100_status();
+  if (int s = fwd_sm100_status()) return s;
+  return bwd_sm100_status();
 }
 
 size_t fa_sizeof_args(int which) {

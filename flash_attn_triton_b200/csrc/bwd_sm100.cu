@@ -1,0 +1,677 @@
+// Backward attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), as two
+// kernels with one writer per output element (no atomics, deterministic):
+//
+//   bwd_dkdv_sm100_kernel  CTA = 128 keys of one (batch, kv head); loops over the query
+//                          tiles (and the query heads of the GQA group) that can see them.
+//                          Works on the TRANSPOSED tiles  S^T = K Q^T,  dP^T = V dO^T  so
+//                          that a TMEM lane is a key: P^T and dS^T are written back to TMEM
+//                          in place and feed  dV += P^T dO,  dK += dS^T Q  as the A operand.
+//   bwd_dq_sm100_kernel    CTA = 128 query rows of one (batch, head); loops over key tiles:
+//                          S = Q K^T, dP = dO V^T, dS in place over dP, dQ += dS K.
+//
+// Roles in both kernels (384 threads):
+//   warps 0-3 / 4-7  element-wise groups A / B: columns 0..63 / 64..127 of the 128 x 128
+//                    score tiles, one TMEM lane (row) per thread
+//   warp 8           TMA producer (resident tiles once, then a ring of streamed tile pairs)
+//   warp 9           MMA issuer (whole warp runs the control flow, one elected lane issues)
+//   warp 10          loads the per-row statistics (base-2 LSE, delta) of the streamed query
+//                    tile into shared memory (dK/dV kernel only)
+//   warp 11          idle (completes the warpgroup for setmaxnreg)
+//
+// TMEM, dK/dV kernel: S^T | dP^T | dV | dK  (4 x 128 columns).
+// TMEM, dQ kernel:    S   | dP   | dQ       (3 x 128 columns).
+// All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
+// K-major (contraction over head_dim) or MN-major (contraction over its rows) through
+// different descriptors.  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace fa {
+
+using namespace sm100;
+
+__device__ int g_bwd_sm100_status = 0;
+
+namespace {
+
+constexpr int kT = 128;        // tile edge: rows of Q / keys of K,V per tile
+constexpr int kHalfT = 64;
+constexpr int kBwdThreads = 384;
+
+template <int D> struct BCfg {
+  static constexpr int kTileBytes = kT * D * 2;
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kStages = (D == 128) ? 2 : 4;  // ring of streamed tile PAIRS
+  static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
+  static constexpr int kSmemBytes = kSmemTiles + 1024 + 8192;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+struct BShared {
+  uint64_t res_full;      // resident tiles (K,V or Q,dO) landed
+  uint64_t full[4];       // streamed pair landed
+  uint64_t empty[4];      // streamed pair (and its statistics) consumed
+  uint64_t stat_full[4];  // statistics of the streamed query tile written (dK/dV kernel)
+  uint64_t s_full;        // S and dP computed
+  uint64_t pds_ready;     // P and dS written back (256 arrivals)
+  uint64_t acc_done;      // every accumulation MMA finished
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  alignas(16) float lse[4][kT];  // [stage][row of the streamed query tile]; read as float4
+  alignas(16) float delta[4][kT];
+};
+static_assert(sizeof(BShared) <= 8192, "BShared must fit its reserve");
+
+template <typename T> struct BFmt;
+template <> struct BFmt<__half> { static constexpr int code = 0; };
+template <> struct BFmt<__nv_bfloat16> { static constexpr int code = 1; };
+
+__device__ __forceinline__ bool bwait(uint64_t* bar, uint32_t parity, BShared* sh, int code) {
+  return bounded_wait(bar, parity, &sh->abort_flag, &g_bwd_sm100_status, code);
+}
+
+// TMA loads of one 128 x D tile (D/64 boxes) at (row, head, batch)
+template <int D>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int row,
+                                          int head, int batch) {
+#pragma unroll
+  for (int x = 0; x < D / 64; ++x) tma_load_4d(dst + x * (kT * 128), tm, bar, x * 64, head, row, batch);
+}
+
+// 128 x 128 x D product of two K-major tiles (contraction over head_dim): D/16 MMAs
+template <int D>
+__device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                           uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t o = (kk / 4) * (kT * 128) + (kk % 4) * 32;
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + o, 16, 1024), make_smem_desc(b_smem + o, 16, 1024), idesc,
+               kk > 0);
+  }
+}
+
+// acc(128 x D) += A(128 x 128, fp16 pairs in TMEM) * B(128 rows x D, MN-major smem tile).
+// A is stored as two 32-column blocks (written by the two element-wise groups) at
+// a_tmem and a_tmem + 64.
+template <int D>
+__device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
+                                              uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < kT / 16; ++kk) {
+    const uint32_t a = a_tmem + (kk / 4) * 64 + (kk % 4) * 8;
+    mma_f16_ts(d_tmem, a, make_smem_desc(b_smem + kk * 2048, kT * 128, 1024), idesc,
+               (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+}  // namespace
+
+// =======================================================================================
+// dK, dV
+// =======================================================================================
+template <typename T, int D, bool kExtras>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      const fa_attn_args p, const ScoreCfg cfg) {
+  using C = BCfg<D>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
+  const uint32_t sK = smem_u32(tiles), sV = sK + C::kTileBytes, sRing = sV + C::kTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const SeqInfo si = seq_info(p, b);
+  const int n0 = nblk * kT;
+  if (n0 >= si.k_len) return;
+  const int G = p.heads_q / p.heads_kv;
+  const int off = p.q_pos_offset;
+
+  int qlo, qhi;
+  visible_query_range(cfg, n0, min(n0 + kT, si.k_len) - 1, off, si.q_len + off, qlo, qhi);
+  const int m_lo = max(qlo - off, 0) / kT;
+  const int m_hi = (max(qhi - off, 0) + kT - 1) / kT;
+  const int ntiles = max(m_hi - m_lo, 0);
+  const int total = ntiles * G;
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sh->res_full), 1);
+    mbar_init(smem_u32(&sh->s_full), 1);
+    mbar_init(smem_u32(&sh->pds_ready), 256);
+    mbar_init(smem_u32(&sh->acc_done), 1);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(smem_u32(&sh->full[i]), 1);
+      mbar_init(smem_u32(&sh->empty[i]), 1);
+      mbar_init(smem_u32(&sh->stat_full[i]), 1);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
+
+  if (warp == 11) {
+    reg_dealloc<56>();
+  } else if (warp == 8) {
+    // ------------------------------- TMA producer ---------------------------------------
+    reg_dealloc<56>();
+    if (lane == 0 && total > 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      prefetch_tmap(&tmdO);
+      {
+        const uint32_t bar = smem_u32(&sh->res_full);
+        mbar_expect_tx(bar, 2 * C::kTileBytes);
+        load_tile<D>(sK, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
+        load_tile<D>(sV, &tmV, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int it = 0; it < total; ++it) {
+        const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
+        if (!bwait(&sh->empty[stage], phase ^ 1, sh, 41)) break;
+        const uint32_t bar = smem_u32(&sh->full[stage]);
+        mbar_expect_tx(bar, 2 * C::kTileBytes);
+        const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
+        load_tile<D>(dst, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        load_tile<D>(dst + C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------- statistics loader ----------------------------------
+    reg_dealloc<56>();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int it = 0; it < total; ++it) {
+      const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
+      bool w = true;
+      if (lane == 0) w = bwait(&sh->empty[stage], phase ^ 1, sh, 42);
+      if (!__all_sync(0xffffffffu, w)) break;
+      for (int i = lane; i < kT; i += 32) {
+        const int row = m * kT + i;
+        float l2 = INFINITY, dl = 0.f;
+        if (row < si.q_len) {
+          const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
+                              (int64_t)hq * p.lse_stride[2];
+          l2 = p.lse2[idx];
+          dl = p.delta[idx];
+          if (l2 == -INFINITY) l2 = INFINITY;  // row without visible keys: P = 0
+        }
+        sh->lse[stage][i] = l2;
+        sh->delta[stage][i] = dl;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->stat_full[stage]));
+      if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer -----------------------------------------
+    reg_dealloc<56>();
+    if (total > 0) {
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+      bool ok = true;
+      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
+        bool w = true;
+        if (lane == 0) w = bwait(bar, parity, sh, code);
+        ok = __all_sync(0xffffffffu, w) && ok;
+        tc_fence_after();
+      };
+      wwait(&sh->res_full, 0, 43);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int it = 0; it < total && ok; ++it) {
+        wwait(&sh->full[stage], phase, 44);
+        if (!ok) break;
+        const uint32_t sQ = sRing + stage * 2 * C::kTileBytes, sdO = sQ + C::kTileBytes;
+        if (elect_one()) {
+          mma_kmajor<D>(tS, sK, sQ, idesc_s);     // S^T  = K Q^T
+          mma_kmajor<D>(tdP, sV, sdO, idesc_s);   // dP^T = V dO^T
+          mma_commit(smem_u32(&sh->s_full));
+        }
+        __syncwarp();
+        wwait(&sh->pds_ready, it & 1, 45);
+        if (!ok) break;
+        if (elect_one()) {
+          mma_from_tmem<D>(tdV, tS, sdO, idesc_acc, it > 0);   // dV += P^T dO
+          mma_from_tmem<D>(tdK, tdP, sQ, idesc_acc, it > 0);   // dK += dS^T Q
+          mma_commit(smem_u32(&sh->empty[stage]));
+        }
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+      if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------- element-wise groups --------------------------------
+    reg_alloc<224>();
+    const int x = warp >> 2;                         // column half
+    const int lrow = (warp & 3) * 32 + lane;         // TMEM lane = key inside the tile
+    const int key = n0 + lrow;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int it = 0; it < total && ok; ++it) {
+      const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
+      const int q0 = m * kT + x * kHalfT;            // first query row of this group's columns
+      const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + hq] : 0.f;
+      bool masked = false;
+      if (cfg.causal) masked |= (n0 + kT - 1 > q0 + off);
+      if (cfg.wl >= 0) masked |= (n0 < q0 + kHalfT - 1 + off - cfg.wl);
+      if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
+
+      ok = bwait(&sh->s_full, it & 1, sh, 46) && bwait(&sh->stat_full[stage], phase, sh, 47);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t rs[2][32], rp[2][32];
+      tmem_ld32(tS + lane_addr + x * kHalfT, rs[0]);
+      tmem_ld32(tS + lane_addr + x * kHalfT + 32, rs[1]);
+      tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
+      tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
+      tmem_wait_ld();
+      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
+      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = L4[cc * 8 + i4], d4 = D4[cc * 8 + i4];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], ds[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = i4 * 4 + e;
+            const float s = __uint_as_float(rs[cc][i]);
+            const float dp = __uint_as_float(rp[cc][i]);
+            float th = 0.f;
+            float sc;
+            if (kExtras) sc = score_log2(cfg, slope, s, q0 + cc * 32 + i + off, key, th) - lv[e];
+            else sc = fmaf(s, cfg.scale_log2, -lv[e]);
+            float pe = ex2(sc);
+            if (masked && !visible(cfg, q0 + cc * 32 + i + off, key, 0x7fffffff)) pe = 0.f;
+            float de = pe * (dp - dv[e]);
+            if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+            pv[e] = pe;
+            ds[e] = de;
+          }
+          pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
+          pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
+          dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
+          dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
+        }
+        tmem_st16(tS + lane_addr + x * kHalfT + cc * 16, pk);
+        tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->pds_ready));
+      if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+    }
+
+    // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
+    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 48);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t tsrc = (x == 0 ? tdV : tdK) + lane_addr;
+      const float mul = (x == 0) ? 1.f : cfg.scale;
+      T* base = (x == 0) ? reinterpret_cast<T*>(p.dv) + si.k_boff * p.dv_stride[0] +
+                               (si.k_row0 + key) * p.dv_stride[1] + (int64_t)hk * p.dv_stride[2]
+                         : reinterpret_cast<T*>(p.dk) + si.k_boff * p.dk_stride[0] +
+                               (si.k_row0 + key) * p.dk_stride[1] + (int64_t)hk * p.dk_stride[2];
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t r[32];
+        if (total > 0) {
+          tmem_ld32(tsrc + cc * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (key < si.k_len) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = Elem<T>::pack(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+            v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+            v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+            v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+            *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, 512);
+}
+
+// =======================================================================================
+// dQ
+// =======================================================================================
+template <typename T, int D, bool kExtras>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const fa_attn_args p, const ScoreCfg cfg) {
+  using C = BCfg<D>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
+  const uint32_t sQ = smem_u32(tiles), sdO = sQ + C::kTileBytes, sRing = sdO + C::kTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int mblk = cfg.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy blocks first
+  const SeqInfo si = seq_info(p, b);
+  const int m0 = mblk * kT;
+  if (m0 >= si.q_len) return;
+  const int hk = h / (p.heads_q / p.heads_kv);
+  const int off = p.q_pos_offset;
+
+  int klo, khi;
+  visible_key_range(cfg, m0 + off, min(m0 + kT, si.q_len) - 1 + off, si.k_len, klo, khi);
+  const int n_lo = klo / kT;
+  const int n_hi = (khi + kT - 1) / kT;
+  const int total = max(n_hi - n_lo, 0);
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sh->res_full), 1);
+    mbar_init(smem_u32(&sh->s_full), 1);
+    mbar_init(smem_u32(&sh->pds_ready), 256);
+    mbar_init(smem_u32(&sh->acc_done), 1);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(smem_u32(&sh->full[i]), 1);
+      mbar_init(smem_u32(&sh->empty[i]), 1);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(&sh->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+
+  if (warp >= 10) {
+    reg_dealloc<56>();
+  } else if (warp == 8) {
+    // ------------------------------- TMA producer ---------------------------------------
+    reg_dealloc<56>();
+    if (lane == 0 && total > 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      prefetch_tmap(&tmdO);
+      {
+        const uint32_t bar = smem_u32(&sh->res_full);
+        mbar_expect_tx(bar, 2 * C::kTileBytes);
+        load_tile<D>(sQ, &tmQ, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
+        load_tile<D>(sdO, &tmdO, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < total; ++j) {
+        if (!bwait(&sh->empty[stage], phase ^ 1, sh, 51)) break;
+        const uint32_t bar = smem_u32(&sh->full[stage]);
+        mbar_expect_tx(bar, 2 * C::kTileBytes);
+        const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
+        load_tile<D>(dst, &tmK, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+        load_tile<D>(dst + C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------- MMA issuer -----------------------------------------
+    reg_dealloc<56>();
+    if (total > 0) {
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+      bool ok = true;
+      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
+        bool w = true;
+        if (lane == 0) w = bwait(bar, parity, sh, code);
+        ok = __all_sync(0xffffffffu, w) && ok;
+        tc_fence_after();
+      };
+      wwait(&sh->res_full, 0, 53);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int j = 0; j < total && ok; ++j) {
+        wwait(&sh->full[stage], phase, 54);
+        if (!ok) break;
+        const uint32_t sKj = sRing + stage * 2 * C::kTileBytes, sVj = sKj + C::kTileBytes;
+        if (elect_one()) {
+          mma_kmajor<D>(tS, sQ, sKj, idesc_s);     // S  = Q K^T
+          mma_kmajor<D>(tdP, sdO, sVj, idesc_s);   // dP = dO V^T
+          mma_commit(smem_u32(&sh->s_full));
+        }
+        __syncwarp();
+        wwait(&sh->pds_ready, j & 1, 55);
+        if (!ok) break;
+        if (elect_one()) {
+          mma_from_tmem<D>(tdQ, tdP, sKj, idesc_acc, j > 0);   // dQ += dS K
+          mma_commit(smem_u32(&sh->empty[stage]));
+        }
+        __syncwarp();
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+      if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------- element-wise groups --------------------------------
+    reg_alloc<224>();
+    const int x = warp >> 2;
+    const int lrow = (warp & 3) * 32 + lane;  // TMEM lane = query row inside the tile
+    const int row = m0 + lrow;
+    const int qpos = row + off;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + h] : 0.f;
+    float l2 = INFINITY, dl = 0.f;
+    if (row < si.q_len) {
+      const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
+                          (int64_t)h * p.lse_stride[2];
+      l2 = p.lse2[idx];
+      dl = p.delta[idx];
+      if (l2 == -INFINITY) l2 = INFINITY;
+    }
+    bool ok = true;
+    for (int j = 0; j < total && ok; ++j) {
+      const int k0 = (n_lo + j) * kT + x * kHalfT;
+      bool masked = (k0 + kHalfT > si.k_len);
+      if (cfg.causal) masked |= (k0 + kHalfT - 1 > m0 + off);
+      if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);
+      if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > m0 + off + cfg.wr);
+
+      ok = bwait(&sh->s_full, j & 1, sh, 56);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t rs[2][32], rp[2][32];
+      tmem_ld32(tS + lane_addr + x * kHalfT, rs[0]);
+      tmem_ld32(tS + lane_addr + x * kHalfT + 32, rs[1]);
+      tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
+      tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t dk_[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float ds2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = k0 + cc * 32 + i + e;
+            const float s = __uint_as_float(rs[cc][i + e]);
+            const float dp = __uint_as_float(rp[cc][i + e]);
+            float th = 0.f;
+            float sc;
+            if (kExtras) sc = score_log2(cfg, slope, s, qpos, col, th) - l2;
+            else sc = fmaf(s, cfg.scale_log2, -l2);
+            float pe = ex2(sc);
+            if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
+            float de = pe * (dp - dl);
+            if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+            ds2[e] = de;
+          }
+          dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
+        }
+        tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->pds_ready));
+    }
+
+    // ---- epilogue: dQ * softmax_scale; each group stores half of the head_dim columns -----
+    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 58);
+    if (ok) {
+      tc_fence_after();
+      constexpr int DH = D / 2;
+      T* base = reinterpret_cast<T*>(p.dq) + si.q_boff * p.dq_stride[0] +
+                (si.q_row0 + row) * p.dq_stride[1] + (int64_t)h * p.dq_stride[2] + x * DH;
+#pragma unroll
+      for (int cc = 0; cc < DH / 32; ++cc) {
+        uint32_t r[32];
+        if (total > 0) {
+          tmem_ld32(tdQ + lane_addr + x * DH + cc * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row < si.q_len) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = Elem<T>::pack(__uint_as_float(r[i]) * cfg.scale, __uint_as_float(r[i + 1]) * cfg.scale);
+            v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * cfg.scale, __uint_as_float(r[i + 3]) * cfg.scale);
+            v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * cfg.scale, __uint_as_float(r[i + 5]) * cfg.scale);
+            v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * cfg.scale, __uint_as_float(r[i + 7]) * cfg.scale);
+            *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem, 512);
+}
+
+// =======================================================================================
+// host side
+// =======================================================================================
+bool bwd_sm100_supported(const fa_attn_args& a) {
+  if (a.head_dim != 128 && a.head_dim != 64) return false;
+  if (a.softmax_scale < 0.f) return false;
+  if (a.batch == 0 || a.seqlen_q == 0 || a.seqlen_k == 0) return false;
+  if (a.impl == FA_IMPL_AUTO && (a.seqlen_k < 256 || a.seqlen_q < 128)) return false;
+  return true;
+}
+
+namespace {
+
+bool make_map4(CUtensorMap* m, const void* base, const int64_t* stride, int rows, int heads, int batch,
+               int D, bool packed) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)rows, (uint64_t)(packed ? 1 : batch)};
+  const uint64_t strides[3] = {(uint64_t)stride[2] * 2, (uint64_t)stride[1] * 2,
+                               (uint64_t)(packed ? (int64_t)rows * stride[1] : stride[0]) * 2};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  return encode_tmap(m, base, 2, 4, dims, strides, box);
+}
+
+struct Maps { CUtensorMap q, k, v, dout; };
+
+bool make_maps(Maps& m, const fa_attn_args& a) {
+  const bool packed = a.cu_seqlens_q != nullptr;
+  const int qr = packed ? a.total_q : a.seqlen_q, kr = packed ? a.total_k : a.seqlen_k;
+  const int D = a.head_dim;
+  return make_map4(&m.q, a.q, a.q_stride, qr, a.heads_q, a.batch, D, packed) &&
+         make_map4(&m.k, a.k, a.k_stride, kr, a.heads_kv, a.batch, D, packed) &&
+         make_map4(&m.v, a.v, a.v_stride, kr, a.heads_kv, a.batch, D, packed) &&
+         make_map4(&m.dout, a.dout, a.do_stride, qr, a.heads_q, a.batch, D, packed);
+}
+
+template <typename K> int set_smem_attr(K kern, int bytes, const char* what) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_error("%s: cudaFuncSetAttribute(%d): %s", what, bytes, cudaGetErrorString(e));
+    return FA_ERR_LAUNCH;
+  }
+  return FA_OK;
+}
+
+template <typename T, int D>
+int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  Maps m;
+  if (!make_maps(m, a)) {
+    set_error("bwd_dkdv_sm100: cuTensorMapEncodeTiled failed");
+    return FA_ERR_LAUNCH;
+  }
+  const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
+  auto kern = extras ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
+  if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dkdv_sm100")) return r;
+  dim3 grid((a.seqlen_k + kT - 1) / kT, a.heads_kv, a.batch);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, a, cfg);
+  return check_launch("bwd_dkdv_sm100");
+}
+
+template <typename T, int D>
+int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  Maps m;
+  if (!make_maps(m, a)) {
+    set_error("bwd_dq_sm100: cuTensorMapEncodeTiled failed");
+    return FA_ERR_LAUNCH;
+  }
+  const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
+  auto kern = extras ? bwd_dq_sm100_kernel<T, D, true> : bwd_dq_sm100_kernel<T, D, false>;
+  if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dq_sm100")) return r;
+  dim3 grid((a.seqlen_q + kT - 1) / kT, a.heads_q, a.batch);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, a, cfg);
+  return check_launch("bwd_dq_sm100");
+}
+
+}  // namespace
+
+int bwd_dkdv_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  if (a.head_dim == 128)
+    return a.dtype == FA_BF16 ? launch_dkdv<__nv_bfloat16, 128>(a, cfg, st) : launch_dkdv<__half, 128>(a, cfg, st);
+  return a.dtype == FA_BF16 ? launch_dkdv<__nv_bfloat16, 64>(a, cfg, st) : launch_dkdv<__half, 64>(a, cfg, st);
+}
+
+int bwd_dq_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  if (a.head_dim == 128)
+    return a.dtype == FA_BF16 ? launch_dq<__nv_bfloat16, 128>(a, cfg, st) : launch_dq<__half, 128>(a, cfg, st);
+  return a.dtype == FA_BF16 ? launch_dq<__nv_bfloat16, 64>(a, cfg, st) : launch_dq<__half, 64>(a, cfg, st);
+}
+
+int bwd_sm100_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_bwd_sm100_status, sizeof(int));
+  return v;
+}
+
+}  // namespace fa

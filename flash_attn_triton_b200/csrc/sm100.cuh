@@ -57,6 +57,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
   return false;
 }
 
+// Bounded wait used by the warp-specialised kernels: the already-complete case costs one
+// try_wait; otherwise spin, and every 256 polls look at the CTA's abort flag and at the clock.
+// After ~2 s the waiter raises the CTA's abort flag (so every other role of the CTA unwinds
+// at its next poll) and the device-wide status word, and returns false.
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                             int* status, int code) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
+  if (mbar_try_wait(a, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(a, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*cta_abort) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *cta_abort = code;
+        atomicExch(status, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA (tiled tensor maps, no multicast)
 // ---------------------------------------------------------------------------------------

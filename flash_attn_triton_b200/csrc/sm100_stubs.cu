@@ -11,6 +11,7 @@ int fwd_sm100_status() { return 0; }
 bool bwd_sm100_supported(const fa_attn_args&) { return false; }
 int bwd_dq_sm100(const fa_attn_args&, const ScoreCfg&, cudaStream_t) { set_error("not built"); return FA_ERR_UNSUPPORTED; }
 int bwd_dkdv_sm100(const fa_attn_args&, const ScoreCfg&, cudaStream_t) { set_error("not built"); return FA_ERR_UNSUPPORTED; }
+int bwd_sm100_status() { return 0; }
 #endif
 #ifndef FA_HAVE_INT8_SM100
 bool fwd_int8_sm100_supported(const fa_int8_args&) { return false; }

@@ -1,0 +1,94 @@
+"""The tcgen05/TMEM/TMA kernels, forced on (FA_IMPL_TCGEN05) at sizes below the automatic
+switch-over too, against the fp32 oracle and against the independent mma.sync kernels."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import util
+from oracle import attention_oracle as orc
+from util import DEV, LN2, maxdiff
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # B, Sq, Sk, Hq, Hkv, D
+    (1, 128, 128, 1, 1, 128),
+    (2, 512, 512, 2, 1, 128),
+    (1, 300, 300, 2, 2, 128),
+    (2, 1000, 777, 4, 2, 128),
+    (1, 384, 384, 2, 2, 64),
+    (2, 100, 900, 2, 1, 64),
+    (1, 640, 640, 8, 2, 128),
+]
+FEATS = [
+    dict(causal=False), dict(causal=True), dict(causal=True, wl=100, wr=0), dict(causal=False, wl=50, wr=70),
+    dict(causal=True, softcap=10.0), dict(causal=True, alibi=True),
+    dict(causal=True, wl=200, wr=0, softcap=30.0, alibi=True),
+]
+
+
+def _run(impl, q, k, v, do, scale, kw, alibi):
+    from flash_attn_triton_b200 import _ops
+    args = (scale, kw.get("causal", False), kw.get("wl", -1), kw.get("wr", -1), kw.get("softcap", 0.0), alibi, 0)
+    o, lse, _ = _ops.dense_forward(q, k, v, *args, impl, "bshd", True)
+    dq, dk, dv = _ops.dense_backward(q, k, v, o, lse, do, *args, impl, "bshd")
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("feat", range(len(FEATS)))
+def test_tcgen05_forward_backward(shape, feat):
+    from flash_attn_triton_b200 import _native as N
+    B, Sq, Sk, Hq, Hkv, D = shape
+    kw = FEATS[feat]
+    q, k, v, do = cases.dense_case(2000 + feat, B, Sq, Sk, Hq, Hkv, D)
+    sl = torch.tensor([[2.0 ** (-(i + 1)) for i in range(Hq)]] * B) if kw.get("alibi") else None
+    scale = 0.1 if feat >= 2 else 1.0 / np.sqrt(D)
+    out = _run(N.IMPL_TCGEN05, *(t.to(DEV) for t in (q, k, v, do)), scale, kw, None if sl is None else sl.to(DEV))
+    assert N.lib().fa_device_wait_status(0) == 0
+    ro, rl, rdq, rdk, rdv = orc.attention_grads_ref(
+        q, k, v, do, softmax_scale=scale, causal=kw.get("causal", False),
+        window=(kw.get("wl", -1), kw.get("wr", -1)), softcap=kw.get("softcap", 0.0), alibi_slopes=sl)
+    assert maxdiff(out[0], ro) <= util.FWD_TOL
+    assert maxdiff(out[1] * LN2, rl) <= util.FWD_TOL
+    for t, r in zip(out[2:], (rdq, rdk, rdv)):
+        assert maxdiff(t, r) <= util.GRAD_TOL
+
+
+def test_tcgen05_varlen_and_bf16():
+    from flash_attn_triton_b200 import _native as N, _ops
+    ql = [200, 129, 640, 64]
+    q, k, v, do, cu, _ = cases.varlen_case(77, ql, ql, 8, 2, 128)
+    sl = torch.tensor([[2.0 ** (-8 * (i + 1) / 8) for i in range(8)]] * 4)
+    args = (max(ql), max(ql), 0.09, True, 150, 0, 30.0, sl.to(DEV))
+    qd, kd, vd, dod, cud = (t.to(DEV) for t in (q, k, v, do, cu))
+    o, lse, _ = _ops.varlen_forward(qd, kd, vd, cud, cud, *args, N.IMPL_TCGEN05, True)
+    dq, dk, dv = _ops.varlen_backward(qd, kd, vd, o, lse, dod, cud, cud, *args, N.IMPL_TCGEN05)
+    assert N.lib().fa_device_wait_status(0) == 0
+    ro, _, rdq, rdk, rdv = orc.varlen_attention_grads_ref(q, k, v, do, cu, cu, softmax_scale=0.09, causal=True,
+                                                          window=(150, 0), softcap=30.0, alibi_slopes=sl[0])
+    assert maxdiff(o, ro) <= util.FWD_TOL
+    for t, r in zip((dq, dk, dv), (rdq, rdk, rdv)):
+        assert maxdiff(t, r) <= util.GRAD_TOL
+    # bf16
+    q, k, v, do = (t.bfloat16() for t in cases.dense_case(78, 2, 400, 400, 4, 2, 128))
+    out = _run(N.IMPL_TCGEN05, *(t.to(DEV) for t in (q, k, v, do)), 0.088, dict(causal=True), None)
+    ro, _, rdq, rdk, rdv = orc.attention_grads_ref(q, k, v, do, softmax_scale=0.088, causal=True)
+    assert maxdiff(out[0], ro) <= util.BF16_FWD_TOL
+    for t, r in zip(out[2:], (rdq, rdk, rdv)):
+        assert maxdiff(t, r) <= util.BF16_GRAD_TOL
+
+
+def test_tcgen05_agrees_with_mma_at_full_size():
+    """B16 H16 S4096 D128 causal: two independent implementations of every kernel."""
+    from flash_attn_triton_b200 import _native as N
+    torch.manual_seed(1)
+    q, k, v, do = (torch.randn(16, 4096, 16, 128, device=DEV, dtype=torch.float16) for _ in range(4))
+    a = _run(N.IMPL_TCGEN05, q, k, v, do, 128 ** -0.5, dict(causal=True), None)
+    assert N.lib().fa_device_wait_status(0) == 0
+    b = _run(N.IMPL_MMA, q, k, v, do, 128 ** -0.5, dict(causal=True), None)
+    assert (a[0].float() - b[0].float()).abs().max().item() <= util.FWD_TOL
+    assert maxdiff(a[1], b[1]) <= util.FWD_TOL
+    for x, y in zip(a[2:], b[2:]):
+        assert (x.float() - y.float()).abs().max().item() <= util.GRAD_TOL
