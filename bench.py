@@ -58,6 +58,58 @@ def measured_peaks():
     return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
 
 
+class NvmlSampler:
+    """SM clock and throttle reasons read through NVML every few ms while the timed region
+    runs (read-only queries)."""
+
+    def __init__(self, gpu_index):
+        import pynvml
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        self.sm, self.reasons, self.stop_flag = [], 0, False
+
+    def start(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.sm.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.reasons |= nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            except Exception:
+                break
+            time.sleep(0.005)
+
+    def stop(self):
+        nv = self.nv
+        self.stop_flag = True
+        self.thread.join(timeout=1)
+        names = []
+        for bit, name in ((getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8), "hw_slowdown"),
+                          (getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40), "hw_thermal_slowdown"),
+                          (getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20), "sw_thermal_slowdown"),
+                          (getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4), "sw_power_cap")):
+            if self.reasons & bit:
+                names.append(name)
+        sm = sorted(self.sm)
+        try:
+            mx = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": names,
+                "samples": len(sm), "source": "nvml"}
+
+
+def make_sampler(gpu_index):
+    try:
+        return NvmlSampler(gpu_index)
+    except Exception:
+        return ClockSampler(gpu_index)
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
 
@@ -221,6 +273,22 @@ def decode_bench(dev, peaks, iters=20):
             "config": "batch 64, Hq32/Hkv8, D128, page 256, pool 4096, lens U[1024,32768], append+rotary"}
 
 
+def profile_case(args):
+    """Forward + backward on B=2 H=16 S=4096 D=128 causal (inputs 128 MiB > L2), W+K steps."""
+    from flash_attn_triton_b200 import _native as N
+    from flash_attn_triton_b200 import _ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v, do = (torch.randn(2, S, H, D, device=dev, dtype=torch.float16, generator=g) for _ in range(4))
+    scale = 1.0 / math.sqrt(D)
+    for _ in range(args.warmup + args.steps):
+        o, lse, _ = _ops.dense_forward(q, k, v, scale, True, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd", True)
+        _ops.dense_backward(q, k, v, o, lse, do, scale, True, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd")
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": "B2 H16 S4096 D128 causal fwd+bwd", "steps": args.warmup + args.steps,
+                      "device_wait_status": N.lib().fa_device_wait_status(0)}))
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -254,7 +322,7 @@ def run_ours(args, rank, world, local_rank):
         step()
     torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
+    sampler = make_sampler(local_rank)
     if world > 1:
         dist.barrier()
     sampler.start()
@@ -294,7 +362,8 @@ def run_ours(args, rank, world, local_rank):
     executed = {"fwd": FWD_FLOPS, "bwd_dq": FWD_FLOPS * 1.5, "bwd_dkdv": FWD_FLOPS * 2.0, "bwd_preprocess": 0.0}
     top = max(("fwd", "bwd_dq", "bwd_dkdv"), key=lambda n: kernels[n])
     # DRAM traffic per launch of each kernel from the ncu captures summarised in profiles/
-    traffic = {"fwd": None, "bwd_dq": None, "bwd_dkdv": None}
+    # (B=2 capture scaled x8 by batch, profiles/fwd_bwd_sm100_B2_H16_S4096_D128_causal.md)
+    traffic = {"fwd": 0.94e9, "bwd_dq": 1.24e9, "bwd_dkdv": 1.40e9}
     roofline = {"kernel": top, "bound": "tensor", "achieved": algo[top] / kernels[top] / 1e9,
                 "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": algo[top] / kernels[top] / 1e9 / peaks["bf16"],
                 "peak_source": peaks["source"] + " cuBLAS bf16 burst", "traffic": traffic[top],
@@ -371,15 +440,21 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run only forward+backward steps on a reduced batch (B=2) and exit: the small "
+                         "case used for ncu captures")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.profile_case:
+        profile_case(args)
         return
     if world > 1:
         import torch.distributed as dist
