@@ -23,6 +23,8 @@
 // All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
 // K-major (contraction over head_dim) or MN-major (contraction over its rows) through
 // different descriptors.  Every mbarrier wait is bounded.
+#include <type_traits>
+
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -31,6 +33,22 @@ namespace fa {
 using namespace sm100;
 
 __device__ int g_bwd_sm100_status = 0;
+
+#ifdef FA_TRACE
+// Timeline of one CTA of the dK/dV kernel (blockIdx 0,0,0) for tuning: clock64 per role/step.
+__device__ long long g_bwd_trace[3][32][8];
+#define FA_BTRACE(role, step, ev)                                                            \
+  do {                                                                                       \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (step) < 32 &&              \
+        (threadIdx.x & 31) == 0)                                                             \
+      g_bwd_trace[role][step][ev] = clock64();                                               \
+  } while (0)
+extern "C" int fa_debug_bwd_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * 3 * 32 * 8);
+}
+#else
+#define FA_BTRACE(role, step, ev) do {} while (0)
+#endif
 
 namespace {
 
@@ -68,6 +86,17 @@ template <> struct BFmt<__nv_bfloat16> { static constexpr int code = 1; };
 
 __device__ __forceinline__ bool bwait(uint64_t* bar, uint32_t parity, BShared* sh, int code) {
   return bounded_wait(bar, parity, &sh->abort_flag, &g_bwd_sm100_status, code);
+}
+
+// For roles that are far ahead of the critical path (producer, statistics loader): back off
+// between polls so the spin does not take issue slots from the element-wise warps.
+__device__ __forceinline__ bool bwait_relaxed(uint64_t* bar, uint32_t parity, BShared* sh, int code) {
+  const uint32_t a = smem_u32(bar);
+  for (int i = 0; i < 64; ++i) {
+    if (mbar_try_wait(a, parity)) return true;
+    __nanosleep(100);
+  }
+  return bwait(bar, parity, sh, code);
 }
 
 // TMA loads of one 128 x D tile (D/64 boxes) at (row, head, batch)
@@ -179,7 +208,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-        if (!bwait(&sh->empty[stage], phase ^ 1, sh, 41)) break;
+        if (!bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 41)) break;
         const uint32_t bar = smem_u32(&sh->full[stage]);
         mbar_expect_tx(bar, 2 * C::kTileBytes);
         const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
@@ -196,7 +225,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int it = 0; it < total; ++it) {
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
       bool w = true;
-      if (lane == 0) w = bwait(&sh->empty[stage], phase ^ 1, sh, 42);
+      if (lane == 0) w = bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 42);
       if (!__all_sync(0xffffffffu, w)) break;
       for (int i = lane; i < kT; i += 32) {
         const int row = m * kT + i;
@@ -232,8 +261,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       for (int it = 0; it < total && ok; ++it) {
+        FA_BTRACE(2, it, 0);
         wwait(&sh->full[stage], phase, 44);
         if (!ok) break;
+        FA_BTRACE(2, it, 1);
         const uint32_t sQ = sRing + stage * 2 * C::kTileBytes, sdO = sQ + C::kTileBytes;
         if (elect_one()) {
           mma_kmajor<D>(tS, sK, sQ, idesc_s);     // S^T  = K Q^T
@@ -241,14 +272,17 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           mma_commit(smem_u32(&sh->s_full));
         }
         __syncwarp();
+        FA_BTRACE(2, it, 2);
         wwait(&sh->pds_ready, it & 1, 45);
         if (!ok) break;
+        FA_BTRACE(2, it, 3);
         if (elect_one()) {
           mma_from_tmem<D>(tdV, tS, sdO, idesc_acc, it > 0);   // dV += P^T dO
           mma_from_tmem<D>(tdK, tdP, sQ, idesc_acc, it > 0);   // dK += dS^T Q
           mma_commit(smem_u32(&sh->empty[stage]));
         }
         __syncwarp();
+        FA_BTRACE(2, it, 4);
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
@@ -273,52 +307,69 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (cfg.wl >= 0) masked |= (n0 < q0 + kHalfT - 1 + off - cfg.wl);
       if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
 
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
       ok = bwait(&sh->s_full, it & 1, sh, 46) && bwait(&sh->stat_full[stage], phase, sh, 47);
       if (!ok) break;
       tc_fence_after();
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 1);
       uint32_t rs[2][32], rp[2][32];
       tmem_ld32(tS + lane_addr + x * kHalfT, rs[0]);
       tmem_ld32(tS + lane_addr + x * kHalfT + 32, rs[1]);
       tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
       tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
       tmem_wait_ld();
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
       const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
       const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+      // kSlow: score pipeline extras and/or the mask have to be evaluated per element
+      auto body = [&](auto slow_tag) {
+        constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t pk[16], dk_[16];
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t pk[16], dk_[16];
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 l4 = L4[cc * 8 + i4], d4 = D4[cc * 8 + i4];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], ds[4];
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 l4 = L4[cc * 8 + i4], d4 = D4[cc * 8 + i4];
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], ds[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = i4 * 4 + e;
-            const float s = __uint_as_float(rs[cc][i]);
-            const float dp = __uint_as_float(rp[cc][i]);
-            float th = 0.f;
-            float sc;
-            if (kExtras) sc = score_log2(cfg, slope, s, q0 + cc * 32 + i + off, key, th) - lv[e];
-            else sc = fmaf(s, cfg.scale_log2, -lv[e]);
-            float pe = ex2(sc);
-            if (masked && !visible(cfg, q0 + cc * 32 + i + off, key, 0x7fffffff)) pe = 0.f;
-            float de = pe * (dp - dv[e]);
-            if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-            pv[e] = pe;
-            ds[e] = de;
+            for (int e = 0; e < 4; ++e) {
+              const int i = i4 * 4 + e;
+              const float s = __uint_as_float(rs[cc][i]);
+              const float dp = __uint_as_float(rp[cc][i]);
+              if (kSlow) {
+                const int qp = q0 + cc * 32 + i + off;
+                float th = 0.f;
+                float sc;
+                if (kExtras) sc = score_log2(cfg, slope, s, qp, key, th) - lv[e];
+                else sc = fmaf(s, cfg.scale_log2, -lv[e]);
+                float pe = ex2(sc);
+                if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
+                float de = pe * (dp - dv[e]);
+                if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+                pv[e] = pe;
+                ds[e] = de;
+              } else {
+                pv[e] = ex2(fmaf(s, cfg.scale_log2, -lv[e]));
+                ds[e] = pv[e] * (dp - dv[e]);
+              }
+            }
+            pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
+            pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
+            dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
+            dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
           }
-          pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
-          pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
-          dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
-          dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
+          tmem_st16(tS + lane_addr + x * kHalfT + cc * 16, pk);
+          tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
         }
-        tmem_st16(tS + lane_addr + x * kHalfT + cc * 16, pk);
-        tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
-      }
+      };
+      if (kExtras || masked) body(std::true_type{});
+      else body(std::false_type{});
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->pds_ready));
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
       if (++stage == C::kStages) { stage = 0; phase ^= 1; }
     }
 
@@ -433,7 +484,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < total; ++j) {
-        if (!bwait(&sh->empty[stage], phase ^ 1, sh, 51)) break;
+        if (!bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 51)) break;
         const uint32_t bar = smem_u32(&sh->full[stage]);
         mbar_expect_tx(bar, 2 * C::kTileBytes);
         const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
@@ -514,31 +565,40 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
       tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
       tmem_wait_ld();
+      auto body = [&](auto slow_tag) {
+        constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t dk_[16];
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t dk_[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float ds2[2];
+          for (int i = 0; i < 32; i += 2) {
+            float ds2[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = k0 + cc * 32 + i + e;
-            const float s = __uint_as_float(rs[cc][i + e]);
-            const float dp = __uint_as_float(rp[cc][i + e]);
-            float th = 0.f;
-            float sc;
-            if (kExtras) sc = score_log2(cfg, slope, s, qpos, col, th) - l2;
-            else sc = fmaf(s, cfg.scale_log2, -l2);
-            float pe = ex2(sc);
-            if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
-            float de = pe * (dp - dl);
-            if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-            ds2[e] = de;
+            for (int e = 0; e < 2; ++e) {
+              const float s = __uint_as_float(rs[cc][i + e]);
+              const float dp = __uint_as_float(rp[cc][i + e]);
+              if (kSlow) {
+                const int col = k0 + cc * 32 + i + e;
+                float th = 0.f;
+                float sc;
+                if (kExtras) sc = score_log2(cfg, slope, s, qpos, col, th) - l2;
+                else sc = fmaf(s, cfg.scale_log2, -l2);
+                float pe = ex2(sc);
+                if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
+                float de = pe * (dp - dl);
+                if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+                ds2[e] = de;
+              } else {
+                ds2[e] = ex2(fmaf(s, cfg.scale_log2, -l2)) * (dp - dl);
+              }
+            }
+            dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
           }
-          dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
+          tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
         }
-        tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
-      }
+      };
+      if (kExtras || masked) body(std::true_type{});
+      else body(std::false_type{});
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->pds_ready));
