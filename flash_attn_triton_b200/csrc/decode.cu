@@ -132,6 +132,21 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
     T* dK = sK + st * BN * P;
     T* dV = sV + st * BN * P;
     const int key0 = k_begin + ti * BN;
+    if (geo.page_shift >= 6 && pad == 0) {
+      // the 64-key tile lies inside one page (pages are a power of two >= 64 rows and tiles
+      // start on multiples of 64): one table lookup per thread and tile
+      const int64_t kt = cache_row_offset(p, b, key0, geo.page_shift, p.kc_stride);
+      const int64_t vt = cache_row_offset(p, b, key0, geo.page_shift, p.vc_stride);
+#pragma unroll
+      for (int i = tid; i < BN * CPR; i += NT) {
+        const int r = i / CPR, c = i % CPR;
+        const bool ok = key0 + r < k_end;
+        const int rr = ok ? r : 0;
+        cp_async16(smem_u32(dK + r * P + c * 8), kbase + kt + rr * p.kc_stride[1] + c * 8, ok ? 16 : 0);
+        cp_async16(smem_u32(dV + r * P + c * 8), vbase + vt + rr * p.vc_stride[1] + c * 8, ok ? 16 : 0);
+      }
+      return;
+    }
     for (int i = tid; i < BN * CPR; i += NT) {
       const int r = i / CPR, c = i % CPR;
       const int key = key0 + r;
