@@ -66,6 +66,7 @@ class Int8Args(C.Structure):
         ("q", C.c_void_p), ("k8", C.c_void_p), ("s_k", C.c_void_p), ("v", C.c_void_p),
         ("o", C.c_void_p), ("lse2", C.c_void_p),
         ("softmax_scale", C.c_float), ("causal", C.c_int32),
+        ("q8_scratch", C.c_void_p), ("sq_scratch", C.c_void_p),
     ]
 
 

@@ -237,6 +237,10 @@ def int8_forward(q, k, v, causal, scale, impl=N.IMPL_AUTO):
                                            v.data_ptr(), o.data_ptr(), lse.data_ptr())
     a.softmax_scale = float(scale)
     a.causal = int(bool(causal))
+    if D == 128 and impl != N.IMPL_MMA:
+        q8 = torch.empty(q.shape, dtype=torch.int8, device=q.device)
+        s_q = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+        a.q8_scratch, a.sq_scratch = q8.data_ptr(), s_q.data_ptr()
     with torch.cuda.device(q.device):
         N.check(N.lib().fa_fwd_int8(C.byref(a), N.stream_ptr(q.device)), "fa_fwd_int8")
     return o, lse, k8, s_k

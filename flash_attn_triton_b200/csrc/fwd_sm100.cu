@@ -27,6 +27,8 @@
 //
 // Every mbarrier wait is bounded; on timeout the CTA raises a device-side status word,
 // releases its TMEM and returns.
+#include <cstring>
+
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -77,6 +79,10 @@ struct Shared {
   uint32_t tmem_base;
   volatile int abort_flag;
   float2 ml[2][kBM];       // epilogue exchange: (reference max, row sum) of each stream
+  // INT8 variant: key scales of the current score tiles, staged by warp 10
+  uint64_t sk_full[2];     // [score buffer] scales written
+  uint64_t sk_empty[2];    // [score buffer] scales consumed (256 arrivals)
+  alignas(16) float skt[2][kBN];
 };
 
 __device__ __forceinline__ bool wait_bar_slow(uint32_t a, uint32_t parity, Shared* sh, int code) {
@@ -108,10 +114,15 @@ static_assert(sizeof(Shared) <= 4096, "Shared must fit its reserve");
 
 }  // namespace
 
-template <typename T, int D, bool kExtras>
+// kInt8: Q and K are int8 codes (tensor maps over the code buffers, 1 byte per element), QK^T is
+// tcgen05.mma.kind::i8 with an int32 accumulator, and the per-row / per-key scales sq, sk are
+// folded into the score epilogue; P@V stays in T.
+template <typename T, int D, bool kExtras, bool kInt8>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const fa_attn_args p, const ScoreCfg cfg) {
+                 const __grid_constant__ CUtensorMap tmV, const fa_attn_args p, const ScoreCfg cfg,
+                 const float* __restrict__ sq, const float* __restrict__ sk) {
+  static_assert(!kInt8 || D == 128, "the INT8 variant stages 128-byte code rows");
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
@@ -150,6 +161,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(smem_u32(&sh->kv_full[i]), 1);
       mbar_init(smem_u32(&sh->kv_empty[i]), 1);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh->sk_full[i]), 1);
+      mbar_init(smem_u32(&sh->sk_empty[i]), 256);
+    }
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -163,8 +178,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem = sh->tmem_base;
 
   if (warp >= 10) {
-    // idle warps of the producer/MMA warpgroup
+    // idle warps of the producer/MMA warpgroup; in the INT8 variant warp 10 stages the key
+    // scales of score tile j into shared memory (slot j & 1)
     reg_dealloc<56>();
+    if (kInt8 && warp == 10) {
+      const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
+      for (int j = 0; j < nsteps; ++j) {
+        const int buf = j & 1;
+        bool w = true;
+        if (lane == 0) w = wait_bar(&sh->sk_empty[buf], ((j >> 1) & 1) ^ 1, sh, 12);
+        if (!__all_sync(0xffffffffu, w)) break;
+        for (int i = lane; i < kBN; i += 32) {
+          const int col = (n_lo + j) * kBN + i;
+          sh->skt[buf][i] = col < si.k_len ? sk[bh_rows + col] : 1.f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->sk_full[buf]));
+      }
+    }
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
     reg_dealloc<56>();
@@ -176,30 +207,40 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int kb = (int)si.k_boff;
       {
         const uint32_t bar = smem_u32(&sh->q_full);
-        mbar_expect_tx(bar, C::kTileBytes);
-        for (int x = 0; x < C::kBoxes; ++x)
-          tma_load_4d(sQ + x * (kBM * 128), &tmQ, bar, x * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+        if (kInt8) {
+          mbar_expect_tx(bar, kBM * D);
+          tma_load_4d(sQ, &tmQ, bar, 0, h, (int)si.q_row0 + m0, (int)si.q_boff);
+        } else {
+          mbar_expect_tx(bar, C::kTileBytes);
+          for (int x = 0; x < C::kBoxes; ++x)
+            tma_load_4d(sQ + x * (kBM * 128), &tmQ, bar, x * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+        }
       }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      auto load_kv = [&](const CUtensorMap* tm, int tile) {
+      auto load_kv = [&](const CUtensorMap* tm, int tile, bool codes) {
         if (!ok) return;
         ok = wait_bar(&sh->kv_empty[stage], phase ^ 1, sh, 11);
         if (!ok) return;
         const uint32_t bar = smem_u32(&sh->kv_full[stage]);
-        mbar_expect_tx(bar, C::kTileBytes);
-        for (int x = 0; x < C::kBoxes; ++x)
-          tma_load_4d(sKV + stage * C::kTileBytes + x * (kBN * 128), tm, bar, x * 64, hk,
-                      krow0 + tile * kBN, kb);
+        if (codes) {  // int8 K tile: one box of 128-byte rows
+          mbar_expect_tx(bar, kBN * D);
+          tma_load_4d(sKV + stage * C::kTileBytes, tm, bar, 0, hk, krow0 + tile * kBN, kb);
+        } else {
+          mbar_expect_tx(bar, C::kTileBytes);
+          for (int x = 0; x < C::kBoxes; ++x)
+            tma_load_4d(sKV + stage * C::kTileBytes + x * (kBN * 128), tm, bar, x * 64, hk,
+                        krow0 + tile * kBN, kb);
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       };
       // order of use: K0, K1, then V_j, K_{j+2}
-      load_kv(&tmK, n_lo);
-      if (nsteps > 1) load_kv(&tmK, n_lo + 1);
+      load_kv(&tmK, n_lo, kInt8);
+      if (nsteps > 1) load_kv(&tmK, n_lo + 1, kInt8);
       for (int j = 0; j < nsteps; ++j) {
-        load_kv(&tmV, n_lo + j);
-        if (j + 2 < nsteps) load_kv(&tmK, n_lo + j + 2);
+        load_kv(&tmV, n_lo + j, false);
+        if (j + 2 < nsteps) load_kv(&tmK, n_lo + j + 2, kInt8);
       }
     }
   } else if (warp == 9) {
@@ -225,11 +266,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!ok) return;
         const uint32_t kbase = sKV + stage * C::kTileBytes;
         if (elect_one()) {
+          if (kInt8) {
+            constexpr uint32_t idesc_i8 = make_idesc(2, 1, 0, 0, kBM, kBN);  // s32 <- s8 x s8
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t o = (kk / 4) * (kBM * 128) + (kk % 4) * 32;
-            mma_f16_ss(tmem + buf * kBN, make_smem_desc(sQ + o, 16, 1024),
-                       make_smem_desc(kbase + o, 16, 1024), idesc_qk, kk > 0);
+            for (int kk = 0; kk < D / 32; ++kk)
+              mma_i8_ss(tmem + buf * kBN, make_smem_desc(sQ + kk * 32, 16, 1024),
+                        make_smem_desc(kbase + kk * 32, 16, 1024), idesc_i8, kk > 0);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t o = (kk / 4) * (kBM * 128) + (kk % 4) * 32;
+              mma_f16_ss(tmem + buf * kBN, make_smem_desc(sQ + o, 16, 1024),
+                         make_smem_desc(kbase + o, 16, 1024), idesc_qk, kk > 0);
+            }
           }
           mma_commit(smem_u32(&sh->s_full[buf]));
           mma_commit(smem_u32(&sh->kv_empty[stage]));
@@ -283,6 +332,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     const int tq_min = m0 + off, tq_max = tq_min + kBM - 1;
+    // INT8: scale of this query row and the row of key scales of this (batch, head)
+    const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
+    const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
+    const float qk_scale = cfg.scale * 1.44269504f;
 
     for (int j = 0; j < nsteps && ok; ++j) {
       const int buf = j & 1;
@@ -305,8 +358,32 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_wait_ld();
       if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 2);
 
-      const bool prescaled = kExtras || masked;
-      if (prescaled) {
+      const bool prescaled = kExtras || masked || kInt8;
+      if (kInt8) {
+        // (float(acc) * (s_q * s_k)) * (softmax_scale * log2 e), in the reference's order.
+        // |acc| <= 128*127*127 < 2^22, so int -> float is exact through the 1.5*2^23 bias
+        // (an integer add and a float subtract instead of a quarter-rate I2F).
+        ok = wait_bar(&sh->sk_full[buf], (j >> 1) & 1, sh, 37 + x);
+        if (!ok) break;
+        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[buf][x * kHalf]);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 s4 = S4[cc * 8 + i4];
+            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = i4 * 4 + e;
+              const float acc = __uint_as_float(0x4B400000u + r[cc][i]) - 12582912.0f;
+              float v = __fmul_rn(__fmul_rn(acc, __fmul_rn(sq_row, sv[e])), qk_scale);
+              if (masked && !visible(cfg, qpos, k0 + cc * 32 + i, si.k_len)) v = -INFINITY;
+              r[cc][i] = __float_as_uint(v);
+            }
+          }
+        }
+        mbar_arrive(smem_u32(&sh->sk_empty[buf]));
+      } else if (prescaled) {
         // score pipeline and mask applied once, in place; values end up in the log2 domain
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
@@ -381,8 +458,16 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           const float p0 = ex2(fmaf(__uint_as_float(r[cc][i]), mul, -m_safe));
           const float p1 = ex2(fmaf(__uint_as_float(r[cc][i + 1]), mul, -m_safe));
-          ps[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = Elem<T>::pack(p0, p1);
+          if (kInt8) {
+            // Outlier keys make the rows peaky; with a stale reference maximum the dominant
+            // probability is 2^x instead of exactly 1, so its rounding to T would not cancel
+            // in O / l unless l sums the ROUNDED values that enter P@V.
+            const float2 pr = Elem<T>::unpack(pk[i >> 1]);
+            ps[(i >> 1) & 3] += pr.x + pr.y;
+          } else {
+            ps[(i >> 1) & 3] += p0 + p1;
+          }
         }
         tmem_st16(tSx + buf * kBN + cc * 16, pk);
       }
@@ -487,14 +572,14 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
     return FA_ERR_LAUNCH;
   }
   const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
-  auto kern = extras ? fwd_sm100_kernel<T, D, true> : fwd_sm100_kernel<T, D, false>;
+  auto kern = extras ? fwd_sm100_kernel<T, D, true, false> : fwd_sm100_kernel<T, D, false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) {
     set_error("fwd_sm100: cudaFuncSetAttribute(%d): %s", C::kSmemBytes, cudaGetErrorString(e));
     return FA_ERR_LAUNCH;
   }
   dim3 grid((a.seqlen_q + kBM - 1) / kBM, a.heads_q, a.batch);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a, cfg);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a, cfg, nullptr, nullptr);
   return check_launch("fwd_sm100");
 }
 
@@ -511,6 +596,60 @@ int fwd_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
                               : launch<__half, 128>(a, cfg, st, q_rows, k_rows);
   return a.dtype == FA_BF16 ? launch<__nv_bfloat16, 64>(a, cfg, st, q_rows, k_rows)
                             : launch<__half, 64>(a, cfg, st, q_rows, k_rows);
+}
+
+// ---------------------------------------------------------------------------------------
+// INT8-QK^T forward on contiguous (batch, heads, seqlen, 128) tensors
+// ---------------------------------------------------------------------------------------
+int quantize_q(const void* q, int8_t* q8, float* s_q, int64_t rows, int head_dim, cudaStream_t st);
+
+bool fwd_int8_sm100_supported(const fa_int8_args& a) {
+  if (a.head_dim != 128 || a.softmax_scale < 0.f) return false;
+  if (a.q8_scratch == nullptr || a.sq_scratch == nullptr) return false;
+  if (a.impl == FA_IMPL_AUTO && a.seqlen < 256) return false;
+  return true;
+}
+
+int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
+  constexpr int D = 128;
+  using C = Cfg<D>;
+  const int64_t rows = (int64_t)a.batch * a.heads * a.seqlen;
+  if (int r = quantize_q(a.q, a.q8_scratch, a.sq_scratch, rows, D, st)) return r;
+  const int B = a.batch, H = a.heads, S = a.seqlen;
+  CUtensorMap tq, tk, tv;
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+    const uint64_t s8[3] = {(uint64_t)S * D, (uint64_t)D, (uint64_t)H * S * D};
+    const uint64_t s16[3] = {(uint64_t)S * D * 2, (uint64_t)D * 2, (uint64_t)H * S * D * 2};
+    const uint32_t box8[4] = {128, 1, 128, 1}, box16[4] = {64, 1, 128, 1};
+    if (!encode_tmap(&tq, a.q8_scratch, 1, 4, dims, s8, box8) || !encode_tmap(&tk, a.k8, 1, 4, dims, s8, box8) ||
+        !encode_tmap(&tv, a.v, 2, 4, dims, s16, box16)) {
+      set_error("fwd_int8_sm100: cuTensorMapEncodeTiled failed");
+      return FA_ERR_LAUNCH;
+    }
+  }
+  fa_attn_args p;
+  memset(&p, 0, sizeof(p));
+  p.dtype = FA_F16;
+  p.device = a.device;
+  p.batch = B; p.seqlen_q = S; p.seqlen_k = S; p.heads_q = H; p.heads_kv = H; p.head_dim = D;
+  p.o = a.o;
+  p.o_stride[0] = (int64_t)H * S * D; p.o_stride[1] = D; p.o_stride[2] = (int64_t)S * D;
+  p.lse2 = a.lse2;
+  p.lse_stride[0] = (int64_t)H * S; p.lse_stride[1] = 1; p.lse_stride[2] = S;
+  p.softmax_scale = a.softmax_scale;
+  p.causal = a.causal;
+  p.window_left = p.window_right = -1;
+  const ScoreCfg cfg = make_score_cfg(a.softmax_scale, 0.f, a.causal, -1, -1, false);
+  auto kern = fwd_sm100_kernel<__half, D, false, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) {
+    set_error("fwd_int8_sm100: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return FA_ERR_LAUNCH;
+  }
+  dim3 grid((S + kBM - 1) / kBM, H, B);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p, cfg, a.sq_scratch, a.s_k);
+  return check_launch("fwd_int8_sm100");
 }
 
 #ifdef FA_TRACE

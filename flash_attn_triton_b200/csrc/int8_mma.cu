@@ -14,7 +14,8 @@ __device__ __forceinline__ int round_i8(float x) {
 // K quantiser: rows x D fp16 -> int8 codes + fp32 scale per row.  HBM-bound: 2 B read and
 // 1 B written per element.  One 16-byte load per thread, D/8 lanes per row.
 // ---------------------------------------------------------------------------------------
-template <int D>
+// kDivide: codes = round(x / s) (the reference's query form) instead of round(x * (1/s))
+template <int D, bool kDivide = false>
 __global__ void __launch_bounds__(256) quantize_k_kernel(const __half* __restrict__ k,
                                                          int8_t* __restrict__ k8,
                                                          float* __restrict__ s_k, int64_t rows) {
@@ -43,8 +44,10 @@ __global__ void __launch_bounds__(256) quantize_k_kernel(const __half* __restric
   uint32_t lo = 0, hi = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    lo |= (uint32_t)(uint8_t)(int8_t)round_i8(__fmul_rn(x[i], inv)) << (8 * i);
-    hi |= (uint32_t)(uint8_t)(int8_t)round_i8(__fmul_rn(x[4 + i], inv)) << (8 * i);
+    const float a = kDivide ? __fdiv_rn(x[i], sc) : __fmul_rn(x[i], inv);
+    const float c2 = kDivide ? __fdiv_rn(x[4 + i], sc) : __fmul_rn(x[4 + i], inv);
+    lo |= (uint32_t)(uint8_t)(int8_t)round_i8(a) << (8 * i);
+    hi |= (uint32_t)(uint8_t)(int8_t)round_i8(c2) << (8 * i);
   }
   if (ok) {
     *reinterpret_cast<uint2*>(k8 + row * D + c * 8) = make_uint2(lo, hi);
@@ -67,6 +70,20 @@ int quantize_k(const void* k, int8_t* k8, float* s_k, int64_t rows, int head_dim
 #undef FA_Q
   set_error("INT8 path needs head_dim in {32,64,128,256}, got %d", head_dim);
   return FA_ERR_UNSUPPORTED;
+}
+
+// Per-query-row codes in the division form q / s_q (attention_kernel_int8.py:33-39, :100);
+// used by the tcgen05 INT8 forward, which stages the codes with TMA.
+int quantize_q(const void* q, int8_t* q8, float* s_q, int64_t rows, int head_dim, cudaStream_t st) {
+  if (rows == 0) return FA_OK;
+  if (head_dim != 128) {
+    set_error("quantize_q: head_dim 128 only");
+    return FA_ERR_UNSUPPORTED;
+  }
+  constexpr int RPB = 256 / (128 / 8);
+  quantize_k_kernel<128, true><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(
+      reinterpret_cast<const __half*>(q), q8, s_q, rows);
+  return check_launch("quantize_q");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -223,6 +223,11 @@ typedef struct fa_int8_args {
   float* lse2;      /* (batch, heads, seqlen) or NULL */
   float softmax_scale;
   int32_t causal;
+  /* Scratch for the tcgen05 kernel, which stages the query codes with TMA: int8
+   * (batch*heads, seqlen, head_dim) and fp32 (batch*heads, seqlen).  When either is NULL the
+   * mma.sync kernel (which quantises q in shared memory) is used. */
+  int8_t* q8_scratch;
+  float* sq_scratch;
 } fa_int8_args;
 
 int fa_fwd_int8(const fa_int8_args* args, void* stream);
