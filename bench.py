@@ -181,6 +181,7 @@ def cpu_sample(seconds_budget=20.0):
     """fwd+bwd of (batch, head) slices of the headline workload through the fp32 oracle until
     the budget is used.  Returns (TFLOP/s, threads, description)."""
     from oracle import attention_oracle as orc
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))  # torchrun pins OMP to 1
     g = torch.Generator().manual_seed(0)
     bh = 1
     q = torch.randn(1, S, bh, D, generator=g).half()
@@ -287,6 +288,56 @@ def profile_case(args):
     torch.cuda.synchronize()
     print(json.dumps({"profile_case": "B2 H16 S4096 D128 causal fwd+bwd", "steps": args.warmup + args.steps,
                       "device_wait_status": N.lib().fa_device_wait_status(0)}))
+
+
+def extras_bench(dev, peaks):
+    """The other BASELINE configs, one number each (rank 0, after the headline measurement)."""
+    import numpy as np
+
+    import flash_attn_triton_b200 as fa
+    from flash_attn_triton_b200 import _ops
+    out = {}
+    # config 5: INT8 forward B8 H32 S8192 D128, 1 % of K entries x8
+    Bq, Hq, Sq, Dq = 8, 32, 8192, 128
+    g = torch.Generator(device=dev).manual_seed(5)
+    q = torch.randn(Bq, Hq, Sq, Dq, device=dev, dtype=torch.float16, generator=g)
+    v = torch.randn(Bq, Hq, Sq, Dq, device=dev, dtype=torch.float16, generator=g)
+    k = torch.randn(Bq, Hq, Sq, Dq, device=dev, dtype=torch.float16, generator=g)
+    k = torch.where(torch.rand(Bq, Hq, Sq, Dq, device=dev, generator=g) < 0.01, k * 8, k)
+    for _ in range(2):
+        _ops.quantize_k_int8(k)
+    ms = event_time(lambda: _ops.quantize_k_int8(k), 5)
+    out["int8_k_quantiser"] = {"ms": ms, "GB/s": k.numel() * 3 / ms / 1e6, "frac_of_measured_hbm": k.numel() * 3 / ms / 1e6 / peaks["hbm"]}
+    for causal in (False, True):
+        for _ in range(2):
+            fa.attention_int8(q, k, v, causal=causal)
+        ms = event_time(lambda: fa.attention_int8(q, k, v, causal=causal), 3)
+        fl = (2.0 if causal else 4.0) * Bq * Hq * Sq * Sq * Dq
+        out["int8_fwd_causal" if causal else "int8_fwd"] = {"ms": ms, "tflops": fl / ms / 1e9, "note": "incl. K and Q quantiser prepasses"}
+    del q, k, v
+    # config 3: packed varlen fwd+bwd, 32 sequences, H32 D128, causal + window 1024 + ALiBi + softcap 30
+    rng = np.random.default_rng(3)
+    lens = (64 * rng.integers(4, 65, size=32)).tolist()
+    Hh, Dd, T = 32, 128, int(sum(lens))
+    g = torch.Generator(device=dev).manual_seed(3)
+    q, k, v, do = (torch.randn(T, Hh, Dd, device=dev, dtype=torch.float16, generator=g) for _ in range(4))
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+    sl = torch.tensor([2.0 ** (-8 * (i + 1) / Hh) for i in range(Hh)], device=dev)
+    fa.set_validation(False)
+
+    def vstep():
+        qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
+        o = fa.flash_attn_varlen_func(qq, kk, vv, cu, cu, max(lens), max(lens), causal=True,
+                                      window_size=(1024, 0), alibi_slopes=sl, softcap=30.0)
+        torch.autograd.grad(o, (qq, kk, vv), do)
+    for _ in range(2):
+        vstep()
+    ms = event_time(vstep, 3)
+    fa.set_validation(True)
+    pairs = sum(L * (L + 1) // 2 if L <= 1025 else 1025 * 1026 // 2 + (L - 1025) * 1025 for L in lens)
+    fl = 3.5 * 4.0 * Dd * Hh * pairs
+    out["varlen_fwd_bwd"] = {"ms": ms, "tflops": fl / ms / 1e9, "tokens": T}
+    return out
 
 
 def run_ours(args, rank, world, local_rank):
@@ -419,6 +470,9 @@ def run_ours(args, rank, world, local_rank):
     if rank != 0:
         return
     decode = decode_bench(dev, peaks)
+    del q, k, v, do, o, lse, dq, dk, dv, delta
+    torch.cuda.empty_cache()
+    extras = extras_bench(dev, peaks)
     cpu_v, cores, sample = cpu_sample(15.0)
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -431,7 +485,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
-        "kernels": kern, "decode": decode, "device_wait_status": wait_status,
+        "kernels": kern, "decode": decode, "other_configs": extras, "device_wait_status": wait_status,
         "frac_of_2250_datasheet": value / world / 2250.0, "gather_ms": gather_ms,
     }
     print(json.dumps(line))
