@@ -70,8 +70,8 @@ struct BShared {
   uint64_t full[4];       // streamed pair landed
   uint64_t empty[4];      // streamed pair (and its statistics) consumed
   uint64_t stat_full[4];  // statistics of the streamed query tile written (dK/dV kernel)
-  uint64_t s_full;        // S and dP computed
-  uint64_t pds_ready;     // P and dS written back (256 arrivals)
+  uint64_t s_full[2];     // [half] S and dP of that half computed
+  uint64_t pds_ready[2];  // [half] P and dS of that half written back (256 arrivals)
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -133,6 +133,34 @@ __device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t a_tmem, 
   }
 }
 
+// Half-tile forms used by the pipelined loops: the streamed 128-row tile is consumed as two
+// 64-row halves, each with its own 64-column score buffers, so that the element-wise work on
+// one half overlaps the MMAs of the other.
+//
+// 128 x 64 x D product: A = resident K-major tile, B = rows [64h, 64h+64) of a K-major tile
+template <int D>
+__device__ __forceinline__ void mma_kmajor_half(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
+                                                int h, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t o = (kk / 4) * (kT * 128) + (kk % 4) * 32;
+    mma_f16_ss(d_tmem, make_smem_desc(a_smem + o, 16, 1024),
+               make_smem_desc(b_smem + h * (kHalfT * 128) + o, 16, 1024), idesc, kk > 0);
+  }
+}
+// acc(128 x D) += A(128 x 64 fp16 pairs in TMEM) * B(rows [64h, 64h+64) of an MN-major tile).
+// A was written by the two element-wise groups as two 16-column blocks at a_tmem, a_tmem+32.
+template <int D>
+__device__ __forceinline__ void mma_from_tmem_half(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
+                                                   int h, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < kHalfT / 16; ++kk) {
+    const uint32_t a = a_tmem + (kk / 2) * 32 + (kk % 2) * 8;
+    mma_f16_ts(d_tmem, a, make_smem_desc(b_smem + h * (kHalfT * 128) + kk * 2048, kT * 128, 1024), idesc,
+               (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
 }  // namespace
 
 // =======================================================================================
@@ -167,8 +195,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
-    mbar_init(smem_u32(&sh->s_full), 1);
-    mbar_init(smem_u32(&sh->pds_ready), 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh->s_full[i]), 1);
+      mbar_init(smem_u32(&sh->pds_ready[i]), 256);
+    }
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(smem_u32(&sh->full[i]), 1);
@@ -248,7 +278,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // ------------------------------- MMA issuer -----------------------------------------
     reg_dealloc<56>();
     if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kHalfT);
       constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
       bool ok = true;
       auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
@@ -257,33 +287,40 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         ok = __all_sync(0xffffffffu, w) && ok;
         tc_fence_after();
       };
+      auto ring = [&](int it) { return sRing + (it % C::kStages) * 2 * C::kTileBytes; };
+      // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for half-step g (iteration g/2, half g&1)
+      auto issue_scores = [&](int g) {
+        const int it = g >> 1, h = g & 1;
+        if (h == 0) wwait(&sh->full[it % C::kStages], (it / C::kStages) & 1, 44);
+        if (!ok) return;
+        const uint32_t sQ = ring(it), sdO = sQ + C::kTileBytes;
+        if (elect_one()) {
+          mma_kmajor_half<D>(tS + h * kHalfT, sK, sQ, h, idesc_s);
+          mma_kmajor_half<D>(tdP + h * kHalfT, sV, sdO, h, idesc_s);
+          mma_commit(smem_u32(&sh->s_full[h]));
+        }
+        __syncwarp();
+      };
       wwait(&sh->res_full, 0, 43);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int it = 0; it < total && ok; ++it) {
-        FA_BTRACE(2, it, 0);
-        wwait(&sh->full[stage], phase, 44);
+      const int G2 = 2 * total;
+      if (ok) issue_scores(0);
+      if (ok) issue_scores(1);
+      for (int g = 0; g < G2 && ok; ++g) {
+        const int it = g >> 1, h = g & 1;
+        FA_BTRACE(2, g, 0);
+        wwait(&sh->pds_ready[h], it & 1, 45);
         if (!ok) break;
-        FA_BTRACE(2, it, 1);
-        const uint32_t sQ = sRing + stage * 2 * C::kTileBytes, sdO = sQ + C::kTileBytes;
+        FA_BTRACE(2, g, 1);
+        const uint32_t sQ = ring(it), sdO = sQ + C::kTileBytes;
         if (elect_one()) {
-          mma_kmajor<D>(tS, sK, sQ, idesc_s);     // S^T  = K Q^T
-          mma_kmajor<D>(tdP, sV, sdO, idesc_s);   // dP^T = V dO^T
-          mma_commit(smem_u32(&sh->s_full));
+          mma_from_tmem_half<D>(tdV, tS + h * kHalfT, sdO, h, idesc_acc, g > 0);   // dV += P^T_h dO_h
+          mma_from_tmem_half<D>(tdK, tdP + h * kHalfT, sQ, h, idesc_acc, g > 0);   // dK += dS^T_h Q_h
+          if (h == 1) mma_commit(smem_u32(&sh->empty[it % C::kStages]));
         }
         __syncwarp();
-        FA_BTRACE(2, it, 2);
-        wwait(&sh->pds_ready, it & 1, 45);
-        if (!ok) break;
-        FA_BTRACE(2, it, 3);
-        if (elect_one()) {
-          mma_from_tmem<D>(tdV, tS, sdO, idesc_acc, it > 0);   // dV += P^T dO
-          mma_from_tmem<D>(tdK, tdP, sQ, idesc_acc, it > 0);   // dK += dS^T Q
-          mma_commit(smem_u32(&sh->empty[stage]));
-        }
-        __syncwarp();
-        FA_BTRACE(2, it, 4);
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        FA_BTRACE(2, g, 2);
+        if (g + 2 < G2) issue_scores(g + 2);
+        FA_BTRACE(2, g, 3);
       }
       if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
       __syncwarp();
@@ -296,81 +333,77 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int it = 0; it < total && ok; ++it) {
+    for (int g = 0; g < 2 * total && ok; ++g) {
+      const int it = g >> 1, h = g & 1;
+      const int stage = it % C::kStages;
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-      const int q0 = m * kT + x * kHalfT;            // first query row of this group's columns
+      const int c0 = h * kHalfT + x * 32;            // first column (query row of the tile) of this thread
+      const int q0 = m * kT + c0;
       const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + hq] : 0.f;
       bool masked = false;
       if (cfg.causal) masked |= (n0 + kT - 1 > q0 + off);
-      if (cfg.wl >= 0) masked |= (n0 < q0 + kHalfT - 1 + off - cfg.wl);
+      if (cfg.wl >= 0) masked |= (n0 < q0 + 31 + off - cfg.wl);
       if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
 
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
-      ok = bwait(&sh->s_full, it & 1, sh, 46) && bwait(&sh->stat_full[stage], phase, sh, 47);
+      if ((warp & 3) == 0) FA_BTRACE(x, g, 0);
+      ok = bwait(&sh->s_full[h], it & 1, sh, 46);
+      if (ok && h == 0) ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
       if (!ok) break;
       tc_fence_after();
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 1);
-      uint32_t rs[2][32], rp[2][32];
-      tmem_ld32(tS + lane_addr + x * kHalfT, rs[0]);
-      tmem_ld32(tS + lane_addr + x * kHalfT + 32, rs[1]);
-      tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
-      tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
+      if ((warp & 3) == 0) FA_BTRACE(x, g, 1);
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_addr + c0, rs);
+      tmem_ld32(tdP + lane_addr + c0, rp);
       tmem_wait_ld();
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
-      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
-      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+      if ((warp & 3) == 0) FA_BTRACE(x, g, 2);
+      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][c0]);
+      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][c0]);
+      uint32_t pk[16], dk_[16];
       // kSlow: score pipeline extras and/or the mask have to be evaluated per element
       auto body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t pk[16], dk_[16];
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = L4[i4], d4 = D4[i4];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], ds[4];
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 l4 = L4[cc * 8 + i4], d4 = D4[cc * 8 + i4];
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pv[4], ds[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = i4 * 4 + e;
-              const float s = __uint_as_float(rs[cc][i]);
-              const float dp = __uint_as_float(rp[cc][i]);
-              if (kSlow) {
-                const int qp = q0 + cc * 32 + i + off;
-                float th = 0.f;
-                float sc;
-                if (kExtras) sc = score_log2(cfg, slope, s, qp, key, th) - lv[e];
-                else sc = fmaf(s, cfg.scale_log2, -lv[e]);
-                float pe = ex2(sc);
-                if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
-                float de = pe * (dp - dv[e]);
-                if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-                pv[e] = pe;
-                ds[e] = de;
-              } else {
-                pv[e] = ex2(fmaf(s, cfg.scale_log2, -lv[e]));
-                ds[e] = pv[e] * (dp - dv[e]);
-              }
+          for (int e = 0; e < 4; ++e) {
+            const int i = i4 * 4 + e;
+            const float sv = __uint_as_float(rs[i]);
+            const float dp = __uint_as_float(rp[i]);
+            if (kSlow) {
+              const int qp = q0 + i + off;
+              float th = 0.f;
+              float sc;
+              if (kExtras) sc = score_log2(cfg, slope, sv, qp, key, th) - lv[e];
+              else sc = fmaf(sv, cfg.scale_log2, -lv[e]);
+              float pe = ex2(sc);
+              if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
+              float de = pe * (dp - dv[e]);
+              if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+              pv[e] = pe;
+              ds[e] = de;
+            } else {
+              pv[e] = ex2(fmaf(sv, cfg.scale_log2, -lv[e]));
+              ds[e] = pv[e] * (dp - dv[e]);
             }
-            pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
-            pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
-            dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
-            dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
           }
-          tmem_st16(tS + lane_addr + x * kHalfT + cc * 16, pk);
-          tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
+          pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
+          pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
+          dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
+          dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
         }
       };
       if (kExtras || masked) body(std::true_type{});
       else body(std::false_type{});
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
+      tmem_st16(tS + lane_addr + c0, pk);
+      tmem_st16(tdP + lane_addr + c0, dk_);
+      if ((warp & 3) == 0) FA_BTRACE(x, g, 3);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->pds_ready));
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
-      if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      mbar_arrive(smem_u32(&sh->pds_ready[h]));
+      if ((warp & 3) == 0) FA_BTRACE(x, g, 4);
     }
 
     // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
@@ -445,8 +478,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
-    mbar_init(smem_u32(&sh->s_full), 1);
-    mbar_init(smem_u32(&sh->pds_ready), 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sh->s_full[i]), 1);
+      mbar_init(smem_u32(&sh->pds_ready[i]), 256);
+    }
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(smem_u32(&sh->full[i]), 1);
@@ -497,7 +532,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // ------------------------------- MMA issuer -----------------------------------------
     reg_dealloc<56>();
     if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kHalfT);
       constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
       bool ok = true;
       auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
@@ -506,27 +541,34 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         ok = __all_sync(0xffffffffu, w) && ok;
         tc_fence_after();
       };
+      auto ring = [&](int j) { return sRing + (j % C::kStages) * 2 * C::kTileBytes; };
+      // S_h = Q K_h^T and dP_h = dO V_h^T for half-step g (key tile g/2, half g&1)
+      auto issue_scores = [&](int g) {
+        const int j = g >> 1, h = g & 1;
+        if (h == 0) wwait(&sh->full[j % C::kStages], (j / C::kStages) & 1, 54);
+        if (!ok) return;
+        const uint32_t sKj = ring(j), sVj = sKj + C::kTileBytes;
+        if (elect_one()) {
+          mma_kmajor_half<D>(tS + h * kHalfT, sQ, sKj, h, idesc_s);
+          mma_kmajor_half<D>(tdP + h * kHalfT, sdO, sVj, h, idesc_s);
+          mma_commit(smem_u32(&sh->s_full[h]));
+        }
+        __syncwarp();
+      };
       wwait(&sh->res_full, 0, 53);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < total && ok; ++j) {
-        wwait(&sh->full[stage], phase, 54);
-        if (!ok) break;
-        const uint32_t sKj = sRing + stage * 2 * C::kTileBytes, sVj = sKj + C::kTileBytes;
-        if (elect_one()) {
-          mma_kmajor<D>(tS, sQ, sKj, idesc_s);     // S  = Q K^T
-          mma_kmajor<D>(tdP, sdO, sVj, idesc_s);   // dP = dO V^T
-          mma_commit(smem_u32(&sh->s_full));
-        }
-        __syncwarp();
-        wwait(&sh->pds_ready, j & 1, 55);
+      const int G2 = 2 * total;
+      if (ok) issue_scores(0);
+      if (ok) issue_scores(1);
+      for (int g = 0; g < G2 && ok; ++g) {
+        const int j = g >> 1, h = g & 1;
+        wwait(&sh->pds_ready[h], j & 1, 55);
         if (!ok) break;
         if (elect_one()) {
-          mma_from_tmem<D>(tdQ, tdP, sKj, idesc_acc, j > 0);   // dQ += dS K
-          mma_commit(smem_u32(&sh->empty[stage]));
+          mma_from_tmem_half<D>(tdQ, tdP + h * kHalfT, ring(j), h, idesc_acc, g > 0);   // dQ += dS_h K_h
+          if (h == 1) mma_commit(smem_u32(&sh->empty[j % C::kStages]));
         }
         __syncwarp();
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        if (g + 2 < G2) issue_scores(g + 2);
       }
       if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
       __syncwarp();
@@ -549,59 +591,56 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (l2 == -INFINITY) l2 = INFINITY;
     }
     bool ok = true;
-    for (int j = 0; j < total && ok; ++j) {
-      const int k0 = (n_lo + j) * kT + x * kHalfT;
-      bool masked = (k0 + kHalfT > si.k_len);
-      if (cfg.causal) masked |= (k0 + kHalfT - 1 > m0 + off);
+    for (int g = 0; g < 2 * total && ok; ++g) {
+      const int j = g >> 1, h = g & 1;
+      const int c0 = h * kHalfT + x * 32;          // first column (key of the tile) of this thread
+      const int k0 = (n_lo + j) * kT + c0;
+      bool masked = (k0 + 32 > si.k_len);
+      if (cfg.causal) masked |= (k0 + 31 > m0 + off);
       if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);
-      if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > m0 + off + cfg.wr);
+      if (cfg.wr >= 0) masked |= (k0 + 31 > m0 + off + cfg.wr);
 
-      ok = bwait(&sh->s_full, j & 1, sh, 56);
+      ok = bwait(&sh->s_full[h], j & 1, sh, 56);
       if (!ok) break;
       tc_fence_after();
-      uint32_t rs[2][32], rp[2][32];
-      tmem_ld32(tS + lane_addr + x * kHalfT, rs[0]);
-      tmem_ld32(tS + lane_addr + x * kHalfT + 32, rs[1]);
-      tmem_ld32(tdP + lane_addr + x * kHalfT, rp[0]);
-      tmem_ld32(tdP + lane_addr + x * kHalfT + 32, rp[1]);
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_addr + c0, rs);
+      tmem_ld32(tdP + lane_addr + c0, rp);
       tmem_wait_ld();
+      uint32_t dk_[16];
       auto body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t dk_[16];
+        for (int i = 0; i < 32; i += 2) {
+          float ds2[2];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float ds2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float s = __uint_as_float(rs[cc][i + e]);
-              const float dp = __uint_as_float(rp[cc][i + e]);
-              if (kSlow) {
-                const int col = k0 + cc * 32 + i + e;
-                float th = 0.f;
-                float sc;
-                if (kExtras) sc = score_log2(cfg, slope, s, qpos, col, th) - l2;
-                else sc = fmaf(s, cfg.scale_log2, -l2);
-                float pe = ex2(sc);
-                if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
-                float de = pe * (dp - dl);
-                if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-                ds2[e] = de;
-              } else {
-                ds2[e] = ex2(fmaf(s, cfg.scale_log2, -l2)) * (dp - dl);
-              }
+          for (int e = 0; e < 2; ++e) {
+            const float sv = __uint_as_float(rs[i + e]);
+            const float dp = __uint_as_float(rp[i + e]);
+            if (kSlow) {
+              const int col = k0 + i + e;
+              float th = 0.f;
+              float sc;
+              if (kExtras) sc = score_log2(cfg, slope, sv, qpos, col, th) - l2;
+              else sc = fmaf(sv, cfg.scale_log2, -l2);
+              float pe = ex2(sc);
+              if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
+              float de = pe * (dp - dl);
+              if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
+              ds2[e] = de;
+            } else {
+              ds2[e] = ex2(fmaf(sv, cfg.scale_log2, -l2)) * (dp - dl);
             }
-            dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
           }
-          tmem_st16(tdP + lane_addr + x * kHalfT + cc * 16, dk_);
+          dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
         }
       };
       if (kExtras || masked) body(std::true_type{});
       else body(std::false_type{});
+      tmem_st16(tdP + lane_addr + c0, dk_);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->pds_ready));
+      mbar_arrive(smem_u32(&sh->pds_ready[h]));
     }
 
     // ---- epilogue: dQ * softmax_scale; each group stores half of the head_dim columns -----
