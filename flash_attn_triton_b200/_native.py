@@ -11,7 +11,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
+# FA_B200_LIB selects another build of the same library (e.g. a variant made with FA_BUILD_TAG)
+LIB_PATH = os.environ.get("FA_B200_LIB") or os.path.join(_HERE, "libfa_b200.so")
 
 FA_F16, FA_BF16 = 0, 1
 IMPL_AUTO, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2

@@ -14,8 +14,11 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.path.join(HERE, "build")
-LIB = os.path.join(HERE, "libfa_b200.so")
+# FA_BUILD_TAG=<tag> builds an experimental variant (extra -D flags from FA_BUILD_DEFS) into
+# build_<tag>/ and libfa_b200_<tag>.so; load it by pointing FA_B200_LIB at that file.
+TAG = os.environ.get("FA_BUILD_TAG", "")
+OBJ = os.path.join(HERE, "build" + ("_" + TAG if TAG else ""))
+LIB = os.path.join(HERE, "libfa_b200" + ("_" + TAG if TAG else "") + ".so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
@@ -58,6 +61,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     defs = [f"-D{HAVE[s]}" for s in srcs if s in HAVE]
     if os.environ.get("FA_TRACE"):
         defs.append("-DFA_TRACE")
+    defs += os.environ.get("FA_BUILD_DEFS", "").split()
     rebuilt = False
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         for src, log, did in ex.map(lambda s: _compile(s, defs, force, verbose), srcs):

@@ -9,17 +9,28 @@
 //   bwd_dq_sm100_kernel    CTA = 128 query rows of one (batch, head); loops over key tiles:
 //                          S = Q K^T, dP = dO V^T, dS in place over dP, dQ += dS K.
 //
-// Roles in both kernels (384 threads):
+// Both kernels are software-pipelined through the ORDER in which the MMA warp feeds the (in-
+// order) tensor pipe, so that the element-wise warps always work while independent MMAs run:
+//
+//   dK/dV, per query tile i:   S(i+1) | dK += dS(i)^T Q(i) | dP(i+1) | dV += P(i+1)^T dO(i+1)
+//       exp phase  of tile i+1 (P = exp2(S - lse), stored over S) runs during dK(i), dP(i+1);
+//       dS  phase  of tile i+1 (dS = P (dP - delta), stored over dP) runs during dV(i+1), S(i+2).
+//       S(i+1) may overwrite P(i) and dP(i+1) may overwrite dS(i) because their last readers,
+//       dV(i) and dK(i), precede them in the pipe.
+//   dQ, per key tile k:        S(k+1) -> other S buffer | dQ += dS(k) K(k) | dP(k+1)
+//       S is double-buffered (P is no MMA operand here, nothing orders a single buffer).
+//
+// Roles (384 threads):
 //   warps 0-3 / 4-7  element-wise groups A / B: columns 0..63 / 64..127 of the 128 x 128
-//                    score tiles, one TMEM lane (row) per thread
-//   warp 8           TMA producer (resident tiles once, then a ring of streamed tile pairs)
-//   warp 9           MMA issuer (whole warp runs the control flow, one elected lane issues)
+//                    tiles, one TMEM lane (row) per thread
+//   warp 8           TMA producer (resident tiles once, then two rings of streamed tiles)
+//   warp 9           MMA issuer (uniform control flow, one elected lane issues)
 //   warp 10          loads the per-row statistics (base-2 LSE, delta) of the streamed query
 //                    tile into shared memory (dK/dV kernel only)
 //   warp 11          idle (completes the warpgroup for setmaxnreg)
 //
-// TMEM, dK/dV kernel: S^T | dP^T | dV | dK  (4 x 128 columns).
-// TMEM, dQ kernel:    S   | dP   | dQ       (3 x 128 columns).
+// TMEM, dK/dV kernel: S^T | dP^T | dV | dK     (4 x 128 columns).
+// TMEM, dQ kernel:    S[0] | S[1] | dP | dQ    (4 x 128 columns).
 // All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
 // K-major (contraction over head_dim) or MN-major (contraction over its rows) through
 // different descriptors.  Every mbarrier wait is bounded.
@@ -53,13 +64,19 @@ extern "C" int fa_debug_bwd_trace(long long* out) {
 namespace {
 
 constexpr int kT = 128;        // tile edge: rows of Q / keys of K,V per tile
-constexpr int kHalfT = 64;
+constexpr int kHalfT = 64;     // columns per element-wise group
 constexpr int kBwdThreads = 384;
+// Register re-balancing (setmaxnreg): the CTA starts with 168 registers per thread; the four
+// service warps drop to kRegsService and the eight element-wise warps grow to kRegsEw.
+// setmaxnreg.inc blocks until the registers exist, so the split has to satisfy
+// (kRegsEw - 168) * 256 <= (168 - kRegsService) * 128.
+constexpr int kRegsService = 88, kRegsEw = 208;
+static_assert((kRegsEw - 168) * 256 <= (168 - kRegsService) * 128, "register split");
 
 template <int D> struct BCfg {
   static constexpr int kTileBytes = kT * D * 2;
   static constexpr int kBoxes = D / 64;
-  static constexpr int kStages = (D == 128) ? 2 : 4;  // ring of streamed tile PAIRS
+  static constexpr int kStages = (D == 128) ? 2 : 4;  // depth of each streamed-tile ring
   static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
   static constexpr int kSmemBytes = kSmemTiles + 1024 + 8192;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -67,11 +84,15 @@ template <int D> struct BCfg {
 
 struct BShared {
   uint64_t res_full;      // resident tiles (K,V or Q,dO) landed
-  uint64_t full[4];       // streamed pair landed
-  uint64_t empty[4];      // streamed pair (and its statistics) consumed
+  uint64_t full_a[4];     // streamed tile A (Q in dK/dV, K in dQ) landed
+  uint64_t full_b[4];     // streamed tile B (dO in dK/dV, V in dQ) landed
+  uint64_t empty_a[4];    // last MMA reading tile A (and its statistics) finished
+  uint64_t empty_b[4];    // last MMA reading tile B finished
   uint64_t stat_full[4];  // statistics of the streamed query tile written (dK/dV kernel)
-  uint64_t s_full[2];     // [half] S and dP of that half computed
-  uint64_t pds_ready[2];  // [half] P and dS of that half written back (256 arrivals)
+  uint64_t s_full[2];     // S computed ([buffer] in the dQ kernel, [0] in the dK/dV kernel)
+  uint64_t dp_full;       // dP computed
+  uint64_t p_ready;       // P written back (256 arrivals; dK/dV kernel)
+  uint64_t ds_ready;      // dS written back (256 arrivals)
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -107,15 +128,16 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* tm, u
   for (int x = 0; x < D / 64; ++x) tma_load_4d(dst + x * (kT * 128), tm, bar, x * 64, head, row, batch);
 }
 
-// 128 x 128 x D product of two K-major tiles (contraction over head_dim): D/16 MMAs
+// 128 x 128 x D product of two K-major tiles (contraction over head_dim): D/16 MMAs.
+// Whole warp, uniform control flow; the lane with leader != 0 issues.
 template <int D>
 __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
-                                           uint32_t idesc) {
+                                           uint32_t idesc, uint32_t leader) {
+  const uint64_t da = make_smem_desc(a_smem, 16, 1024), db = make_smem_desc(b_smem, 16, 1024);
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
-    const uint32_t o = (kk / 4) * (kT * 128) + (kk % 4) * 32;
-    mma_f16_ss(d_tmem, make_smem_desc(a_smem + o, 16, 1024), make_smem_desc(b_smem + o, 16, 1024), idesc,
-               kk > 0);
+    const uint32_t o = ((kk / 4) * (kT * 128) + (kk % 4) * 32) >> 4;
+    mma_f16_ss_lp(d_tmem, da + o, db + o, idesc, kk > 0, leader);
   }
 }
 
@@ -124,40 +146,12 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_smem, uin
 // a_tmem and a_tmem + 64.
 template <int D>
 __device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
-                                              uint32_t idesc, bool accumulate) {
+                                              uint32_t idesc, bool accumulate, uint32_t leader) {
+  const uint64_t db = make_smem_desc(b_smem, kT * 128, 1024);
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
     const uint32_t a = a_tmem + (kk / 4) * 64 + (kk % 4) * 8;
-    mma_f16_ts(d_tmem, a, make_smem_desc(b_smem + kk * 2048, kT * 128, 1024), idesc,
-               (accumulate || kk > 0) ? 1u : 0u);
-  }
-}
-
-// Half-tile forms used by the pipelined loops: the streamed 128-row tile is consumed as two
-// 64-row halves, each with its own 64-column score buffers, so that the element-wise work on
-// one half overlaps the MMAs of the other.
-//
-// 128 x 64 x D product: A = resident K-major tile, B = rows [64h, 64h+64) of a K-major tile
-template <int D>
-__device__ __forceinline__ void mma_kmajor_half(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem,
-                                                int h, uint32_t idesc) {
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) {
-    const uint32_t o = (kk / 4) * (kT * 128) + (kk % 4) * 32;
-    mma_f16_ss(d_tmem, make_smem_desc(a_smem + o, 16, 1024),
-               make_smem_desc(b_smem + h * (kHalfT * 128) + o, 16, 1024), idesc, kk > 0);
-  }
-}
-// acc(128 x D) += A(128 x 64 fp16 pairs in TMEM) * B(rows [64h, 64h+64) of an MN-major tile).
-// A was written by the two element-wise groups as two 16-column blocks at a_tmem, a_tmem+32.
-template <int D>
-__device__ __forceinline__ void mma_from_tmem_half(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
-                                                   int h, uint32_t idesc, bool accumulate) {
-#pragma unroll
-  for (int kk = 0; kk < kHalfT / 16; ++kk) {
-    const uint32_t a = a_tmem + (kk / 2) * 32 + (kk % 2) * 8;
-    mma_f16_ts(d_tmem, a, make_smem_desc(b_smem + h * (kHalfT * 128) + kk * 2048, kT * 128, 1024), idesc,
-               (accumulate || kk > 0) ? 1u : 0u);
+    mma_f16_ts_lp(d_tmem, a, db + ((kk * 2048) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
   }
 }
 
@@ -176,7 +170,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
-  const uint32_t sK = smem_u32(tiles), sV = sK + C::kTileBytes, sRing = sV + C::kTileBytes;
+  const uint32_t sK = smem_u32(tiles), sV = sK + C::kTileBytes;
+  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStages * C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -195,14 +190,17 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&sh->s_full[i]), 1);
-      mbar_init(smem_u32(&sh->pds_ready[i]), 256);
-    }
+    mbar_init(smem_u32(&sh->s_full[0]), 1);
+    mbar_init(smem_u32(&sh->s_full[1]), 1);
+    mbar_init(smem_u32(&sh->dp_full), 1);
+    mbar_init(smem_u32(&sh->p_ready), 256);
+    mbar_init(smem_u32(&sh->ds_ready), 256);
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < C::kStages; ++i) {
-      mbar_init(smem_u32(&sh->full[i]), 1);
-      mbar_init(smem_u32(&sh->empty[i]), 1);
+      mbar_init(smem_u32(&sh->full_a[i]), 1);
+      mbar_init(smem_u32(&sh->full_b[i]), 1);
+      mbar_init(smem_u32(&sh->empty_a[i]), 1);
+      mbar_init(smem_u32(&sh->empty_b[i]), 1);
       mbar_init(smem_u32(&sh->stat_full[i]), 1);
     }
     sh->abort_flag = 0;
@@ -219,10 +217,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
 
   if (warp == 11) {
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
     if (lane == 0 && total > 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
@@ -238,24 +236,31 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-        if (!bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 41)) break;
-        const uint32_t bar = smem_u32(&sh->full[stage]);
-        mbar_expect_tx(bar, 2 * C::kTileBytes);
-        const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
-        load_tile<D>(dst, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
-        load_tile<D>(dst + C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        // dO's slot frees first (after dV of the tile that held it), Q's after dK
+        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
+        {
+          const uint32_t bar = smem_u32(&sh->full_b[stage]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        }
+        if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 41)) break;
+        {
+          const uint32_t bar = smem_u32(&sh->full_a[stage]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(sRingQ + stage * C::kTileBytes, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 10) {
     // ------------------------------- statistics loader ----------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
     int stage = 0;
     uint32_t phase = 0;
     for (int it = 0; it < total; ++it) {
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
       bool w = true;
-      if (lane == 0) w = bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 42);
+      if (lane == 0) w = bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 42);
       if (!__all_sync(0xffffffffu, w)) break;
       for (int i = lane; i < kT; i += 32) {
         const int row = m * kT + i;
@@ -276,102 +281,113 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
     if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kHalfT);
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
       constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+      const uint32_t leader = elect_one() ? 1u : 0u;
       bool ok = true;
-      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
-        bool w = true;
-        if (lane == 0) w = bwait(bar, parity, sh, code);
-        ok = __all_sync(0xffffffffu, w) && ok;
+      // every lane polls (uniform control flow, no vote needed: a completed phase is seen by all)
+      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+        if (ok) ok = bwait(bar, parity, sh, code);
         tc_fence_after();
       };
-      auto ring = [&](int it) { return sRing + (it % C::kStages) * 2 * C::kTileBytes; };
-      // S^T_h = K Q_h^T and dP^T_h = V dO_h^T for half-step g (iteration g/2, half g&1)
-      auto issue_scores = [&](int g) {
-        const int it = g >> 1, h = g & 1;
-        if (h == 0) wwait(&sh->full[it % C::kStages], (it / C::kStages) & 1, 44);
-        if (!ok) return;
-        const uint32_t sQ = ring(it), sdO = sQ + C::kTileBytes;
-        if (elect_one()) {
-          mma_kmajor_half<D>(tS + h * kHalfT, sK, sQ, h, idesc_s);
-          mma_kmajor_half<D>(tdP + h * kHalfT, sV, sdO, h, idesc_s);
-          mma_commit(smem_u32(&sh->s_full[h]));
-        }
-        __syncwarp();
-      };
-      wwait(&sh->res_full, 0, 43);
-      const int G2 = 2 * total;
-      if (ok) issue_scores(0);
-      if (ok) issue_scores(1);
-      for (int g = 0; g < G2 && ok; ++g) {
-        const int it = g >> 1, h = g & 1;
-        FA_BTRACE(2, g, 0);
-        wwait(&sh->pds_ready[h], it & 1, 45);
-        if (!ok) break;
-        FA_BTRACE(2, g, 1);
-        const uint32_t sQ = ring(it), sdO = sQ + C::kTileBytes;
-        if (elect_one()) {
-          mma_from_tmem_half<D>(tdV, tS + h * kHalfT, sdO, h, idesc_acc, g > 0);   // dV += P^T_h dO_h
-          mma_from_tmem_half<D>(tdK, tdP + h * kHalfT, sQ, h, idesc_acc, g > 0);   // dK += dS^T_h Q_h
-          if (h == 1) mma_commit(smem_u32(&sh->empty[it % C::kStages]));
-        }
-        __syncwarp();
-        FA_BTRACE(2, g, 2);
-        if (g + 2 < G2) issue_scores(g + 2);
-        FA_BTRACE(2, g, 3);
+      auto slotQ = [&](int it) { return sRingQ + (it % C::kStages) * C::kTileBytes; };
+      auto slotO = [&](int it) { return sRingO + (it % C::kStages) * C::kTileBytes; };
+      wq(&sh->res_full, 0, 43);
+      wq(&sh->full_a[0], 0, 44);
+      if (ok) {
+        mma_kmajor<D>(tS, sK, slotQ(0), idesc_s, leader);                      // S^T(0) = K Q(0)^T
+        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
       }
-      if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
+      wq(&sh->full_b[0], 0, 44);
+      if (ok) {
+        mma_kmajor<D>(tdP, sV, slotO(0), idesc_s, leader);                     // dP^T(0) = V dO(0)^T
+        mma_commit_lp(smem_u32(&sh->dp_full), leader);
+      }
+      wq(&sh->p_ready, 0, 45);
+      if (ok) {
+        mma_from_tmem<D>(tdV, tS, slotO(0), idesc_acc, false, leader);         // dV = P(0)^T dO(0)
+        mma_commit_lp(smem_u32(&sh->empty_b[0]), leader);
+      }
+      for (int i = 0; i < total && ok; ++i) {
+        const int st = i % C::kStages, st1 = (i + 1) % C::kStages;
+        const uint32_t ph1 = ((i + 1) / C::kStages) & 1;
+        const bool more = i + 1 < total;
+        FA_BTRACE(2, i, 0);
+        if (more) {
+          wq(&sh->full_a[st1], ph1, 44);
+          if (!ok) break;
+          mma_kmajor<D>(tS, sK, slotQ(i + 1), idesc_s, leader);                // S^T(i+1)
+          mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+        }
+        FA_BTRACE(2, i, 1);
+        wq(&sh->ds_ready, i & 1, 46);
+        if (!ok) break;
+        FA_BTRACE(2, i, 2);
+        mma_from_tmem<D>(tdK, tdP, slotQ(i), idesc_acc, i > 0, leader);        // dK += dS(i)^T Q(i)
+        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        FA_BTRACE(2, i, 3);
+        if (more) {
+          wq(&sh->full_b[st1], ph1, 44);
+          if (!ok) break;
+          mma_kmajor<D>(tdP, sV, slotO(i + 1), idesc_s, leader);               // dP^T(i+1)
+          mma_commit_lp(smem_u32(&sh->dp_full), leader);
+          FA_BTRACE(2, i, 4);
+          wq(&sh->p_ready, (i + 1) & 1, 45);
+          if (!ok) break;
+          FA_BTRACE(2, i, 5);
+          mma_from_tmem<D>(tdV, tS, slotO(i + 1), idesc_acc, true, leader);    // dV += P(i+1)^T dO(i+1)
+          mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
+          FA_BTRACE(2, i, 6);
+        }
+      }
+      mma_commit_lp(smem_u32(&sh->acc_done), leader);
       __syncwarp();
     }
   } else {
     // ------------------------------- element-wise groups --------------------------------
-    reg_alloc<224>();
+    reg_alloc<kRegsEw>();
     const int x = warp >> 2;                         // column half
     const int lrow = (warp & 3) * 32 + lane;         // TMEM lane = key inside the tile
     const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tSx = tS + lane_addr + x * kHalfT, tdPx = tdP + lane_addr + x * kHalfT;
     bool ok = true;
-    for (int g = 0; g < 2 * total && ok; ++g) {
-      const int it = g >> 1, h = g & 1;
+    for (int it = 0; it < total && ok; ++it) {
       const int stage = it % C::kStages;
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-      const int c0 = h * kHalfT + x * 32;            // first column (query row of the tile) of this thread
-      const int q0 = m * kT + c0;
+      const int q0 = m * kT + x * kHalfT;            // first query row of this thread's columns
       const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + hq] : 0.f;
       bool masked = false;
       if (cfg.causal) masked |= (n0 + kT - 1 > q0 + off);
-      if (cfg.wl >= 0) masked |= (n0 < q0 + 31 + off - cfg.wl);
+      if (cfg.wl >= 0) masked |= (n0 < q0 + kHalfT - 1 + off - cfg.wl);
       if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
 
-      if ((warp & 3) == 0) FA_BTRACE(x, g, 0);
-      ok = bwait(&sh->s_full[h], it & 1, sh, 46);
-      if (ok && h == 0) ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
+      ok = bwait(&sh->s_full[0], it & 1, sh, 46);
+      if (ok) ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
       if (!ok) break;
       tc_fence_after();
-      if ((warp & 3) == 0) FA_BTRACE(x, g, 1);
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_addr + c0, rs);
-      tmem_ld32(tdP + lane_addr + c0, rp);
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 1);
+
+      // ---- exp phase: P = exp2(score - lse), written back over S as T pairs -------------
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tSx, r0);
+      tmem_ld32(tSx + 32, r1);
       tmem_wait_ld();
-      if ((warp & 3) == 0) FA_BTRACE(x, g, 2);
-      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][c0]);
-      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][c0]);
-      uint32_t pk[16], dk_[16];
-      // kSlow: score pipeline extras and/or the mask have to be evaluated per element
-      auto body = [&](auto slow_tag) {
+      float pf[kHalfT];                              // P in fp32, kept for the dS phase
+      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
+      auto exp_body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 l4 = L4[i4], d4 = D4[i4];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], ds[4];
+        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
+          const float4 l4 = L4[i4];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = i4 * 4 + e;
-            const float sv = __uint_as_float(rs[i]);
-            const float dp = __uint_as_float(rp[i]);
+            const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
             if (kSlow) {
               const int qp = q0 + i + off;
               float th = 0.f;
@@ -380,34 +396,72 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               else sc = fmaf(sv, cfg.scale_log2, -lv[e]);
               float pe = ex2(sc);
               if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
-              float de = pe * (dp - dv[e]);
-              if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-              pv[e] = pe;
-              ds[e] = de;
+              pf[i] = pe;
+              // the tanh factor of the soft cap is folded into the copy kept for dS
+              if (kExtras && cfg.softcap > 0.f) {
+                if (i < 32) r0[i & 31] = __float_as_uint(1.f - th * th);
+                else r1[i & 31] = __float_as_uint(1.f - th * th);
+              }
             } else {
-              pv[e] = ex2(fmaf(sv, cfg.scale_log2, -lv[e]));
-              ds[e] = pv[e] * (dp - dv[e]);
+              pf[i] = ex2(fmaf(sv, cfg.scale_log2, -lv[e]));
             }
           }
-          pk[i4 * 2] = Elem<T>::pack(pv[0], pv[1]);
-          pk[i4 * 2 + 1] = Elem<T>::pack(pv[2], pv[3]);
-          dk_[i4 * 2] = Elem<T>::pack(ds[0], ds[1]);
-          dk_[i4 * 2 + 1] = Elem<T>::pack(ds[2], ds[3]);
         }
       };
-      if (kExtras || masked) body(std::true_type{});
-      else body(std::false_type{});
-      tmem_st16(tS + lane_addr + c0, pk);
-      tmem_st16(tdP + lane_addr + c0, dk_);
-      if ((warp & 3) == 0) FA_BTRACE(x, g, 3);
+      if (kExtras || masked) exp_body(std::true_type{});
+      else exp_body(std::false_type{});
+      {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
+          tmem_st16(tSx + c * 16, pk);
+        }
+      }
+      if (kExtras && cfg.softcap > 0.f) {
+#pragma unroll
+        for (int i = 0; i < kHalfT; ++i) pf[i] *= __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
+      }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->pds_ready[h]));
-      if ((warp & 3) == 0) FA_BTRACE(x, g, 4);
+      mbar_arrive(smem_u32(&sh->p_ready));
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
+
+      // ---- dS phase: dS = P (dP - delta), written back over dP ---------------------------
+      ok = bwait(&sh->dp_full, it & 1, sh, 48);
+      if (!ok) break;
+      tc_fence_after();
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
+      tmem_ld32(tdPx, r0);
+      tmem_ld32(tdPx + 32, r1);
+      tmem_wait_ld();
+      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 d4 = D4[c * 8 + i4];
+          const int i = c * 32 + i4 * 4;
+          const uint32_t* rr = c == 0 ? r0 : r1;
+          const float a0 = pf[i] * (__uint_as_float(rr[i4 * 4]) - d4.x);
+          const float a1 = pf[i + 1] * (__uint_as_float(rr[i4 * 4 + 1]) - d4.y);
+          const float a2 = pf[i + 2] * (__uint_as_float(rr[i4 * 4 + 2]) - d4.z);
+          const float a3 = pf[i + 3] * (__uint_as_float(rr[i4 * 4 + 3]) - d4.w);
+          pk[i4 * 2] = Elem<T>::pack(a0, a1);
+          pk[i4 * 2 + 1] = Elem<T>::pack(a2, a3);
+        }
+        tmem_st16(tdPx + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->ds_ready));
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
     }
 
     // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
-    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 48);
+    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 49);
     if (ok) {
       tc_fence_after();
       const uint32_t tsrc = (x == 0 ? tdV : tdK) + lane_addr;
@@ -459,7 +513,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
-  const uint32_t sQ = smem_u32(tiles), sdO = sQ + C::kTileBytes, sRing = sdO + C::kTileBytes;
+  const uint32_t sQ = smem_u32(tiles), sdO = sQ + C::kTileBytes;
+  const uint32_t sRingK = sdO + C::kTileBytes, sRingV = sRingK + C::kStages * C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -478,14 +533,17 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&sh->s_full[i]), 1);
-      mbar_init(smem_u32(&sh->pds_ready[i]), 256);
-    }
+    mbar_init(smem_u32(&sh->s_full[0]), 1);
+    mbar_init(smem_u32(&sh->s_full[1]), 1);
+    mbar_init(smem_u32(&sh->dp_full), 1);
+    mbar_init(smem_u32(&sh->p_ready), 256);
+    mbar_init(smem_u32(&sh->ds_ready), 256);
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < C::kStages; ++i) {
-      mbar_init(smem_u32(&sh->full[i]), 1);
-      mbar_init(smem_u32(&sh->empty[i]), 1);
+      mbar_init(smem_u32(&sh->full_a[i]), 1);
+      mbar_init(smem_u32(&sh->full_b[i]), 1);
+      mbar_init(smem_u32(&sh->empty_a[i]), 1);
+      mbar_init(smem_u32(&sh->empty_b[i]), 1);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -498,13 +556,13 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+  const uint32_t tS = tmem /* + buffer * 128 */, tdP = tmem + 256, tdQ = tmem + 384;
 
   if (warp >= 10) {
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
     if (lane == 0 && total > 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
@@ -519,68 +577,81 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       for (int j = 0; j < total; ++j) {
-        if (!bwait_relaxed(&sh->empty[stage], phase ^ 1, sh, 51)) break;
-        const uint32_t bar = smem_u32(&sh->full[stage]);
-        mbar_expect_tx(bar, 2 * C::kTileBytes);
-        const uint32_t dst = sRing + stage * 2 * C::kTileBytes;
-        load_tile<D>(dst, &tmK, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
-        load_tile<D>(dst + C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+        if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 51)) break;
+        {
+          const uint32_t bar = smem_u32(&sh->full_a[stage]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(sRingK + stage * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+        }
+        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 51)) break;
+        {
+          const uint32_t bar = smem_u32(&sh->full_b[stage]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(sRingV + stage * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<kRegsService>();
     if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kHalfT);
+      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
       constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+      const uint32_t leader = elect_one() ? 1u : 0u;
       bool ok = true;
-      auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
-        bool w = true;
-        if (lane == 0) w = bwait(bar, parity, sh, code);
-        ok = __all_sync(0xffffffffu, w) && ok;
+      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+        if (ok) ok = bwait(bar, parity, sh, code);
         tc_fence_after();
       };
-      auto ring = [&](int j) { return sRing + (j % C::kStages) * 2 * C::kTileBytes; };
-      // S_h = Q K_h^T and dP_h = dO V_h^T for half-step g (key tile g/2, half g&1)
-      auto issue_scores = [&](int g) {
-        const int j = g >> 1, h = g & 1;
-        if (h == 0) wwait(&sh->full[j % C::kStages], (j / C::kStages) & 1, 54);
-        if (!ok) return;
-        const uint32_t sKj = ring(j), sVj = sKj + C::kTileBytes;
-        if (elect_one()) {
-          mma_kmajor_half<D>(tS + h * kHalfT, sQ, sKj, h, idesc_s);
-          mma_kmajor_half<D>(tdP + h * kHalfT, sdO, sVj, h, idesc_s);
-          mma_commit(smem_u32(&sh->s_full[h]));
-        }
-        __syncwarp();
-      };
-      wwait(&sh->res_full, 0, 53);
-      const int G2 = 2 * total;
-      if (ok) issue_scores(0);
-      if (ok) issue_scores(1);
-      for (int g = 0; g < G2 && ok; ++g) {
-        const int j = g >> 1, h = g & 1;
-        wwait(&sh->pds_ready[h], j & 1, 55);
-        if (!ok) break;
-        if (elect_one()) {
-          mma_from_tmem_half<D>(tdQ, tdP + h * kHalfT, ring(j), h, idesc_acc, g > 0);   // dQ += dS_h K_h
-          if (h == 1) mma_commit(smem_u32(&sh->empty[j % C::kStages]));
-        }
-        __syncwarp();
-        if (g + 2 < G2) issue_scores(g + 2);
+      auto slotK = [&](int j) { return sRingK + (j % C::kStages) * C::kTileBytes; };
+      auto slotV = [&](int j) { return sRingV + (j % C::kStages) * C::kTileBytes; };
+      wq(&sh->res_full, 0, 53);
+      wq(&sh->full_a[0], 0, 54);
+      if (ok) {
+        mma_kmajor<D>(tS, sQ, slotK(0), idesc_s, leader);                      // S(0) = Q K(0)^T
+        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
       }
-      if (elect_one()) mma_commit(smem_u32(&sh->acc_done));
+      wq(&sh->full_b[0], 0, 54);
+      if (ok) {
+        mma_kmajor<D>(tdP, sdO, slotV(0), idesc_s, leader);                    // dP(0) = dO V(0)^T
+        mma_commit_lp(smem_u32(&sh->dp_full), leader);
+        mma_commit_lp(smem_u32(&sh->empty_b[0]), leader);
+      }
+      for (int k = 0; k < total && ok; ++k) {
+        const int st = k % C::kStages, st1 = (k + 1) % C::kStages;
+        const uint32_t ph1 = ((k + 1) / C::kStages) & 1;
+        const bool more = k + 1 < total;
+        if (more) {
+          wq(&sh->full_a[st1], ph1, 54);
+          if (!ok) break;
+          mma_kmajor<D>(tS + ((k + 1) & 1) * kT, sQ, slotK(k + 1), idesc_s, leader);   // S(k+1)
+          mma_commit_lp(smem_u32(&sh->s_full[(k + 1) & 1]), leader);
+        }
+        wq(&sh->ds_ready, k & 1, 55);
+        if (!ok) break;
+        mma_from_tmem<D>(tdQ, tdP, slotK(k), idesc_acc, k > 0, leader);        // dQ += dS(k) K(k)
+        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        if (more) {
+          wq(&sh->full_b[st1], ph1, 54);
+          if (!ok) break;
+          mma_kmajor<D>(tdP, sdO, slotV(k + 1), idesc_s, leader);              // dP(k+1)
+          mma_commit_lp(smem_u32(&sh->dp_full), leader);
+          mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
+        }
+      }
+      mma_commit_lp(smem_u32(&sh->acc_done), leader);
       __syncwarp();
     }
   } else {
     // ------------------------------- element-wise groups --------------------------------
-    reg_alloc<224>();
+    reg_alloc<kRegsEw>();
     const int x = warp >> 2;
     const int lrow = (warp & 3) * 32 + lane;  // TMEM lane = query row inside the tile
     const int row = m0 + lrow;
     const int qpos = row + off;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tdPx = tdP + lane_addr + x * kHalfT;
     const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + h] : 0.f;
     float l2 = INFINITY, dl = 0.f;
     if (row < si.q_len) {
@@ -591,56 +662,66 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (l2 == -INFINITY) l2 = INFINITY;
     }
     bool ok = true;
-    for (int g = 0; g < 2 * total && ok; ++g) {
-      const int j = g >> 1, h = g & 1;
-      const int c0 = h * kHalfT + x * 32;          // first column (key of the tile) of this thread
-      const int k0 = (n_lo + j) * kT + c0;
-      bool masked = (k0 + 32 > si.k_len);
-      if (cfg.causal) masked |= (k0 + 31 > m0 + off);
+    for (int j = 0; j < total && ok; ++j) {
+      const int k0 = (n_lo + j) * kT + x * kHalfT;   // first key of this thread's columns
+      bool masked = (k0 + kHalfT > si.k_len);
+      if (cfg.causal) masked |= (k0 + kHalfT - 1 > m0 + off);
       if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);
-      if (cfg.wr >= 0) masked |= (k0 + 31 > m0 + off + cfg.wr);
+      if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > m0 + off + cfg.wr);
 
-      ok = bwait(&sh->s_full[h], j & 1, sh, 56);
+      ok = bwait(&sh->s_full[j & 1], (j >> 1) & 1, sh, 56);
       if (!ok) break;
       tc_fence_after();
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_addr + c0, rs);
-      tmem_ld32(tdP + lane_addr + c0, rp);
+      uint32_t r0[32], r1[32];
+      const uint32_t tSx = tS + (j & 1) * kT + lane_addr + x * kHalfT;
+      tmem_ld32(tSx, r0);
+      tmem_ld32(tSx + 32, r1);
       tmem_wait_ld();
-      uint32_t dk_[16];
-      auto body = [&](auto slow_tag) {
+      // ---- exp phase: P (times the soft cap's tanh factor) in fp32 registers -------------
+      float pf[kHalfT];
+      auto exp_body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float ds2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float sv = __uint_as_float(rs[i + e]);
-            const float dp = __uint_as_float(rp[i + e]);
-            if (kSlow) {
-              const int col = k0 + i + e;
-              float th = 0.f;
-              float sc;
-              if (kExtras) sc = score_log2(cfg, slope, sv, qpos, col, th) - l2;
-              else sc = fmaf(sv, cfg.scale_log2, -l2);
-              float pe = ex2(sc);
-              if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
-              float de = pe * (dp - dl);
-              if (kExtras && cfg.softcap > 0.f) de *= (1.f - th * th);
-              ds2[e] = de;
-            } else {
-              ds2[e] = ex2(fmaf(sv, cfg.scale_log2, -l2)) * (dp - dl);
-            }
+        for (int i = 0; i < kHalfT; ++i) {
+          const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
+          if (kSlow) {
+            const int col = k0 + i;
+            float th = 0.f;
+            float sc;
+            if (kExtras) sc = score_log2(cfg, slope, sv, qpos, col, th) - l2;
+            else sc = fmaf(sv, cfg.scale_log2, -l2);
+            float pe = ex2(sc);
+            if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
+            if (kExtras && cfg.softcap > 0.f) pe *= (1.f - th * th);
+            pf[i] = pe;
+          } else {
+            pf[i] = ex2(fmaf(sv, cfg.scale_log2, -l2));
           }
-          dk_[i >> 1] = Elem<T>::pack(ds2[0], ds2[1]);
         }
       };
-      if (kExtras || masked) body(std::true_type{});
-      else body(std::false_type{});
-      tmem_st16(tdP + lane_addr + c0, dk_);
+      if (kExtras || masked) exp_body(std::true_type{});
+      else exp_body(std::false_type{});
+
+      // ---- dS phase --------------------------------------------------------------------
+      ok = bwait(&sh->dp_full, j & 1, sh, 57);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld32(tdPx, r0);
+      tmem_ld32(tdPx + 32, r1);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+        const uint32_t* rr = c == 0 ? r0 : r1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i] * (__uint_as_float(rr[2 * i]) - dl),
+                                pf[c * 32 + 2 * i + 1] * (__uint_as_float(rr[2 * i + 1]) - dl));
+        tmem_st16(tdPx + c * 16, pk);
+      }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->pds_ready[h]));
+      mbar_arrive(smem_u32(&sh->ds_ready));
     }
 
     // ---- epilogue: dQ * softmax_scale; each group stores half of the head_dim columns -----

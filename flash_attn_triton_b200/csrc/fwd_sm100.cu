@@ -85,25 +85,9 @@ struct Shared {
   alignas(16) float skt[2][kBN];
 };
 
-__device__ __forceinline__ bool wait_bar_slow(uint32_t a, uint32_t parity, Shared* sh, int code) {
-  const long long t0 = clock64();
-  for (uint32_t it = 0;; ++it) {
-    if (mbar_try_wait(a, parity)) return true;
-    if ((it & 255u) == 255u) {
-      if (sh->abort_flag) return false;
-      if (clock64() - t0 > 4000000000LL) {  // ~2 s
-        sh->abort_flag = code;
-        atomicExch(&g_fwd_sm100_status, code);
-        return false;
-      }
-    }
-  }
-}
 // Bounded wait on an mbarrier phase; the common "already complete" case costs one try_wait.
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Shared* sh, int code) {
-  const uint32_t a = smem_u32(bar);
-  if (mbar_try_wait(a, parity)) return true;
-  return wait_bar_slow(a, parity, sh, code);
+  return bounded_wait(bar, parity, &sh->abort_flag, &g_fwd_sm100_status, code);
 }
 
 template <typename T> struct Fmt;
@@ -224,6 +208,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = wait_bar(&sh->kv_empty[stage], phase ^ 1, sh, 11);
         if (!ok) return;
         const uint32_t bar = smem_u32(&sh->kv_full[stage]);
+#ifdef FA_ABL_NOTMA
+        if (phase != 0) {
+          mbar_arrive(bar);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          return;
+        }
+#endif
         if (codes) {  // int8 K tile: one box of 128-byte rows
           mbar_expect_tx(bar, kBN * D);
           tma_load_4d(sKV + stage * C::kTileBytes, tm, bar, 0, hk, krow0 + tile * kBN, kb);
@@ -359,6 +350,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 2);
 
       const bool prescaled = kExtras || masked || kInt8;
+#ifdef FA_ABL_NOSOFTMAX
+      {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = r[0][i] ^ r[1][i];
+        tmem_st16(tSx + buf * kBN, pk);
+        tmem_st16(tSx + buf * kBN + 16, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->p_ready[x][buf]));
+        continue;
+      }
+#endif
       if (kInt8) {
         // (float(acc) * (s_q * s_k)) * (softmax_scale * log2 e), in the reference's order.
         // |acc| <= 128*127*127 < 2^22, so int -> float is exact through the 1.5*2^23 bias

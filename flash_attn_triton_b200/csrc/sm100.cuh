@@ -58,9 +58,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
 }
 
 // Bounded wait used by the warp-specialised kernels: the already-complete case costs one
-// try_wait; otherwise spin, and every 256 polls look at the CTA's abort flag and at the clock.
-// After ~2 s the waiter raises the CTA's abort flag (so every other role of the CTA unwinds
-// at its next poll) and the device-wide status word, and returns false.
+// try_wait; otherwise spin, and every 256 polls look at the CTA's abort flag, at the device-wide
+// status word and at the clock.  After FA_WAIT_CLOCKS (~1 s) the waiter raises the CTA's abort
+// flag (so every other role of the CTA unwinds at its next poll) and the status word (so every
+// other CTA of this and of later launches gives up at once instead of waiting out its own
+// limit), and returns false.  The status word stays set until the process ends.
+#ifndef FA_WAIT_CLOCKS
+#define FA_WAIT_CLOCKS 2000000000LL
+#endif
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                              int* status, int code) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
@@ -70,9 +75,13 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
     if (mbar_try_wait(a, parity)) return true;
     if ((it & 255u) == 255u) {
       if (*cta_abort) return false;
-      if (clock64() - t0 > 4000000000LL) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) {
         *cta_abort = code;
-        atomicExch(status, code);
+        return false;
+      }
+      if (clock64() - t0 > FA_WAIT_CLOCKS) {
+        *cta_abort = code;
+        atomicCAS(status, 0, code);
         return false;
       }
     }
@@ -252,6 +261,44 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
                    bar)
                : "memory");
+}
+
+// Leader-predicated forms.  The whole warp executes these in uniform control flow and only the
+// lane with leader != 0 (chosen once with elect_one) issues: the operands stay warp-uniform,
+// which costs fewer issue cycles per MMA than branching around a single-lane block.
+__device__ __forceinline__ void mma_f16_ss_lp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_lp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                              uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.ne.b32 q, %5, 0;\n"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_lp(uint32_t bar, uint32_t leader) {
+  asm volatile(
+      "{\n"
+      ".reg .pred q;\n"
+      "setp.ne.b32 q, %1, 0;\n"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(bar),
+      "r"(leader)
+      : "memory");
 }
 
 // Register re-balancing between warpgroups (all 4 warps of the group execute it together).
