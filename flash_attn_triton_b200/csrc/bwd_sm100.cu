@@ -46,19 +46,48 @@ using namespace sm100;
 __device__ int g_bwd_sm100_status = 0;
 
 #ifdef FA_TRACE
-// Timeline of one CTA of the dK/dV kernel (blockIdx 0,0,0) for tuning: clock64 per role/step.
+#ifndef FA_TRACE_Y
+#define FA_TRACE_Y 0
+#define FA_TRACE_Z 0
+#endif
+// Timeline of one CTA (blockIdx.x 0) of the dK/dV kernel -- of the dQ kernel when FA_TRACE_DQ is
+// defined -- for tuning: clock64 per role/step.
 __device__ long long g_bwd_trace[3][32][8];
-#define FA_BTRACE(role, step, ev)                                                            \
+#define FA_TRACE_REC(role, step, ev)                                                          \
   do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (step) < 32 &&              \
-        (threadIdx.x & 31) == 0)                                                             \
+    if (blockIdx.x == 0 && blockIdx.y == FA_TRACE_Y && blockIdx.z == FA_TRACE_Z &&           \
+        (step) < 32 && (threadIdx.x & 31) == 0)                                              \
       g_bwd_trace[role][step][ev] = clock64();                                               \
   } while (0)
+// per-launch totals over all CTAs of the dK/dV kernel: [0] clock64 cycles, [1] tiles, [2] CTAs,
+// [3] globaltimer ns of the first start, [4] of the last end
+__device__ unsigned long long g_bwd_cta_stats[8];
+extern "C" int fa_debug_bwd_cta_stats(unsigned long long* out, int reset) {
+  int r = (int)cudaMemcpyFromSymbol(out, g_bwd_cta_stats, sizeof(unsigned long long) * 8);
+  if (reset) {
+    unsigned long long z[8] = {0, 0, 0, ~0ull, 0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_bwd_cta_stats, z, sizeof(z));
+  }
+  return r;
+}
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 extern "C" int fa_debug_bwd_trace(long long* out) {
   return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * 3 * 32 * 8);
 }
+#ifdef FA_TRACE_DQ
+#define FA_QTRACE(role, step, ev) FA_TRACE_REC(role, step, ev)
+#define FA_BTRACE(role, step, ev) do {} while (0)
+#else
+#define FA_QTRACE(role, step, ev) do {} while (0)
+#define FA_BTRACE(role, step, ev) FA_TRACE_REC(role, step, ev)
+#endif
 #else
 #define FA_BTRACE(role, step, ev) do {} while (0)
+#define FA_QTRACE(role, step, ev) do {} while (0)
 #endif
 
 namespace {
@@ -71,6 +100,11 @@ constexpr int kBwdThreads = 384;
 // setmaxnreg.inc blocks until the registers exist, so the split has to satisfy
 // (kRegsEw - 168) * 256 <= (168 - kRegsService) * 128.
 constexpr int kRegsService = 88, kRegsEw = 208;
+// Share of the exponentials of the unmasked fast path that run on the FMA pipe (every n-th).
+#ifndef FA_POLY_BWD
+#define FA_POLY_BWD 0
+#endif
+constexpr int kPolyEvery = FA_POLY_BWD;
 static_assert((kRegsEw - 168) * 256 <= (168 - kRegsService) * 128, "register split");
 
 template <int D> struct BCfg {
@@ -96,8 +130,8 @@ struct BShared {
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
-  alignas(16) float lse[4][kT];  // [stage][row of the streamed query tile]; read as float4
-  alignas(16) float delta[4][kT];
+  alignas(16) float lse[4][kT];  // [stage][row of the streamed query tile]: MINUS the base-2 LSE
+  alignas(16) float delta[4][kT];  //                                       MINUS delta
 };
 static_assert(sizeof(BShared) <= 8192, "BShared must fit its reserve");
 
@@ -187,6 +221,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const int m_hi = (max(qhi - off, 0) + kT - 1) / kT;
   const int ntiles = max(m_hi - m_lo, 0);
   const int total = ntiles * G;
+#ifdef FA_TRACE
+  const long long cta_c0 = clock64();
+  const unsigned long long cta_g0 = gtimer();
+#endif
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
@@ -238,12 +276,18 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
         // dO's slot frees first (after dV of the tile that held it), Q's after dK
         if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
+#ifdef FA_ABL_NOTMA
+        if (it >= C::kStages) mbar_arrive(smem_u32(&sh->full_b[stage])); else
+#endif
         {
           const uint32_t bar = smem_u32(&sh->full_b[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
           load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
         }
         if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 41)) break;
+#ifdef FA_ABL_NOTMA
+        if (it >= C::kStages) mbar_arrive(smem_u32(&sh->full_a[stage])); else
+#endif
         {
           const uint32_t bar = smem_u32(&sh->full_a[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
@@ -264,16 +308,17 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (!__all_sync(0xffffffffu, w)) break;
       for (int i = lane; i < kT; i += 32) {
         const int row = m * kT + i;
-        float l2 = INFINITY, dl = 0.f;
+        // stored NEGATED: the consumers add them with packed FMAs / adds
+        float nl2 = -INFINITY, ndl = 0.f;
         if (row < si.q_len) {
           const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
                               (int64_t)hq * p.lse_stride[2];
-          l2 = p.lse2[idx];
-          dl = p.delta[idx];
-          if (l2 == -INFINITY) l2 = INFINITY;  // row without visible keys: P = 0
+          nl2 = -p.lse2[idx];
+          ndl = -p.delta[idx];
+          if (nl2 == INFINITY) nl2 = -INFINITY;  // row without visible keys: P = 0
         }
-        sh->lse[stage][i] = l2;
-        sh->delta[stage][i] = dl;
+        sh->lse[stage][i] = nl2;
+        sh->delta[stage][i] = ndl;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->stat_full[stage]));
@@ -294,6 +339,18 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       };
       auto slotQ = [&](int it) { return sRingQ + (it % C::kStages) * C::kTileBytes; };
       auto slotO = [&](int it) { return sRingO + (it % C::kStages) * C::kTileBytes; };
+#ifdef FA_TRACE_SERIAL
+      // debug: wait for every MMA group right after issuing it and record how long it ran
+      uint32_t dbg_phase = 0;
+      auto drain = [&](int step, int ev) {
+        mma_commit_lp(smem_u32(&sh->s_full[1]), leader);
+        wq(&sh->s_full[1], dbg_phase, 99);
+        dbg_phase ^= 1;
+        FA_TRACE_REC(2, step, ev);
+      };
+#else
+      auto drain = [&](int, int) {};
+#endif
       wq(&sh->res_full, 0, 43);
       wq(&sh->full_a[0], 0, 44);
       if (ok) {
@@ -318,28 +375,51 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (more) {
           wq(&sh->full_a[st1], ph1, 44);
           if (!ok) break;
+          drain(i, 0);
           mma_kmajor<D>(tS, sK, slotQ(i + 1), idesc_s, leader);                // S^T(i+1)
           mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+          drain(i, 1);
         }
+#ifndef FA_TRACE_SERIAL
         FA_BTRACE(2, i, 1);
+#endif
         wq(&sh->ds_ready, i & 1, 46);
         if (!ok) break;
         FA_BTRACE(2, i, 2);
         mma_from_tmem<D>(tdK, tdP, slotQ(i), idesc_acc, i > 0, leader);        // dK += dS(i)^T Q(i)
         mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+#ifdef FA_TRACE_SERIAL
+        drain(i, 3);
+#else
         FA_BTRACE(2, i, 3);
+#endif
         if (more) {
           wq(&sh->full_b[st1], ph1, 44);
           if (!ok) break;
+#ifdef FA_TRACE_SERIAL
+          FA_TRACE_REC(2, i, 4);
+#endif
           mma_kmajor<D>(tdP, sV, slotO(i + 1), idesc_s, leader);               // dP^T(i+1)
           mma_commit_lp(smem_u32(&sh->dp_full), leader);
+#ifdef FA_TRACE_SERIAL
+          drain(i, 5);
+#else
           FA_BTRACE(2, i, 4);
+#endif
           wq(&sh->p_ready, (i + 1) & 1, 45);
           if (!ok) break;
+#ifdef FA_TRACE_SERIAL
+          FA_TRACE_REC(2, i, 6);
+#else
           FA_BTRACE(2, i, 5);
+#endif
           mma_from_tmem<D>(tdV, tS, slotO(i + 1), idesc_acc, true, leader);    // dV += P(i+1)^T dO(i+1)
           mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
+#ifdef FA_TRACE_SERIAL
+          drain(i, 7);
+#else
           FA_BTRACE(2, i, 6);
+#endif
         }
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
@@ -365,8 +445,21 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
 
       if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
+      // The statistics are fetched into registers BEFORE the wait for the scores: shared-memory
+      // loads issued while the tensor pipe streams its operands take hundreds of cycles, and
+      // here that latency hides behind the wait.
+      ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
+      if (!ok) break;
+      float st[kHalfT];                              // -lse, later -delta, of this thread's columns
+      {
+        const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
+#pragma unroll
+        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
+          const float4 l4 = L4[i4];
+          st[i4 * 4] = l4.x; st[i4 * 4 + 1] = l4.y; st[i4 * 4 + 2] = l4.z; st[i4 * 4 + 3] = l4.w;
+        }
+      }
       ok = bwait(&sh->s_full[0], it & 1, sh, 46);
-      if (ok) ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
       if (!ok) break;
       tc_fence_after();
       if ((warp & 3) == 0) FA_BTRACE(x, it, 1);
@@ -376,40 +469,40 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tmem_ld32(tSx, r0);
       tmem_ld32(tSx + 32, r1);
       tmem_wait_ld();
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
       float pf[kHalfT];                              // P in fp32, kept for the dS phase
-      const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
       auto exp_body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
+        if (kSlow) {
 #pragma unroll
-        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
-          const float4 l4 = L4[i4];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = i4 * 4 + e;
+          for (int i = 0; i < kHalfT; ++i) {
             const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
-            if (kSlow) {
-              const int qp = q0 + i + off;
-              float th = 0.f;
-              float sc;
-              if (kExtras) sc = score_log2(cfg, slope, sv, qp, key, th) - lv[e];
-              else sc = fmaf(sv, cfg.scale_log2, -lv[e]);
-              float pe = ex2(sc);
-              if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
-              pf[i] = pe;
-              // the tanh factor of the soft cap is folded into the copy kept for dS
-              if (kExtras && cfg.softcap > 0.f) {
-                if (i < 32) r0[i & 31] = __float_as_uint(1.f - th * th);
-                else r1[i & 31] = __float_as_uint(1.f - th * th);
-              }
-            } else {
-              pf[i] = ex2(fmaf(sv, cfg.scale_log2, -lv[e]));
-            }
+            const int qp = q0 + i + off;
+            float th = 0.f;
+            float sc;
+            if (kExtras) sc = score_log2(cfg, slope, sv, qp, key, th) + st[i];
+            else sc = fmaf(sv, cfg.scale_log2, st[i]);
+            float pe = ex2(sc);
+            if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
+            pf[i] = pe;
+            // the tanh factor of the soft cap is folded into the copy kept for dS
+            if (kExtras && cfg.softcap > 0.f) st[i] = 1.f - th * th;
+          }
+        } else {
+          const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2);
+#pragma unroll
+          for (int i = 0; i < kHalfT; i += 2) {
+            const uint32_t* rr = i < 32 ? r0 : r1;
+            const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2,
+                                   make_float2(st[i], st[i + 1]));
+            pf[i] = ex2_mixed<kPolyEvery>(a.x, i);
+            pf[i + 1] = ex2_mixed<kPolyEvery>(a.y, i + 1);
           }
         }
       };
       if (kExtras || masked) exp_body(std::true_type{});
       else exp_body(std::false_type{});
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
       {
         uint32_t pk[16];
 #pragma unroll
@@ -421,43 +514,47 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       if (kExtras && cfg.softcap > 0.f) {
 #pragma unroll
-        for (int i = 0; i < kHalfT; ++i) pf[i] *= __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
+        for (int i = 0; i < kHalfT; ++i) pf[i] *= st[i];
       }
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->p_ready));
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 5);
+      {
+        // delta replaces lse in the same registers, again ahead of the wait it hides behind
+        const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+#pragma unroll
+        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
+          const float4 d4 = D4[i4];
+          st[i4 * 4] = d4.x; st[i4 * 4 + 1] = d4.y; st[i4 * 4 + 2] = d4.z; st[i4 * 4 + 3] = d4.w;
+        }
+      }
 
       // ---- dS phase: dS = P (dP - delta), written back over dP ---------------------------
       ok = bwait(&sh->dp_full, it & 1, sh, 48);
       if (!ok) break;
       tc_fence_after();
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
-      tmem_ld32(tdPx, r0);
-      tmem_ld32(tdPx + 32, r1);
-      tmem_wait_ld();
-      const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 6);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        tmem_ld32(tdPx + c * 32, r0);
+        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const float4 d4 = D4[c * 8 + i4];
-          const int i = c * 32 + i4 * 4;
-          const uint32_t* rr = c == 0 ? r0 : r1;
-          const float a0 = pf[i] * (__uint_as_float(rr[i4 * 4]) - d4.x);
-          const float a1 = pf[i + 1] * (__uint_as_float(rr[i4 * 4 + 1]) - d4.y);
-          const float a2 = pf[i + 2] * (__uint_as_float(rr[i4 * 4 + 2]) - d4.z);
-          const float a3 = pf[i + 3] * (__uint_as_float(rr[i4 * 4 + 3]) - d4.w);
-          pk[i4 * 2] = Elem<T>::pack(a0, a1);
-          pk[i4 * 2 + 1] = Elem<T>::pack(a2, a3);
+        for (int i = 0; i < 16; ++i) {
+          const int e = c * 32 + 2 * i;
+          const float2 d = f2add(make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])),
+                                 make_float2(st[e], st[e + 1]));
+          const float2 ds = f2mul(make_float2(pf[e], pf[e + 1]), d);
+          pk[i] = Elem<T>::pack(ds.x, ds.y);
         }
         tmem_st16(tdPx + c * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->ds_ready));
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
+      if ((warp & 3) == 0) FA_BTRACE(x, it, 7);
     }
 
     // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
@@ -498,6 +595,15 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, 512);
+#ifdef FA_TRACE
+  if (tid == 0) {
+    atomicAdd(&g_bwd_cta_stats[0], (unsigned long long)(clock64() - cta_c0));
+    atomicAdd(&g_bwd_cta_stats[1], (unsigned long long)total);
+    atomicAdd(&g_bwd_cta_stats[2], 1ull);
+    atomicMin(&g_bwd_cta_stats[3], cta_g0);
+    atomicMax(&g_bwd_cta_stats[4], gtimer());
+  }
+#endif
 }
 
 // =======================================================================================
@@ -622,16 +728,20 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int st = k % C::kStages, st1 = (k + 1) % C::kStages;
         const uint32_t ph1 = ((k + 1) / C::kStages) & 1;
         const bool more = k + 1 < total;
+        FA_QTRACE(2, k, 0);
         if (more) {
           wq(&sh->full_a[st1], ph1, 54);
           if (!ok) break;
           mma_kmajor<D>(tS + ((k + 1) & 1) * kT, sQ, slotK(k + 1), idesc_s, leader);   // S(k+1)
           mma_commit_lp(smem_u32(&sh->s_full[(k + 1) & 1]), leader);
         }
+        FA_QTRACE(2, k, 1);
         wq(&sh->ds_ready, k & 1, 55);
         if (!ok) break;
+        FA_QTRACE(2, k, 2);
         mma_from_tmem<D>(tdQ, tdP, slotK(k), idesc_acc, k > 0, leader);        // dQ += dS(k) K(k)
         mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        FA_QTRACE(2, k, 3);
         if (more) {
           wq(&sh->full_b[st1], ph1, 54);
           if (!ok) break;
@@ -639,6 +749,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_commit_lp(smem_u32(&sh->dp_full), leader);
           mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
         }
+        FA_QTRACE(2, k, 4);
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
       __syncwarp();
@@ -669,14 +780,17 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);
       if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > m0 + off + cfg.wr);
 
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 0);
       ok = bwait(&sh->s_full[j & 1], (j >> 1) & 1, sh, 56);
       if (!ok) break;
       tc_fence_after();
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 1);
       uint32_t r0[32], r1[32];
       const uint32_t tSx = tS + (j & 1) * kT + lane_addr + x * kHalfT;
       tmem_ld32(tSx, r0);
       tmem_ld32(tSx + 32, r1);
       tmem_wait_ld();
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 2);
       // ---- exp phase: P (times the soft cap's tanh factor) in fp32 registers -------------
       float pf[kHalfT];
       auto exp_body = [&](auto slow_tag) {
@@ -695,33 +809,50 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (kExtras && cfg.softcap > 0.f) pe *= (1.f - th * th);
             pf[i] = pe;
           } else {
-            pf[i] = ex2(fmaf(sv, cfg.scale_log2, -l2));
+            pf[i] = ex2_mixed<kPolyEvery>(fmaf(sv, cfg.scale_log2, -l2), i);
           }
         }
       };
+      auto exp_fast = [&]() {
+        const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2), nl = make_float2(-l2, -l2);
+#pragma unroll
+        for (int i = 0; i < kHalfT; i += 2) {
+          const uint32_t* rr = i < 32 ? r0 : r1;
+          const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2, nl);
+          pf[i] = ex2_mixed<kPolyEvery>(a.x, i);
+          pf[i + 1] = ex2_mixed<kPolyEvery>(a.y, i + 1);
+        }
+      };
       if (kExtras || masked) exp_body(std::true_type{});
-      else exp_body(std::false_type{});
+      else exp_fast();
 
       // ---- dS phase --------------------------------------------------------------------
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 3);
       ok = bwait(&sh->dp_full, j & 1, sh, 57);
       if (!ok) break;
       tc_fence_after();
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 4);
       tmem_ld32(tdPx, r0);
       tmem_ld32(tdPx + 32, r1);
       tmem_wait_ld();
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 5);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
         const uint32_t* rr = c == 0 ? r0 : r1;
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i] * (__uint_as_float(rr[2 * i]) - dl),
-                                pf[c * 32 + 2 * i + 1] * (__uint_as_float(rr[2 * i + 1]) - dl));
+        for (int i = 0; i < 16; ++i) {
+          const float2 d = f2add(make_float2(__uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1])),
+                                 make_float2(-dl, -dl));
+          const float2 ds = f2mul(make_float2(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]), d);
+          pk[i] = Elem<T>::pack(ds.x, ds.y);
+        }
         tmem_st16(tdPx + c * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->ds_ready));
+      if ((warp & 3) == 0) FA_QTRACE(x, j, 6);
     }
 
     // ---- epilogue: dQ * softmax_scale; each group stores half of the head_dim columns -----

@@ -62,6 +62,59 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Packed fp32 pairs (one issue slot for two results) and the three-input maximum of sm_100.
+// The element-wise warps of the tcgen05 kernels are short of issue slots, not of FP32 lanes.
+__device__ __forceinline__ uint64_t f2_pack(float x, float y) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+  return r;
+}
+__device__ __forceinline__ float2 f2_unpack(uint64_t r) {
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(r));
+  return d;
+}
+__device__ __forceinline__ float2 f2fma(float2 a, float2 b, float2 c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(f2_pack(a.x, a.y)), "l"(f2_pack(b.x, b.y)), "l"(f2_pack(c.x, c.y)));
+  return f2_unpack(d);
+}
+__device__ __forceinline__ float2 f2add(float2 a, float2 b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_pack(a.x, a.y)), "l"(f2_pack(b.x, b.y)));
+  return f2_unpack(d);
+}
+__device__ __forceinline__ float2 f2mul(float2 a, float2 b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_pack(a.x, a.y)), "l"(f2_pack(b.x, b.y)));
+  return f2_unpack(d);
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x on the FMA pipe instead of the special-function unit (which is the scarcer resource next
+// to the tensor cores: 16 results per clock per SM): round-to-nearest split x = n + f with
+// f in [-0.5, 0.5], a degree-3 minimax polynomial for 2^f (relative error 1.0e-4, below the
+// rounding of the 16-bit probabilities it feeds), n added into the exponent field.
+// Arguments below -125 return 2^-125 rather than 0, so masked (-inf) scores must not come here.
+__device__ __forceinline__ float ex2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.05500862f, f, 0.24221021f);
+  p = fmaf(p, f, 0.6932829f);
+  p = fmaf(p, f, 1.f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// Every kEvery-th exponential of an unrolled loop (index i) goes to ex2_fma (0 = none).
+template <int kEvery> __device__ __forceinline__ float ex2_mixed(float x, int i) {
+  if (kEvery > 0 && (i % (kEvery > 0 ? kEvery : 1)) == (kEvery > 0 ? kEvery : 1) - 1) return ex2_fma(x);
+  return ex2(x);
+}
+
 // tanh through one exp2: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.
 __device__ __forceinline__ float fast_tanh(float x) {
   float e = exp2f(x * (2.f * FA_LOG2E));

@@ -2,21 +2,24 @@
 // accumulators in tensor memory, warp-specialised online softmax.
 //
 // One CTA owns 128 query rows of one (batch, head).  Keys arrive in tiles of 128; the score
-// tile S = Q K^T (128 x 128, one N=128 MMA chain) is DOUBLE-BUFFERED in tensor memory, so
-// the tensor pipe computes S(j+1) while the softmax warps are still working on S(j).
-// The two column halves of every score tile are two independent online-softmax streams,
-// each owned by one warpgroup with its own running maximum, row sum and output accumulator
-// (like a 2-way split over keys, merged in the epilogue):
+// tile S = Q K^T (128 x 128, one N=128 MMA chain) is DOUBLE-BUFFERED in tensor memory.  The
+// key tiles are dealt alternately to two softmax warpgroups ("streams"): stream A takes the
+// even tiles and score buffer S[0], stream B the odd tiles and S[1].  Each stream is an
+// independent online softmax over its own keys (own running maximum, row sum and output
+// accumulator, like a 2-way split over keys, merged in the epilogue), so the two groups run
+// half a step out of phase: while one is in its exp2 (MUFU) phase the other waits, loads or
+// reduces, and the tensor pipe always has the other stream's P V and Q K^T to run:
 //
-//   warps 0-3   softmax group A : columns   0..63 of every score tile, accumulator O_a
-//   warps 4-7   softmax group B : columns 64..127 of every score tile, accumulator O_b
+//   warps 0-3   softmax group A : key tiles 0, 2, 4, ... (S[0], accumulator O_a)
+//   warps 4-7   softmax group B : key tiles 1, 3, 5, ... (S[1], accumulator O_b)
 //   warp  8     TMA producer    : Q once, then K/V tiles through a ring
-//   warp  9     MMA issuer      : S = Q K^T (SS);  O_x += P_x V[x-half] (A = P_x from TMEM)
+//   warp  9     MMA issuer      : S[x] = Q K_j^T (SS);  O_x += P_j V_j (A = P_j from TMEM)
 //   warps 10-11 idle; they complete the third warpgroup so that it can hand its registers
 //               to the softmax groups (setmaxnreg)
 //
-// One thread owns one query row of its stream (TMEM lane = row).  P (fp16/bf16) overwrites
-// the first 32 columns of its half of S.  The running maximum is only raised when it grows
+// One thread owns one query row (TMEM lane = row) and all 128 scores of a tile.  P (fp16/bf16)
+// overwrites the first 64 columns of its S buffer; Q K_{j+2}^T may overwrite it because P_j V_j
+// precedes it in the in-order tensor pipe.  The running maximum is only raised when it grows
 // by more than 2^8 ("lazy rescale"), so O is rarely touched by the softmax warps; exactness
 // is kept because O and the row sum of a stream always share the same reference maximum.
 //
@@ -55,9 +58,14 @@ namespace {
 
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 128;          // keys per K/V tile
-constexpr int kHalf = 64;         // keys per softmax stream and tile
 constexpr int kThreads = 384;     // 8 softmax warps + a warpgroup holding producer and MMA warps
 constexpr float kRescaleThreshold = 8.0f;
+// Share of the exponentials of the unmasked fast path that run on the FMA pipe (every n-th;
+// 0 = none: measured slower here, the softmax warps are short of issue slots, not of MUFU).
+#ifndef FA_POLY_FWD
+#define FA_POLY_FWD 0
+#endif
+constexpr int kPolyEvery = FA_POLY_FWD;
 constexpr int kMaxStages = 8;
 
 template <int D> struct Cfg {
@@ -73,15 +81,15 @@ struct Shared {
   uint64_t q_full;
   uint64_t kv_full[kMaxStages];
   uint64_t kv_empty[kMaxStages];
-  uint64_t s_full[2];      // [score buffer]
-  uint64_t p_ready[2][2];  // [stream][score buffer]
-  uint64_t o_ready[2][2];  // [stream][parity of the PV index]: see the note at the waits
+  uint64_t s_full[2];      // [stream]: its score tile computed
+  uint64_t p_ready[2];     // [stream]: P written back (128 arrivals)
+  uint64_t o_ready[2];     // [stream]: its latest P V finished
   uint32_t tmem_base;
   volatile int abort_flag;
   float2 ml[2][kBM];       // epilogue exchange: (reference max, row sum) of each stream
   // INT8 variant: key scales of the current score tiles, staged by warp 10
   uint64_t sk_full[2];     // [score buffer] scales written
-  uint64_t sk_empty[2];    // [score buffer] scales consumed (256 arrivals)
+  uint64_t sk_empty[2];    // [score buffer] scales consumed (128 arrivals)
   alignas(16) float skt[2][kBN];
 };
 
@@ -136,10 +144,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(smem_u32(&sh->q_full), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sh->s_full[i]), 1);
-      for (int k = 0; k < 2; ++k) {
-        mbar_init(smem_u32(&sh->o_ready[i][k]), 1);
-        mbar_init(smem_u32(&sh->p_ready[i][k]), 128);
-      }
+      mbar_init(smem_u32(&sh->o_ready[i]), 1);
+      mbar_init(smem_u32(&sh->p_ready[i]), 128);
     }
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(smem_u32(&sh->kv_full[i]), 1);
@@ -147,7 +153,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sh->sk_full[i]), 1);
-      mbar_init(smem_u32(&sh->sk_empty[i]), 256);
+      mbar_init(smem_u32(&sh->sk_empty[i]), 128);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -236,88 +242,83 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
-    // The whole warp runs the control flow (so it stays warp-uniform and cheap); one elected
-    // lane issues the MMAs and commits.
+    // The whole warp runs the control flow in lock step and every lane polls the barriers;
+    // the lane chosen once by elect_one issues the MMAs and commits.
     reg_dealloc<56>();
     if (nsteps > 0) {
       constexpr uint32_t idesc_qk = make_idesc(1, Fmt<T>::code, 0, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(1, Fmt<T>::code, 0, 1, kBM, D);
+      const uint32_t leader = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       auto wwait = [&](uint64_t* bar, uint32_t parity, int code) {
-        bool w = true;
-        if (lane == 0) w = wait_bar(bar, parity, sh, code);
-        ok = __all_sync(0xffffffffu, w) && ok;
+        if (ok) ok = wait_bar(bar, parity, sh, code);
         tc_fence_after();
       };
       auto advance = [&]() { if (++stage == C::kStages) { stage = 0; phase ^= 1; } };
-      auto issue_qk = [&](int buf) {
+      const uint64_t dq = make_smem_desc(sQ, 16, 1024);
+      auto issue_qk = [&](int x) {
         wwait(&sh->kv_full[stage], phase, 22);
         if (!ok) return;
         const uint32_t kbase = sKV + stage * C::kTileBytes;
-        if (elect_one()) {
-          if (kInt8) {
-            constexpr uint32_t idesc_i8 = make_idesc(2, 1, 0, 0, kBM, kBN);  // s32 <- s8 x s8
+        const uint64_t dk = make_smem_desc(kbase, 16, 1024);
+        if (kInt8) {
+          constexpr uint32_t idesc_i8 = make_idesc(2, 1, 0, 0, kBM, kBN);  // s32 <- s8 x s8
+          if (leader) {
 #pragma unroll
             for (int kk = 0; kk < D / 32; ++kk)
-              mma_i8_ss(tmem + buf * kBN, make_smem_desc(sQ + kk * 32, 16, 1024),
-                        make_smem_desc(kbase + kk * 32, 16, 1024), idesc_i8, kk > 0);
-          } else {
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t o = (kk / 4) * (kBM * 128) + (kk % 4) * 32;
-              mma_f16_ss(tmem + buf * kBN, make_smem_desc(sQ + o, 16, 1024),
-                         make_smem_desc(kbase + o, 16, 1024), idesc_qk, kk > 0);
-            }
+              mma_i8_ss(tmem + x * kBN, dq + ((kk * 32) >> 4), dk + ((kk * 32) >> 4), idesc_i8, kk > 0);
           }
-          mma_commit(smem_u32(&sh->s_full[buf]));
-          mma_commit(smem_u32(&sh->kv_empty[stage]));
+          __syncwarp();
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t o = ((kk / 4) * (kBM * 128) + (kk % 4) * 32) >> 4;
+            mma_f16_ss_lp(tmem + x * kBN, dq + o, dk + o, idesc_qk, kk > 0, leader);
+          }
         }
-        __syncwarp();
+        mma_commit_lp(smem_u32(&sh->s_full[x]), leader);
+        mma_commit_lp(smem_u32(&sh->kv_empty[stage]), leader);
         advance();
       };
       wwait(&sh->q_full, 0, 21);
       if (ok) issue_qk(0);
       if (ok && nsteps > 1) issue_qk(1);
       for (int j = 0; j < nsteps && ok; ++j) {
-        const int buf = j & 1;
+        const int x = j & 1;
         FA_TRACE_EV(2, j, 0);
         wwait(&sh->kv_full[stage], phase, 24);
         const uint32_t vbase = sKV + stage * C::kTileBytes;
         FA_TRACE_EV(2, j, 1);
-        for (int x = 0; x < 2 && ok; ++x) {
-          wwait(&sh->p_ready[x][buf], (j >> 1) & 1, 25 + x);
-          if (!ok) break;
-          FA_TRACE_EV(2, j, 2 + x);
-          if (elect_one()) {
-            const uint32_t a = tmem + buf * kBN + x * kHalf;
-#pragma unroll
-            for (int kk = 0; kk < kHalf / 16; ++kk)
-              mma_f16_ts(tmem + 256 + x * 128, a + kk * 8,
-                         make_smem_desc(vbase + x * (kHalf * 128) + kk * 2048, kBN * 128, 1024), idesc_pv,
-                         (j > 0 || kk > 0) ? 1u : 0u);
-            mma_commit(smem_u32(&sh->o_ready[x][j & 1]));
-            if (x == 1) mma_commit(smem_u32(&sh->kv_empty[stage]));
-          }
-          __syncwarp();
-        }
+        wwait(&sh->p_ready[x], (j >> 1) & 1, 25 + x);
         if (!ok) break;
+        FA_TRACE_EV(2, j, 2);
+        {
+          const uint32_t a = tmem + x * kBN;
+          const uint64_t dv = make_smem_desc(vbase, kBN * 128, 1024);
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk)
+            mma_f16_ts_lp(tmem + 256 + x * 128, a + kk * 8, dv + ((kk * 2048) >> 4), idesc_pv,
+                          (j >= 2 || kk > 0) ? 1u : 0u, leader);
+          mma_commit_lp(smem_u32(&sh->o_ready[x]), leader);
+          mma_commit_lp(smem_u32(&sh->kv_empty[stage]), leader);
+        }
         advance();
         FA_TRACE_EV(2, j, 4);
-        if (j + 2 < nsteps) issue_qk(buf);
+        if (j + 2 < nsteps) issue_qk(x);
         FA_TRACE_EV(2, j, 5);
       }
     }
   } else {
     // ------------------------------- softmax groups -------------------------------------
     reg_alloc<224>();
-    const int x = warp >> 2;                         // stream: column half of every score tile
+    const int x = warp >> 2;                         // stream: key tiles j with (j & 1) == x
     const int row_in_tile = (warp & 3) * 32 + lane;  // TMEM lane
     const int row = m0 + row_in_tile;                // query row inside the sequence
     const int qpos = row + off;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tSx = tmem + lane_addr + x * kHalf;       // + buf * 128
+    const uint32_t tSx = tmem + lane_addr + x * kBN;
     const uint32_t tOx = tmem + lane_addr + 256 + x * 128;
     const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + h] : 0.f;
     float m_used = -INFINITY, l = 0.f;
@@ -328,50 +329,37 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
     const float qk_scale = cfg.scale * 1.44269504f;
 
-    for (int j = 0; j < nsteps && ok; ++j) {
-      const int buf = j & 1;
-      const int k0 = (n_lo + j) * kBN + x * kHalf;
-      bool masked = (k0 + kHalf > si.k_len);
-      if (cfg.causal) masked |= (k0 + kHalf - 1 > tq_min);
+    for (int j = x; j < nsteps && ok; j += 2) {
+      const int t = j >> 1;                          // index of the tile inside this stream
+      const int k0 = (n_lo + j) * kBN;
+      bool masked = (k0 + kBN > si.k_len);
+      if (cfg.causal) masked |= (k0 + kBN - 1 > tq_min);
       if (cfg.wl >= 0) masked |= (k0 < tq_max - cfg.wl);
-      if (cfg.wr >= 0) masked |= (k0 + kHalf - 1 > tq_min + cfg.wr);
+      if (cfg.wr >= 0) masked |= (k0 + kBN - 1 > tq_min + cfg.wr);
 
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 0);
-      ok = wait_bar(&sh->s_full[buf], (j >> 1) & 1, sh, 31 + x);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 0);
+      ok = wait_bar(&sh->s_full[x], t & 1, sh, 31 + x);
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 1);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 1);
 
-      // ---- the 64 scores of this row and stream into registers --------------------------
-      uint32_t r[2][32];
-      tmem_ld32(tSx + buf * kBN, r[0]);
-      tmem_ld32(tSx + buf * kBN + 32, r[1]);
+      // ---- the 128 scores of this row into registers -------------------------------------
+      uint32_t r[4][32];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32(tSx + cc * 32, r[cc]);
       tmem_wait_ld();
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 2);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 2);
 
       const bool prescaled = kExtras || masked || kInt8;
-#ifdef FA_ABL_NOSOFTMAX
-      {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = r[0][i] ^ r[1][i];
-        tmem_st16(tSx + buf * kBN, pk);
-        tmem_st16(tSx + buf * kBN + 16, pk);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&sh->p_ready[x][buf]));
-        continue;
-      }
-#endif
       if (kInt8) {
         // (float(acc) * (s_q * s_k)) * (softmax_scale * log2 e), in the reference's order.
         // |acc| <= 128*127*127 < 2^22, so int -> float is exact through the 1.5*2^23 bias
         // (an integer add and a float subtract instead of a quarter-rate I2F).
-        ok = wait_bar(&sh->sk_full[buf], (j >> 1) & 1, sh, 37 + x);
+        ok = wait_bar(&sh->sk_full[x], t & 1, sh, 37 + x);
         if (!ok) break;
-        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[buf][x * kHalf]);
+        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[x][0]);
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
           for (int i4 = 0; i4 < 8; ++i4) {
             const float4 s4 = S4[cc * 8 + i4];
@@ -386,11 +374,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         }
-        mbar_arrive(smem_u32(&sh->sk_empty[buf]));
+        mbar_arrive(smem_u32(&sh->sk_empty[x]));
       } else if (prescaled) {
         // score pipeline and mask applied once, in place; values end up in the log2 domain
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float v = __uint_as_float(r[cc][i]);
@@ -407,29 +395,37 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
 
-      // ---- row maximum: balanced tree (depth 6) ------------------------------------------
-      float mt[32];
+      // ---- row maximum: eight chains of three-input maxima --------------------------------
+      float mx;
+      {
+        float mt[8];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mt[i] = fmaxf(__uint_as_float(r[0][i]), __uint_as_float(r[1][i]));
+        for (int i = 0; i < 8; ++i)
+          mt[i] = fmax3(__uint_as_float(r[0][i]), __uint_as_float(r[0][8 + i]), __uint_as_float(r[0][16 + i]));
 #pragma unroll
-      for (int w = 16; w >= 1; w >>= 1) {
+        for (int i = 0; i < 8; ++i) mt[i] = fmaxf(mt[i], __uint_as_float(r[0][24 + i]));
 #pragma unroll
-        for (int i = 0; i < w; ++i) mt[i] = fmaxf(mt[i], mt[i + w]);
+        for (int cc = 1; cc < 4; ++cc) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            mt[i] = fmax3(mt[i], __uint_as_float(r[cc][i]), __uint_as_float(r[cc][8 + i]));
+            mt[i] = fmax3(mt[i], __uint_as_float(r[cc][16 + i]), __uint_as_float(r[cc][24 + i]));
+          }
+        }
+        mx = fmaxf(fmax3(mt[0], mt[1], mt[2]), fmaxf(fmax3(mt[3], mt[4], mt[5]), fmaxf(mt[6], mt[7])));
       }
-      float mx = mt[0];
       if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
 
       // ---- lazy rescale ----------------------------------------------------------------
-      if (j == 0) {
+      if (t == 0) {
         m_used = mx;
       } else {
         const bool need = mx > m_used + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          // PV number j-1 of this stream.  A parity wait cannot tell "k completions" from
-          // "k+2", and only PV j-3 is known to be complete here (QK j-1 was queued behind
-          // it), so PVs alternate between two barriers: on barrier (j-1)&1 at most one
-          // phase is open.
-          ok = wait_bar(&sh->o_ready[x][(j - 1) & 1], ((j - 1) >> 1) & 1, sh, 33 + x);
+          // The previous P V of this stream (tile j-2) is its (t-1)-th; the one of tile j
+          // cannot complete before P_j is written below, so the barrier is at most one
+          // phase ahead of the parity waited for here.
+          ok = wait_bar(&sh->o_ready[x], (t - 1) & 1, sh, 33 + x);
           if (!ok) break;
           tc_fence_after();
           const float alpha = need ? exp2f(m_used - mx) : 1.f;  // m_used = -inf -> 0
@@ -451,41 +447,59 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       const float mul = prescaled ? 1.f : cfg.scale_log2;
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 3);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 3);
 
-      // ---- P = exp2(s - m), row sum (four chains), P -> TMEM in place over S -------------
+      // ---- P = exp2(s - m), row sum, P -> TMEM in place over S ----------------------------
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      if (kInt8) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t pk[16];
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[cc][i]), mul, -m_safe));
-          const float p1 = ex2(fmaf(__uint_as_float(r[cc][i + 1]), mul, -m_safe));
-          pk[i >> 1] = Elem<T>::pack(p0, p1);
-          if (kInt8) {
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2(__uint_as_float(r[cc][i]) - m_safe);
+            const float p1 = ex2(__uint_as_float(r[cc][i + 1]) - m_safe);
+            pk[i >> 1] = Elem<T>::pack(p0, p1);
             // Outlier keys make the rows peaky; with a stale reference maximum the dominant
             // probability is 2^x instead of exactly 1, so its rounding to T would not cancel
             // in O / l unless l sums the ROUNDED values that enter P@V.
             const float2 pr = Elem<T>::unpack(pk[i >> 1]);
             ps[(i >> 1) & 3] += pr.x + pr.y;
-          } else {
-            ps[(i >> 1) & 3] += p0 + p1;
           }
+          tmem_st16(tSx + cc * 16, pk);
         }
-        tmem_st16(tSx + buf * kBN + cc * 16, pk);
+      } else {
+        // packed pairs: one FMA, two exponentials, one conversion and one add per two scores
+        const float2 mul2 = make_float2(mul, mul), nm2 = make_float2(-m_safe, -m_safe);
+        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 a = f2fma(make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), mul2, nm2);
+            // the unmasked fast path holds no -inf scores: part of its exponentials may run on the FMA pipe
+            float2 pe;
+            pe.x = prescaled ? ex2(a.x) : ex2_mixed<kPolyEvery>(a.x, i);
+            pe.y = prescaled ? ex2(a.y) : ex2_mixed<kPolyEvery>(a.y, i + 1);
+            pk[i >> 1] = Elem<T>::pack(pe.x, pe.y);
+            acc2[(i >> 1) & 1] = f2add(acc2[(i >> 1) & 1], pe);
+          }
+          tmem_st16(tSx + cc * 16, pk);
+        }
+        ps[0] = acc2[0].x; ps[1] = acc2[0].y; ps[2] = acc2[1].x; ps[3] = acc2[1].y;
       }
       l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 4);
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 4);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->p_ready[x][buf]));
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, j, 5);
+      mbar_arrive(smem_u32(&sh->p_ready[x]));
+      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 5);
     }
 
     // ---- epilogue: merge the two streams, O / l -> global, base-2 LSE ---------------------
-    if (ok && nsteps > 0)
-      ok = wait_bar(&sh->o_ready[x][(nsteps - 1) & 1], ((nsteps - 1) >> 1) & 1, sh, 35 + x);
+    const int my_tiles = (nsteps - x + 1) >> 1;      // tiles of this stream (0 if nsteps <= x)
+    if (ok && my_tiles > 0) ok = wait_bar(&sh->o_ready[x], (my_tiles - 1) & 1, sh, 35 + x);
     sh->ml[x][row_in_tile] = make_float2(m_used, l);
     tc_fence_before();
     asm volatile("bar.sync 1, 256;\n" ::: "memory");  // the two softmax groups only
@@ -506,14 +520,18 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t tOa = tmem + lane_addr + 256 + x * DH, tOb = tOa + 128;
 #pragma unroll
       for (int cc = 0; cc < DH / 32; ++cc) {
+        // a stream without tiles never wrote its accumulator
         uint32_t ra[32], rb[32];
-        if (nsteps > 0) {
-          tmem_ld32(tOa + cc * 32, ra);
-          tmem_ld32(tOb + cc * 32, rb);
-          tmem_wait_ld();
-        } else {
+        if (nsteps > 0) tmem_ld32(tOa + cc * 32, ra);
+        if (nsteps > 1) tmem_ld32(tOb + cc * 32, rb);
+        tmem_wait_ld();
+        if (nsteps <= 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ra[i] = rb[i] = 0u;
+          for (int i = 0; i < 32; ++i) ra[i] = 0u;
+        }
+        if (nsteps <= 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rb[i] = 0u;
         }
         if (row_ok) {
 #pragma unroll
