@@ -276,18 +276,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
         // dO's slot frees first (after dV of the tile that held it), Q's after dK
         if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
-#ifdef FA_ABL_NOTMA
-        if (it >= C::kStages) mbar_arrive(smem_u32(&sh->full_b[stage])); else
-#endif
         {
           const uint32_t bar = smem_u32(&sh->full_b[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
           load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
         }
         if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 41)) break;
-#ifdef FA_ABL_NOTMA
-        if (it >= C::kStages) mbar_arrive(smem_u32(&sh->full_a[stage])); else
-#endif
         {
           const uint32_t bar = smem_u32(&sh->full_a[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
@@ -635,6 +629,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   visible_key_range(cfg, m0 + off, min(m0 + kT, si.q_len) - 1 + off, si.k_len, klo, khi);
   const int n_lo = klo / kT;
   const int n_hi = (khi + kT - 1) / kT;
+  // step j works on key tile n_hi - 1 - j: the masked tiles (diagonal, ragged end) come first
   const int total = max(n_hi - n_lo, 0);
 
   if (tid == 0) {
@@ -687,13 +682,13 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         {
           const uint32_t bar = smem_u32(&sh->full_a[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingK + stage * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+          load_tile<D>(sRingK + stage * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
         }
         if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 51)) break;
         {
           const uint32_t bar = smem_u32(&sh->full_b[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingV + stage * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_lo + j) * kT, hk, (int)si.k_boff);
+          load_tile<D>(sRingV + stage * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -774,7 +769,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     bool ok = true;
     for (int j = 0; j < total && ok; ++j) {
-      const int k0 = (n_lo + j) * kT + x * kHalfT;   // first key of this thread's columns
+      const int k0 = (n_hi - 1 - j) * kT + x * kHalfT;   // first key of this thread's columns
       bool masked = (k0 + kHalfT > si.k_len);
       if (cfg.causal) masked |= (k0 + kHalfT - 1 > m0 + off);
       if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);

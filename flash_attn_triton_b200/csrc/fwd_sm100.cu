@@ -50,8 +50,21 @@ __device__ long long g_fwd_trace[3][32][8];
         (threadIdx.x & 31) == 0)                                                             \
       g_fwd_trace[role][step][ev] = clock64();                                               \
   } while (0)
+// per-launch sums over all CTAs: clock64 cycles of [0] setup, [1] until the first score tile,
+// [2] main loop, [3] epilogue, [4] exit barrier, [5] key tiles, [6] CTAs
+__device__ unsigned long long g_fwd_phase[8];
+extern "C" int fa_debug_fwd_phases(unsigned long long* out, int reset) {
+  int r = (int)cudaMemcpyFromSymbol(out, g_fwd_phase, sizeof(unsigned long long) * 8);
+  if (reset) {
+    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_fwd_phase, z, sizeof(z));
+  }
+  return r;
+}
+#define FA_PHASE_STAMP(var) const long long var = clock64()
 #else
 #define FA_TRACE_EV(role, step, ev) do {} while (0)
+#define FA_PHASE_STAMP(var) do {} while (0)
 #endif
 
 namespace {
@@ -112,10 +125,12 @@ static_assert(sizeof(Shared) <= 4096, "Shared must fit its reserve");
 template <typename T, int D, bool kExtras, bool kInt8>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const fa_attn_args p, const ScoreCfg cfg,
-                 const float* __restrict__ sq, const float* __restrict__ sk) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                 const fa_attn_args p, const ScoreCfg cfg, const float* __restrict__ sq,
+                 const float* __restrict__ sk) {
   static_assert(!kInt8 || D == 128, "the INT8 variant stages 128-byte code rows");
   using C = Cfg<D>;
+  FA_PHASE_STAMP(ph_t0);
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -138,6 +153,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   visible_key_range(cfg, m0 + off, min(m0 + kBM, si.q_len) - 1 + off, si.k_len, klo, khi);
   const int n_lo = klo / kBN;
   const int n_hi = (khi + kBN - 1) / kBN;
+  // Step j works on key tile n_hi - 1 - j: the tiles that need masking (the causal diagonal,
+  // the ragged end of the keys) come first, where they overlap the start-up of the pipeline,
+  // and the last steps, which the epilogue has to wait for, are the cheap unmasked ones.
   const int nsteps = max(n_hi - n_lo, 0);
 
   if (tid == 0) {
@@ -166,6 +184,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
+  FA_PHASE_STAMP(ph_t1);
 
   if (warp >= 10) {
     // idle warps of the producer/MMA warpgroup; in the INT8 variant warp 10 stages the key
@@ -179,7 +198,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) w = wait_bar(&sh->sk_empty[buf], ((j >> 1) & 1) ^ 1, sh, 12);
         if (!__all_sync(0xffffffffu, w)) break;
         for (int i = lane; i < kBN; i += 32) {
-          const int col = (n_lo + j) * kBN + i;
+          const int col = (n_hi - 1 - j) * kBN + i;
           sh->skt[buf][i] = col < si.k_len ? sk[bh_rows + col] : 1.f;
         }
         __syncwarp();
@@ -193,6 +212,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
+      prefetch_tmap(&tmO);
       const int krow0 = (int)si.k_row0;
       const int kb = (int)si.k_boff;
       {
@@ -214,13 +234,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = wait_bar(&sh->kv_empty[stage], phase ^ 1, sh, 11);
         if (!ok) return;
         const uint32_t bar = smem_u32(&sh->kv_full[stage]);
-#ifdef FA_ABL_NOTMA
-        if (phase != 0) {
-          mbar_arrive(bar);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
-          return;
-        }
-#endif
         if (codes) {  // int8 K tile: one box of 128-byte rows
           mbar_expect_tx(bar, kBN * D);
           tma_load_4d(sKV + stage * C::kTileBytes, tm, bar, 0, hk, krow0 + tile * kBN, kb);
@@ -233,11 +246,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       };
       // order of use: K0, K1, then V_j, K_{j+2}
-      load_kv(&tmK, n_lo, kInt8);
-      if (nsteps > 1) load_kv(&tmK, n_lo + 1, kInt8);
+      load_kv(&tmK, n_hi - 1, kInt8);
+      if (nsteps > 1) load_kv(&tmK, n_hi - 2, kInt8);
       for (int j = 0; j < nsteps; ++j) {
-        load_kv(&tmV, n_lo + j, false);
-        if (j + 2 < nsteps) load_kv(&tmK, n_lo + j + 2, kInt8);
+        load_kv(&tmV, n_hi - 1 - j, false);
+        if (j + 2 < nsteps) load_kv(&tmK, n_hi - 3 - j, kInt8);
       }
     }
   } else if (warp == 9) {
@@ -329,9 +342,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
     const float qk_scale = cfg.scale * 1.44269504f;
 
+#ifdef FA_TRACE
+    long long ph_t2 = 0;
+#endif
     for (int j = x; j < nsteps && ok; j += 2) {
       const int t = j >> 1;                          // index of the tile inside this stream
-      const int k0 = (n_lo + j) * kBN;
+      const int k0 = (n_hi - 1 - j) * kBN;
       bool masked = (k0 + kBN > si.k_len);
       if (cfg.causal) masked |= (k0 + kBN - 1 > tq_min);
       if (cfg.wl >= 0) masked |= (k0 < tq_max - cfg.wl);
@@ -342,6 +358,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 1);
+#ifdef FA_TRACE
+      if (t == 0) ph_t2 = clock64();
+#endif
 
       // ---- the 128 scores of this row into registers -------------------------------------
       uint32_t r[4][32];
@@ -498,6 +517,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 
     // ---- epilogue: merge the two streams, O / l -> global, base-2 LSE ---------------------
+    FA_PHASE_STAMP(ph_t3);
+#ifdef FA_TRACE
+    if (tid == 0 && nsteps > 0) {
+      atomicAdd(&g_fwd_phase[1], (unsigned long long)(ph_t2 - ph_t1));
+      atomicAdd(&g_fwd_phase[2], (unsigned long long)(ph_t3 - ph_t2));
+    }
+#endif
     const int my_tiles = (nsteps - x + 1) >> 1;      // tiles of this stream (0 if nsteps <= x)
     if (ok && my_tiles > 0) ok = wait_bar(&sh->o_ready[x], (my_tiles - 1) & 1, sh, 35 + x);
     sh->ml[x][row_in_tile] = make_float2(m_used, l);
@@ -513,8 +539,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
       const float ca = (x == 0 ? w_me : w_ot) * inv, cb = (x == 0 ? w_ot : w_me) * inv;
       const bool row_ok = row < si.q_len;
-      // this group writes head_dim columns [x*D/2, (x+1)*D/2) of the row
+      // This group writes head_dim columns [x*D/2, (x+1)*D/2) of the row.  The tile is staged in
+      // shared memory (over Q, which no MMA reads any more) in the swizzled box layout and
+      // written by the TMA unit as full rows; a packed tile that reaches past the end of its
+      // sequence is stored row by row instead (the unit would write the neighbour's rows).
       constexpr int DH = D / 2;
+      const bool via_tma = (p.cu_seqlens_q == nullptr) || (m0 + kBM <= si.q_len);
       T* og = reinterpret_cast<T*>(p.o) + si.q_boff * p.o_stride[0] +
               (si.q_row0 + row) * p.o_stride[1] + (int64_t)h * p.o_stride[2] + x * DH;
       const uint32_t tOa = tmem + lane_addr + 256 + x * DH, tOb = tOa + 128;
@@ -533,31 +563,62 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) rb[i] = 0u;
         }
-        if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            float f[8];
+        for (int i = 0; i < 32; i += 8) {
+          float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              f[e] = __uint_as_float(ra[i + e]) * ca + __uint_as_float(rb[i + e]) * cb;
-            uint4 v;
-            v.x = Elem<T>::pack(f[0], f[1]);
-            v.y = Elem<T>::pack(f[2], f[3]);
-            v.z = Elem<T>::pack(f[4], f[5]);
-            v.w = Elem<T>::pack(f[6], f[7]);
+          for (int e = 0; e < 8; ++e)
+            f[e] = __uint_as_float(ra[i + e]) * ca + __uint_as_float(rb[i + e]) * cb;
+          uint4 v;
+          v.x = Elem<T>::pack(f[0], f[1]);
+          v.y = Elem<T>::pack(f[2], f[3]);
+          v.z = Elem<T>::pack(f[4], f[5]);
+          v.w = Elem<T>::pack(f[6], f[7]);
+          if (via_tma) {
+            const int col = x * DH + cc * 32 + i;          // first of 8 columns = one 16-byte chunk
+            st_shared_v4(sw128_addr(sQ + (col / 64) * (kBM * 128), row_in_tile, (col % 64) / 8), v);
+          } else if (row_ok) {
             *reinterpret_cast<uint4*>(og + cc * 32 + i) = v;
           }
+        }
+      }
+      if (via_tma) {
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (tid == 0) {
+#pragma unroll
+          for (int bx = 0; bx < D / 64; ++bx)
+            tma_store_4d(&tmO, sQ + bx * (kBM * 128), bx * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+          tma_store_commit();
+          tma_store_wait_read();
         }
       }
       if (x == 0 && row_ok && p.lse2 != nullptr)
         p.lse2[si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
                (int64_t)h * p.lse_stride[2]] = lsum > 0.f ? mstar + log2f(lsum) : -INFINITY;
     }
+#ifdef FA_TRACE
+    if (tid == 0) atomicAdd(&g_fwd_phase[3], (unsigned long long)(clock64() - ph_t3));
+#endif
   }
 
+#ifdef FA_TRACE
+  long long ph_t4 = clock64();
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, 512);
+#ifdef FA_TRACE
+  if (tid == 0) {
+    // thread 0 is in softmax group A, whose stamps ph_t2/ph_t3 live in that branch: re-read through shared memory
+    const long long t5 = clock64();
+    atomicAdd(&g_fwd_phase[0], (unsigned long long)(ph_t1 - ph_t0));
+    atomicAdd(&g_fwd_phase[4], (unsigned long long)(t5 - ph_t4));
+    atomicAdd(&g_fwd_phase[5], (unsigned long long)nsteps);
+    atomicAdd(&g_fwd_phase[6], 1ull);
+    atomicAdd(&g_fwd_phase[7], (unsigned long long)(t5 - ph_t0));
+  }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------
@@ -585,9 +646,10 @@ static bool make_map(CUtensorMap* m, const void* base, const int64_t* stride, in
 template <typename T, int D>
 static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, int q_rows, int k_rows) {
   using C = Cfg<D>;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   const bool packed = a.cu_seqlens_q != nullptr;
-  if (!make_map(&tq, a.q, a.q_stride, q_rows, a.heads_q, a.batch, D, packed) ||
+  if (!make_map(&to, a.o, a.o_stride, q_rows, a.heads_q, a.batch, D, packed) ||
+      !make_map(&tq, a.q, a.q_stride, q_rows, a.heads_q, a.batch, D, packed) ||
       !make_map(&tk, a.k, a.k_stride, k_rows, a.heads_kv, a.batch, D, packed) ||
       !make_map(&tv, a.v, a.v_stride, k_rows, a.heads_kv, a.batch, D, packed)) {
     set_error("fwd_sm100: cuTensorMapEncodeTiled failed");
@@ -601,7 +663,7 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
     return FA_ERR_LAUNCH;
   }
   dim3 grid((a.seqlen_q + kBM - 1) / kBM, a.heads_q, a.batch);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, a, cfg, nullptr, nullptr);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, a, cfg, nullptr, nullptr);
   return check_launch("fwd_sm100");
 }
 
@@ -638,14 +700,14 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
   const int64_t rows = (int64_t)a.batch * a.heads * a.seqlen;
   if (int r = quantize_q(a.q, a.q8_scratch, a.sq_scratch, rows, D, st)) return r;
   const int B = a.batch, H = a.heads, S = a.seqlen;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
     const uint64_t s8[3] = {(uint64_t)S * D, (uint64_t)D, (uint64_t)H * S * D};
     const uint64_t s16[3] = {(uint64_t)S * D * 2, (uint64_t)D * 2, (uint64_t)H * S * D * 2};
     const uint32_t box8[4] = {128, 1, 128, 1}, box16[4] = {64, 1, 128, 1};
     if (!encode_tmap(&tq, a.q8_scratch, 1, 4, dims, s8, box8) || !encode_tmap(&tk, a.k8, 1, 4, dims, s8, box8) ||
-        !encode_tmap(&tv, a.v, 2, 4, dims, s16, box16)) {
+        !encode_tmap(&tv, a.v, 2, 4, dims, s16, box16) || !encode_tmap(&to, a.o, 2, 4, dims, s16, box16)) {
       set_error("fwd_int8_sm100: cuTensorMapEncodeTiled failed");
       return FA_ERR_LAUNCH;
     }
@@ -670,7 +732,7 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
     return FA_ERR_LAUNCH;
   }
   dim3 grid((S + kBM - 1) / kBM, H, B);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, p, cfg, a.sq_scratch, a.s_k);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, cfg, a.sq_scratch, a.s_k);
   return check_launch("fwd_int8_sm100");
 }
 

@@ -119,6 +119,31 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// Tiled store shared -> global of one box (the epilogues stage their output tile in shared
+// memory in the swizzled layout and let the TMA unit write full, coalesced rows; rows past the
+// tensor's extent are clipped by the unit).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// returns once the unit has READ the shared-memory source of every committed store
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+}
+// Address of the 16-byte chunk `chunk` (0..7) of row `row` inside a box of 128-byte rows laid
+// out with the 128-byte swizzle (box base 1024-byte aligned).
+__device__ __forceinline__ uint32_t sw128_addr(uint32_t box_base, int row, int chunk) {
+  return box_base + (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // TMEM
 // ---------------------------------------------------------------------------------------
