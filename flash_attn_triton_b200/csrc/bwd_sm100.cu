@@ -333,18 +333,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       };
       auto slotQ = [&](int it) { return sRingQ + (it % C::kStages) * C::kTileBytes; };
       auto slotO = [&](int it) { return sRingO + (it % C::kStages) * C::kTileBytes; };
-#ifdef FA_TRACE_SERIAL
-      // debug: wait for every MMA group right after issuing it and record how long it ran
-      uint32_t dbg_phase = 0;
-      auto drain = [&](int step, int ev) {
-        mma_commit_lp(smem_u32(&sh->s_full[1]), leader);
-        wq(&sh->s_full[1], dbg_phase, 99);
-        dbg_phase ^= 1;
-        FA_TRACE_REC(2, step, ev);
-      };
-#else
-      auto drain = [&](int, int) {};
-#endif
       wq(&sh->res_full, 0, 43);
       wq(&sh->full_a[0], 0, 44);
       if (ok) {
@@ -369,51 +357,28 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (more) {
           wq(&sh->full_a[st1], ph1, 44);
           if (!ok) break;
-          drain(i, 0);
           mma_kmajor<D>(tS, sK, slotQ(i + 1), idesc_s, leader);                // S^T(i+1)
           mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
-          drain(i, 1);
         }
-#ifndef FA_TRACE_SERIAL
         FA_BTRACE(2, i, 1);
-#endif
         wq(&sh->ds_ready, i & 1, 46);
         if (!ok) break;
         FA_BTRACE(2, i, 2);
         mma_from_tmem<D>(tdK, tdP, slotQ(i), idesc_acc, i > 0, leader);        // dK += dS(i)^T Q(i)
         mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
-#ifdef FA_TRACE_SERIAL
-        drain(i, 3);
-#else
         FA_BTRACE(2, i, 3);
-#endif
         if (more) {
           wq(&sh->full_b[st1], ph1, 44);
           if (!ok) break;
-#ifdef FA_TRACE_SERIAL
-          FA_TRACE_REC(2, i, 4);
-#endif
           mma_kmajor<D>(tdP, sV, slotO(i + 1), idesc_s, leader);               // dP^T(i+1)
           mma_commit_lp(smem_u32(&sh->dp_full), leader);
-#ifdef FA_TRACE_SERIAL
-          drain(i, 5);
-#else
           FA_BTRACE(2, i, 4);
-#endif
           wq(&sh->p_ready, (i + 1) & 1, 45);
           if (!ok) break;
-#ifdef FA_TRACE_SERIAL
-          FA_TRACE_REC(2, i, 6);
-#else
           FA_BTRACE(2, i, 5);
-#endif
           mma_from_tmem<D>(tdV, tS, slotO(i + 1), idesc_acc, true, leader);    // dV += P(i+1)^T dO(i+1)
           mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
-#ifdef FA_TRACE_SERIAL
-          drain(i, 7);
-#else
           FA_BTRACE(2, i, 6);
-#endif
         }
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
