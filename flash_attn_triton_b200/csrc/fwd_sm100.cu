@@ -1,32 +1,35 @@
 // Forward attention on the 5th-generation tensor cores: TMA-staged tiles, tcgen05.mma with
 // accumulators in tensor memory, warp-specialised online softmax.
 //
-// One CTA owns 128 query rows of one (batch, head).  Keys arrive in tiles of 128; the score
-// tile S = Q K^T (128 x 128, one N=128 MMA chain) is DOUBLE-BUFFERED in tensor memory.  The
-// key tiles are dealt alternately to two softmax warpgroups ("streams"): stream A takes the
-// even tiles and score buffer S[0], stream B the odd tiles and S[1].  Each stream is an
-// independent online softmax over its own keys (own running maximum, row sum and output
-// accumulator, like a 2-way split over keys, merged in the epilogue), so the two groups run
-// half a step out of phase: while one is in its exp2 (MUFU) phase the other waits, loads or
-// reduces, and the tensor pipe always has the other stream's P V and Q K^T to run:
+// One CTA owns TWO tiles of 128 query rows of one (batch, head) -- 256 consecutive rows -- and
+// every K/V tile it loads is used by both: that halves the TMA writes into shared memory per
+// score tile (the tensor pipe reads its operands from there at the full shared-memory bandwidth,
+// so every byte counts) and the fixed cost per CTA.  Each query tile is a "stream" with its own
+// softmax warpgroup, score buffer and output accumulator; the two streams run out of phase, so
+// that while one group is in its exp2 (MUFU) phase the tensor pipe runs the other stream's
+// P V and Q K^T:
 //
-//   warps 0-3   softmax group A : key tiles 0, 2, 4, ... (S[0], accumulator O_a)
-//   warps 4-7   softmax group B : key tiles 1, 3, 5, ... (S[1], accumulator O_b)
-//   warp  8     TMA producer    : Q once, then K/V tiles through a ring
-//   warp  9     MMA issuer      : S[x] = Q K_j^T (SS);  O_x += P_j V_j (A = P_j from TMEM)
-//   warps 10-11 idle; they complete the third warpgroup so that it can hand its registers
-//               to the softmax groups (setmaxnreg)
+//   warps 0-3   softmax group 0 : query rows   0..127 of the CTA (S[0], accumulator O_0)
+//   warps 4-7   softmax group 1 : query rows 128..255 of the CTA (S[1], accumulator O_1)
+//   warp  8     TMA producer    : both Q tiles once, then K/V tiles through a ring
+//   warp  9     MMA issuer      : S[x] = Q_x K_j^T (SS);  O_x += P_x V_j (A = P_x from TMEM)
+//   warps 10-11 idle (warp 10 stages the key scales of the INT8 variant); they complete the
+//               third warpgroup so that it can hand its registers to the softmax groups
 //
 // One thread owns one query row (TMEM lane = row) and all 128 scores of a tile.  P (fp16/bf16)
-// overwrites the first 64 columns of its S buffer; Q K_{j+2}^T may overwrite it because P_j V_j
-// precedes it in the in-order tensor pipe.  The running maximum is only raised when it grows
-// by more than 2^8 ("lazy rescale"), so O is rarely touched by the softmax warps; exactness
-// is kept because O and the row sum of a stream always share the same reference maximum.
+// overwrites the first 64 columns of its S buffer; Q_x K_{j+1}^T may overwrite it because
+// P_x V_j precedes it in the in-order tensor pipe.  The running maximum is only raised when it
+// grows by more than 2^8 ("lazy rescale"), so O is rarely touched by the softmax warps.
 //
-// TMEM (512 columns): S[0] | S[1] | O_a | O_b, 128 fp32 columns each (O uses head_dim).
-// Shared memory: Q (128 x D) + a ring of K/V tiles (128 keys x D), written by TMA with the
-// 128-byte swizzle the MMA descriptors expect.  Ring order = order of use:
-// K0, K1, V0, K2, V1, K3, ...
+// Step j of a CTA works on key tile n_hi - 1 - j: the tiles that need masking (the causal
+// diagonal, the ragged end of the keys) come first, where they overlap the start-up of the
+// pipeline.  With a causal mask the lower query tile sees one key tile less, so a stream is
+// active only for the steps whose tile it can see.
+//
+// TMEM (512 columns): S[0] | S[1] | O_0 | O_1, 128 fp32 columns each (O uses head_dim).
+// Shared memory: two Q tiles (128 x D each) + a ring of K/V tiles (128 keys x D), written by
+// TMA with the 128-byte swizzle the MMA descriptors expect, in order of use K0, V0, K1, V1, ...
+// The epilogue stages each output tile over its Q tile and lets the TMA unit store it.
 //
 // Every mbarrier wait is bounded; on timeout the CTA raises a device-side status word,
 // releases its TMEM and returns.
@@ -69,7 +72,7 @@ extern "C" int fa_debug_fwd_phases(unsigned long long* out, int reset) {
 
 namespace {
 
-constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int kBN = 128;          // keys per K/V tile
 constexpr int kThreads = 384;     // 8 softmax warps + a warpgroup holding producer and MMA warps
 constexpr float kRescaleThreshold = 8.0f;
@@ -83,9 +86,9 @@ constexpr int kMaxStages = 8;
 
 template <int D> struct Cfg {
   static constexpr int kTileBytes = kBN * D * 2;                    // one Q/K/V tile
-  static constexpr int kStages = (D == 128) ? 5 : 8;                // K/V ring depth
+  static constexpr int kStages = (D == 128) ? 4 : 8;                // K/V ring depth
   static constexpr int kBoxes = D / 64;                             // TMA boxes per tile
-  static constexpr int kSmemTiles = (1 + kStages) * kTileBytes;
+  static constexpr int kSmemTiles = (2 + kStages) * kTileBytes;
   static constexpr int kSmemBytes = kSmemTiles + 1024 /*align slack*/ + 4096 /*barriers, merge*/;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
@@ -99,10 +102,9 @@ struct Shared {
   uint64_t o_ready[2];     // [stream]: its latest P V finished
   uint32_t tmem_base;
   volatile int abort_flag;
-  float2 ml[2][kBM];       // epilogue exchange: (reference max, row sum) of each stream
   // INT8 variant: key scales of the current score tiles, staged by warp 10
   uint64_t sk_full[2];     // [score buffer] scales written
-  uint64_t sk_empty[2];    // [score buffer] scales consumed (128 arrivals)
+  uint64_t sk_empty[2];    // [score buffer] scales consumed (256 arrivals: both groups, active or not)
   alignas(16) float skt[2][kBN];
 };
 
@@ -136,27 +138,41 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   Shared* sh = reinterpret_cast<Shared*>(tiles + C::kSmemTiles);
-  const uint32_t sQ = smem_u32(tiles);
-  const uint32_t sKV = sQ + C::kTileBytes;
+  const uint32_t sQ = smem_u32(tiles);                 // + x * kTileBytes
+  const uint32_t sKV = sQ + 2 * C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, b = blockIdx.z;
   const int mblk = cfg.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy blocks first
   const SeqInfo si = seq_info(p, b);
-  const int m0 = mblk * kBM;
-  if (m0 >= si.q_len) return;
+  const int m00 = mblk * 2 * kBM;
+  if (m00 >= si.q_len) return;
   const int hk = h / (p.heads_q / p.heads_kv);
   const int off = p.q_pos_offset;
 
-  // K/V tiles [n_lo, n_hi) that any of this CTA's rows can see
-  int klo, khi;
-  visible_key_range(cfg, m0 + off, min(m0 + kBM, si.q_len) - 1 + off, si.k_len, klo, khi);
-  const int n_lo = klo / kBN;
-  const int n_hi = (khi + kBN - 1) / kBN;
-  // Step j works on key tile n_hi - 1 - j: the tiles that need masking (the causal diagonal,
-  // the ragged end of the keys) come first, where they overlap the start-up of the pipeline,
-  // and the last steps, which the epilogue has to wait for, are the cheap unmasked ones.
-  const int nsteps = max(n_hi - n_lo, 0);
+  // Key tiles [nlo[x], nhi[x]) that the rows of stream x can see, and their union [n_lo, n_hi).
+  // Step j works on tile n_hi - 1 - j; stream x is active for the steps [jb[x], je[x]).
+  auto tile_range = [&](int m0, int& lo, int& hi) {
+    lo = hi = 0;
+    if (m0 < si.q_len) {
+      int klo, khi;
+      visible_key_range(cfg, m0 + off, min(m0 + kBM, si.q_len) - 1 + off, si.k_len, klo, khi);
+      if (khi > klo) {
+        lo = klo / kBN;
+        hi = (khi + kBN - 1) / kBN;
+      }
+    }
+  };
+  int nlo0, nhi0, nlo1, nhi1;
+  tile_range(m00, nlo0, nhi0);
+  tile_range(m00 + kBM, nlo1, nhi1);
+  const bool has0 = nhi0 > nlo0, has1 = nhi1 > nlo1;
+  const int n_lo = has0 ? (has1 ? min(nlo0, nlo1) : nlo0) : nlo1;
+  const int n_hi = has0 ? (has1 ? max(nhi0, nhi1) : nhi0) : nhi1;
+  const int nsteps = (has0 || has1) ? n_hi - n_lo : 0;
+  const int jb0 = has0 ? n_hi - nhi0 : 0, je0 = has0 ? n_hi - nlo0 : 0;
+  const int jb1 = has1 ? n_hi - nhi1 : 0, je1 = has1 ? n_hi - nlo1 : 0;
+  const bool q1_loaded = m00 + kBM < si.q_len;         // the second query tile exists
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->q_full), 1);
@@ -171,7 +187,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sh->sk_full[i]), 1);
-      mbar_init(smem_u32(&sh->sk_empty[i]), 128);
+      mbar_init(smem_u32(&sh->sk_empty[i]), 256);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -188,8 +204,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp >= 10) {
     // idle warps of the producer/MMA warpgroup; in the INT8 variant warp 10 stages the key
-    // scales of score tile j into shared memory (slot j & 1)
-    reg_dealloc<56>();
+    // scales of the key tile of step j into shared memory (slot j & 1)
+    reg_dealloc<72>();
     if (kInt8 && warp == 10) {
       const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
       for (int j = 0; j < nsteps; ++j) {
@@ -207,7 +223,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
-    reg_dealloc<56>();
+    reg_dealloc<72>();
     if (lane == 0 && nsteps > 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
@@ -217,13 +233,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int kb = (int)si.k_boff;
       {
         const uint32_t bar = smem_u32(&sh->q_full);
+        const int ntile = q1_loaded ? 2 : 1;
         if (kInt8) {
-          mbar_expect_tx(bar, kBM * D);
-          tma_load_4d(sQ, &tmQ, bar, 0, h, (int)si.q_row0 + m0, (int)si.q_boff);
+          mbar_expect_tx(bar, ntile * kBM * D);
+          for (int x = 0; x < ntile; ++x)
+            tma_load_4d(sQ + x * C::kTileBytes, &tmQ, bar, 0, h, (int)si.q_row0 + m00 + x * kBM, (int)si.q_boff);
         } else {
-          mbar_expect_tx(bar, C::kTileBytes);
-          for (int x = 0; x < C::kBoxes; ++x)
-            tma_load_4d(sQ + x * (kBM * 128), &tmQ, bar, x * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+          mbar_expect_tx(bar, ntile * C::kTileBytes);
+          for (int x = 0; x < ntile; ++x)
+            for (int bx = 0; bx < C::kBoxes; ++bx)
+              tma_load_4d(sQ + x * C::kTileBytes + bx * (kBM * 128), &tmQ, bar, bx * 64, h,
+                          (int)si.q_row0 + m00 + x * kBM, (int)si.q_boff);
         }
       }
       int stage = 0;
@@ -239,25 +259,24 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tma_load_4d(sKV + stage * C::kTileBytes, tm, bar, 0, hk, krow0 + tile * kBN, kb);
         } else {
           mbar_expect_tx(bar, C::kTileBytes);
-          for (int x = 0; x < C::kBoxes; ++x)
-            tma_load_4d(sKV + stage * C::kTileBytes + x * (kBN * 128), tm, bar, x * 64, hk,
+          for (int bx = 0; bx < C::kBoxes; ++bx)
+            tma_load_4d(sKV + stage * C::kTileBytes + bx * (kBN * 128), tm, bar, bx * 64, hk,
                         krow0 + tile * kBN, kb);
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       };
-      // order of use: K0, K1, then V_j, K_{j+2}
+      // order of use: K_0, then V_j, K_{j+1}
       load_kv(&tmK, n_hi - 1, kInt8);
-      if (nsteps > 1) load_kv(&tmK, n_hi - 2, kInt8);
       for (int j = 0; j < nsteps; ++j) {
         load_kv(&tmV, n_hi - 1 - j, false);
-        if (j + 2 < nsteps) load_kv(&tmK, n_hi - 3 - j, kInt8);
+        if (j + 1 < nsteps) load_kv(&tmK, n_hi - 2 - j, kInt8);
       }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
     // The whole warp runs the control flow in lock step and every lane polls the barriers;
     // the lane chosen once by elect_one issues the MMAs and commits.
-    reg_dealloc<56>();
+    reg_dealloc<72>();
     if (nsteps > 0) {
       constexpr uint32_t idesc_qk = make_idesc(1, Fmt<T>::code, 0, 0, kBM, kBN);
       constexpr uint32_t idesc_pv = make_idesc(1, Fmt<T>::code, 0, 1, kBM, D);
@@ -270,11 +289,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
       };
       auto advance = [&]() { if (++stage == C::kStages) { stage = 0; phase ^= 1; } };
-      const uint64_t dq = make_smem_desc(sQ, 16, 1024);
-      auto issue_qk = [&](int x) {
-        wwait(&sh->kv_full[stage], phase, 22);
-        if (!ok) return;
-        const uint32_t kbase = sKV + stage * C::kTileBytes;
+      // S[x] = Q_x K^T with the K tile at kbase
+      auto issue_qk = [&](int x, uint32_t kbase) {
+        const uint64_t dq = make_smem_desc(sQ + x * C::kTileBytes, 16, 1024);
         const uint64_t dk = make_smem_desc(kbase, 16, 1024);
         if (kInt8) {
           constexpr uint32_t idesc_i8 = make_idesc(2, 1, 0, 0, kBM, kBN);  // s32 <- s8 x s8
@@ -292,41 +309,71 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         mma_commit_lp(smem_u32(&sh->s_full[x]), leader);
+      };
+      int pcnt0 = 0, pcnt1 = 0;   // P tiles consumed so far, per stream
+      wwait(&sh->q_full, 0, 21);
+      wwait(&sh->kv_full[stage], phase, 22);
+      if (ok) {
+        const uint32_t kbase = sKV + stage * C::kTileBytes;
+        if (jb0 == 0 && je0 > 0) issue_qk(0, kbase);
+        if (jb1 == 0 && je1 > 0) issue_qk(1, kbase);
         mma_commit_lp(smem_u32(&sh->kv_empty[stage]), leader);
         advance();
-      };
-      wwait(&sh->q_full, 0, 21);
-      if (ok) issue_qk(0);
-      if (ok && nsteps > 1) issue_qk(1);
+      }
       for (int j = 0; j < nsteps && ok; ++j) {
-        const int x = j & 1;
         FA_TRACE_EV(2, j, 0);
-        wwait(&sh->kv_full[stage], phase, 24);
-        const uint32_t vbase = sKV + stage * C::kTileBytes;
-        FA_TRACE_EV(2, j, 1);
-        wwait(&sh->p_ready[x], (j >> 1) & 1, 25 + x);
+        wwait(&sh->kv_full[stage], phase, 24);          // V_j
         if (!ok) break;
-        FA_TRACE_EV(2, j, 2);
-        {
-          const uint32_t a = tmem + x * kBN;
-          const uint64_t dv = make_smem_desc(vbase, kBN * 128, 1024);
-#pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk)
-            mma_f16_ts_lp(tmem + 256 + x * 128, a + kk * 8, dv + ((kk * 2048) >> 4), idesc_pv,
-                          (j >= 2 || kk > 0) ? 1u : 0u, leader);
-          mma_commit_lp(smem_u32(&sh->o_ready[x]), leader);
-          mma_commit_lp(smem_u32(&sh->kv_empty[stage]), leader);
-        }
+        const int vstage = stage;
+        const uint32_t vbase = sKV + stage * C::kTileBytes;
         advance();
+        const bool more = j + 1 < nsteps;
+        const int kstage = stage;
+        const uint32_t kbase = sKV + stage * C::kTileBytes;
+        bool k_waited = false;
+        FA_TRACE_EV(2, j, 1);
+        auto do_stream = [&](int x, int sjb, int sje, int& pcnt) {
+          if (j >= sjb && j < sje) {
+            wwait(&sh->p_ready[x], pcnt & 1, 25 + x);
+            if (!ok) return;
+            ++pcnt;
+            const uint32_t a = tmem + x * kBN;
+            const uint64_t dv = make_smem_desc(vbase, kBN * 128, 1024);
+#pragma unroll
+            for (int kk = 0; kk < kBN / 16; ++kk)
+              mma_f16_ts_lp(tmem + 256 + x * 128, a + kk * 8, dv + ((kk * 2048) >> 4), idesc_pv,
+                            (j > sjb || kk > 0) ? 1u : 0u, leader);
+            mma_commit_lp(smem_u32(&sh->o_ready[x]), leader);
+          }
+          if (more && j + 1 >= sjb && j + 1 < sje) {
+            if (!k_waited) {
+              wwait(&sh->kv_full[kstage], phase, 22);   // K_{j+1}
+              if (!ok) return;
+              k_waited = true;
+            }
+            issue_qk(x, kbase);
+          }
+        };
+        do_stream(0, jb0, je0, pcnt0);
+        FA_TRACE_EV(2, j, 2);
+        if (ok) do_stream(1, jb1, je1, pcnt1);
         FA_TRACE_EV(2, j, 4);
-        if (j + 2 < nsteps) issue_qk(x);
-        FA_TRACE_EV(2, j, 5);
+        if (!ok) break;
+        mma_commit_lp(smem_u32(&sh->kv_empty[vstage]), leader);
+        if (more) {
+          // a K tile that no stream needs (cannot happen for contiguous visible ranges) would
+          // still have to be consumed to keep the ring in step
+          if (!k_waited) wwait(&sh->kv_full[kstage], phase, 22);
+          mma_commit_lp(smem_u32(&sh->kv_empty[kstage]), leader);
+          advance();
+        }
       }
     }
   } else {
     // ------------------------------- softmax groups -------------------------------------
-    reg_alloc<224>();
-    const int x = warp >> 2;                         // stream: key tiles j with (j & 1) == x
+    reg_alloc<216>();
+    const int x = warp >> 2;                         // stream = query tile of the CTA
+    const int m0 = m00 + x * kBM;
     const int row_in_tile = (warp & 3) * 32 + lane;  // TMEM lane
     const int row = m0 + row_in_tile;                // query row inside the sequence
     const int qpos = row + off;
@@ -341,12 +388,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
     const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
     const float qk_scale = cfg.scale * 1.44269504f;
-
+    const int my_jb = x ? jb1 : jb0, my_je = x ? je1 : je0;
 #ifdef FA_TRACE
     long long ph_t2 = 0;
 #endif
-    for (int j = x; j < nsteps && ok; j += 2) {
-      const int t = j >> 1;                          // index of the tile inside this stream
+
+    for (int j = kInt8 ? 0 : my_jb; j < (kInt8 ? nsteps : my_je) && ok; ++j) {
+      if (kInt8 && (j < my_jb || j >= my_je)) {
+        // not this stream's tile, but the slot of its key scales is released by both groups
+        ok = wait_bar(&sh->sk_full[j & 1], (j >> 1) & 1, sh, 37 + x);
+        if (ok) mbar_arrive(smem_u32(&sh->sk_empty[j & 1]));
+        continue;
+      }
+      const int t = j - my_jb;                       // index of the tile inside this stream
       const int k0 = (n_hi - 1 - j) * kBN;
       bool masked = (k0 + kBN > si.k_len);
       if (cfg.causal) masked |= (k0 + kBN - 1 > tq_min);
@@ -374,9 +428,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // (float(acc) * (s_q * s_k)) * (softmax_scale * log2 e), in the reference's order.
         // |acc| <= 128*127*127 < 2^22, so int -> float is exact through the 1.5*2^23 bias
         // (an integer add and a float subtract instead of a quarter-rate I2F).
-        ok = wait_bar(&sh->sk_full[x], t & 1, sh, 37 + x);
+        ok = wait_bar(&sh->sk_full[j & 1], (j >> 1) & 1, sh, 37 + x);
         if (!ok) break;
-        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[x][0]);
+        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[j & 1][0]);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
@@ -393,7 +447,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         }
-        mbar_arrive(smem_u32(&sh->sk_empty[x]));
+        mbar_arrive(smem_u32(&sh->sk_empty[j & 1]));
       } else if (prescaled) {
         // score pipeline and mask applied once, in place; values end up in the log2 domain
 #pragma unroll
@@ -441,9 +495,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       } else {
         const bool need = mx > m_used + kRescaleThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          // The previous P V of this stream (tile j-2) is its (t-1)-th; the one of tile j
-          // cannot complete before P_j is written below, so the barrier is at most one
-          // phase ahead of the parity waited for here.
+          // The previous P V of this stream is its (t-1)-th; the one of this tile cannot
+          // complete before P is written below, so the barrier is at most one phase ahead
+          // of the parity waited for here.
           ok = wait_bar(&sh->o_ready[x], (t - 1) & 1, sh, 33 + x);
           if (!ok) break;
           tc_fence_after();
@@ -516,7 +570,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 5);
     }
 
-    // ---- epilogue: merge the two streams, O / l -> global, base-2 LSE ---------------------
+    // ---- epilogue: O / l -> global, base-2 LSE ------------------------------------------
     FA_PHASE_STAMP(ph_t3);
 #ifdef FA_TRACE
     if (tid == 0 && nsteps > 0) {
@@ -524,59 +578,40 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       atomicAdd(&g_fwd_phase[2], (unsigned long long)(ph_t3 - ph_t2));
     }
 #endif
-    const int my_tiles = (nsteps - x + 1) >> 1;      // tiles of this stream (0 if nsteps <= x)
+    const int my_tiles = my_je - my_jb;
     if (ok && my_tiles > 0) ok = wait_bar(&sh->o_ready[x], (my_tiles - 1) & 1, sh, 35 + x);
-    sh->ml[x][row_in_tile] = make_float2(m_used, l);
-    tc_fence_before();
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");  // the two softmax groups only
     tc_fence_after();
-    if (ok && sh->abort_flag == 0) {
-      const float2 mine = make_float2(m_used, l), other = sh->ml[x ^ 1][row_in_tile];
-      const float mstar = fmaxf(mine.x, other.x);
-      const float w_me = (mstar == -INFINITY) ? 0.f : exp2f(mine.x - mstar);
-      const float w_ot = (mstar == -INFINITY) ? 0.f : exp2f(other.x - mstar);
-      const float lsum = mine.y * w_me + other.y * w_ot;
-      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-      const float ca = (x == 0 ? w_me : w_ot) * inv, cb = (x == 0 ? w_ot : w_me) * inv;
+    if (m0 < si.q_len && ok && sh->abort_flag == 0) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = row < si.q_len;
-      // This group writes head_dim columns [x*D/2, (x+1)*D/2) of the row.  The tile is staged in
-      // shared memory (over Q, which no MMA reads any more) in the swizzled box layout and
-      // written by the TMA unit as full rows; a packed tile that reaches past the end of its
-      // sequence is stored row by row instead (the unit would write the neighbour's rows).
-      constexpr int DH = D / 2;
+      // The tile is staged in shared memory (over this stream's Q tile, which no MMA reads any
+      // more) in the swizzled box layout and written by the TMA unit as full rows; a packed
+      // tile that reaches past the end of its sequence is stored row by row instead (the unit
+      // would write the neighbour's rows).
       const bool via_tma = (p.cu_seqlens_q == nullptr) || (m0 + kBM <= si.q_len);
+      const uint32_t sOx = sQ + x * C::kTileBytes;
       T* og = reinterpret_cast<T*>(p.o) + si.q_boff * p.o_stride[0] +
-              (si.q_row0 + row) * p.o_stride[1] + (int64_t)h * p.o_stride[2] + x * DH;
-      const uint32_t tOa = tmem + lane_addr + 256 + x * DH, tOb = tOa + 128;
+              (si.q_row0 + row) * p.o_stride[1] + (int64_t)h * p.o_stride[2];
 #pragma unroll
-      for (int cc = 0; cc < DH / 32; ++cc) {
-        // a stream without tiles never wrote its accumulator
-        uint32_t ra[32], rb[32];
-        if (nsteps > 0) tmem_ld32(tOa + cc * 32, ra);
-        if (nsteps > 1) tmem_ld32(tOb + cc * 32, rb);
-        tmem_wait_ld();
-        if (nsteps <= 0) {
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t ra[32];
+        if (my_tiles > 0) {
+          tmem_ld32(tOx + cc * 32, ra);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) ra[i] = 0u;
         }
-        if (nsteps <= 1) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) rb[i] = 0u;
-        }
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
-          float f[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-            f[e] = __uint_as_float(ra[i + e]) * ca + __uint_as_float(rb[i + e]) * cb;
           uint4 v;
-          v.x = Elem<T>::pack(f[0], f[1]);
-          v.y = Elem<T>::pack(f[2], f[3]);
-          v.z = Elem<T>::pack(f[4], f[5]);
-          v.w = Elem<T>::pack(f[6], f[7]);
+          v.x = Elem<T>::pack(__uint_as_float(ra[i]) * inv, __uint_as_float(ra[i + 1]) * inv);
+          v.y = Elem<T>::pack(__uint_as_float(ra[i + 2]) * inv, __uint_as_float(ra[i + 3]) * inv);
+          v.z = Elem<T>::pack(__uint_as_float(ra[i + 4]) * inv, __uint_as_float(ra[i + 5]) * inv);
+          v.w = Elem<T>::pack(__uint_as_float(ra[i + 6]) * inv, __uint_as_float(ra[i + 7]) * inv);
           if (via_tma) {
-            const int col = x * DH + cc * 32 + i;          // first of 8 columns = one 16-byte chunk
-            st_shared_v4(sw128_addr(sQ + (col / 64) * (kBM * 128), row_in_tile, (col % 64) / 8), v);
+            const int col = cc * 32 + i;                   // first of 8 columns = one 16-byte chunk
+            st_shared_v4(sw128_addr(sOx + (col / 64) * (kBM * 128), row_in_tile, (col % 64) / 8), v);
           } else if (row_ok) {
             *reinterpret_cast<uint4*>(og + cc * 32 + i) = v;
           }
@@ -584,18 +619,19 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (via_tma) {
         fence_proxy_async();
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");
-        if (tid == 0) {
+        if (x == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+        if ((tid & 127) == 0) {
 #pragma unroll
           for (int bx = 0; bx < D / 64; ++bx)
-            tma_store_4d(&tmO, sQ + bx * (kBM * 128), bx * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+            tma_store_4d(&tmO, sOx + bx * (kBM * 128), bx * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
           tma_store_commit();
           tma_store_wait_read();
         }
       }
-      if (x == 0 && row_ok && p.lse2 != nullptr)
+      if (row_ok && p.lse2 != nullptr)
         p.lse2[si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
-               (int64_t)h * p.lse_stride[2]] = lsum > 0.f ? mstar + log2f(lsum) : -INFINITY;
+               (int64_t)h * p.lse_stride[2]] = l > 0.f ? m_used + log2f(l) : -INFINITY;
     }
 #ifdef FA_TRACE
     if (tid == 0) atomicAdd(&g_fwd_phase[3], (unsigned long long)(clock64() - ph_t3));
@@ -610,11 +646,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 8) tmem_dealloc(tmem, 512);
 #ifdef FA_TRACE
   if (tid == 0) {
-    // thread 0 is in softmax group A, whose stamps ph_t2/ph_t3 live in that branch: re-read through shared memory
     const long long t5 = clock64();
     atomicAdd(&g_fwd_phase[0], (unsigned long long)(ph_t1 - ph_t0));
     atomicAdd(&g_fwd_phase[4], (unsigned long long)(t5 - ph_t4));
-    atomicAdd(&g_fwd_phase[5], (unsigned long long)nsteps);
+    atomicAdd(&g_fwd_phase[5], (unsigned long long)((je0 - jb0) + (je1 - jb1)));
     atomicAdd(&g_fwd_phase[6], 1ull);
     atomicAdd(&g_fwd_phase[7], (unsigned long long)(t5 - ph_t0));
   }
@@ -662,7 +697,7 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
     set_error("fwd_sm100: cudaFuncSetAttribute(%d): %s", C::kSmemBytes, cudaGetErrorString(e));
     return FA_ERR_LAUNCH;
   }
-  dim3 grid((a.seqlen_q + kBM - 1) / kBM, a.heads_q, a.batch);
+  dim3 grid((a.seqlen_q + 2 * kBM - 1) / (2 * kBM), a.heads_q, a.batch);
   kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, a, cfg, nullptr, nullptr);
   return check_launch("fwd_sm100");
 }
@@ -731,7 +766,7 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
     set_error("fwd_int8_sm100: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return FA_ERR_LAUNCH;
   }
-  dim3 grid((S + kBM - 1) / kBM, H, B);
+  dim3 grid((S + 2 * kBM - 1) / (2 * kBM), H, B);
   kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, cfg, a.sq_scratch, a.s_k);
   return check_launch("fwd_int8_sm100");
 }

@@ -239,7 +239,8 @@ const char* fa_last_error(void);
 int fa_fwd_uses_tcgen05(const fa_attn_args* args);
 /* Status word of the tcgen05 kernels' bounded waits on `device`: 0, or the code of the wait
  * that ran out (the kernel then released its tensor memory and returned early, leaving its
- * outputs incomplete).  Synchronises the device. */
+ * outputs incomplete).  Once set the word stays set until the process ends, and every later
+ * tcgen05 launch on that device returns at its first wait.  Synchronises the device. */
 int fa_device_wait_status(int device);
 /* sizeof of an argument block as this library was compiled: 0 = fa_attn_args,
  * 1 = fa_decode_args, 2 = fa_int8_args.  Lets a foreign-language binding check its
