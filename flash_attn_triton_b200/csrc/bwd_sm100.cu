@@ -198,6 +198,7 @@ template <typename T, int D, bool kExtras>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
                       const fa_attn_args p, const ScoreCfg cfg) {
   using C = BCfg<D>;
   extern __shared__ unsigned char smem_raw[];
@@ -430,6 +431,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tmem_wait_ld();
       if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
       float pf[kHalfT];                              // P in fp32, kept for the dS phase
+      const float dist0 = (float)(q0 + off - key);   // query position - key position of column 0
       auto exp_body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
         if (kSlow) {
@@ -439,7 +441,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const int qp = q0 + i + off;
             float th = 0.f;
             float sc;
-            if (kExtras) sc = score_log2(cfg, slope, sv, qp, key, th) + st[i];
+            if (kExtras) sc = score_log2_dist(cfg, slope, sv, dist0 + (float)i, th) + st[i];
             else sc = fmaf(sv, cfg.scale_log2, st[i]);
             float pe = ex2(sc);
             if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
@@ -517,11 +519,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
 
     // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
+    // Each group stages its tile in shared memory (dV over V, dK over K: every MMA is done) in
+    // the swizzled box layout and lets the TMA unit write full rows; a packed tile that reaches
+    // past the end of its sequence is stored row by row instead.
     if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 49);
     if (ok) {
       tc_fence_after();
       const uint32_t tsrc = (x == 0 ? tdV : tdK) + lane_addr;
       const float mul = (x == 0) ? 1.f : cfg.scale;
+      const bool via_tma = (p.cu_seqlens_k == nullptr) || (n0 + kT <= si.k_len);
+      const uint32_t stg = (x == 0) ? sV : sK;
       T* base = (x == 0) ? reinterpret_cast<T*>(p.dv) + si.k_boff * p.dv_stride[0] +
                                (si.k_row0 + key) * p.dv_stride[1] + (int64_t)hk * p.dv_stride[2]
                          : reinterpret_cast<T*>(p.dk) + si.k_boff * p.dk_stride[0] +
@@ -536,16 +543,32 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-        if (key < si.k_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = Elem<T>::pack(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
-            v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
-            v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
-            v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = Elem<T>::pack(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+          v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+          v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+          v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+          if (via_tma) {
+            const int col = cc * 32 + i;
+            st_shared_v4(sw128_addr(stg + (col / 64) * (kT * 128), lrow, (col % 64) / 8), v);
+          } else if (key < si.k_len) {
             *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
           }
+        }
+      }
+      if (via_tma) {
+        fence_proxy_async();
+        if (x == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+        if ((tid & 127) == 0) {
+          const CUtensorMap* tm = (x == 0) ? &tmdV : &tmdK;
+#pragma unroll
+          for (int bx = 0; bx < D / 64; ++bx)
+            tma_store_4d(tm, stg + bx * (kT * 128), bx * 64, hk, (int)si.k_row0 + n0, (int)si.k_boff);
+          tma_store_commit();
+          tma_store_wait_read();
         }
       }
     }
@@ -572,7 +595,7 @@ template <typename T, int D, bool kExtras>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const fa_attn_args p, const ScoreCfg cfg) {
+                    const __grid_constant__ CUtensorMap tmdQ, const fa_attn_args p, const ScoreCfg cfg) {
   using C = BCfg<D>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -752,6 +775,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_ld();
       if ((warp & 3) == 0) FA_QTRACE(x, j, 2);
       // ---- exp phase: P (times the soft cap's tanh factor) in fp32 registers -------------
+      const float dist0 = (float)(qpos - k0);        // query position - key position of column 0
       float pf[kHalfT];
       auto exp_body = [&](auto slow_tag) {
         constexpr bool kSlow = decltype(slow_tag)::value;
@@ -762,7 +786,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int col = k0 + i;
             float th = 0.f;
             float sc;
-            if (kExtras) sc = score_log2(cfg, slope, sv, qpos, col, th) - l2;
+            if (kExtras) sc = score_log2_dist(cfg, slope, sv, dist0 - (float)i, th) - l2;
             else sc = fmaf(sv, cfg.scale_log2, -l2);
             float pe = ex2(sc);
             if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
@@ -815,11 +839,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if ((warp & 3) == 0) FA_QTRACE(x, j, 6);
     }
 
-    // ---- epilogue: dQ * softmax_scale; each group stores half of the head_dim columns -----
+    // ---- epilogue: dQ * softmax_scale; each group handles half of the head_dim columns -----
+    // The tile is staged over the resident Q tile (every MMA is done) and stored by the TMA
+    // unit; a packed tile that crosses the end of its sequence is stored row by row instead.
     if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 58);
     if (ok) {
       tc_fence_after();
       constexpr int DH = D / 2;
+      const bool via_tma = (p.cu_seqlens_q == nullptr) || (m0 + kT <= si.q_len);
       T* base = reinterpret_cast<T*>(p.dq) + si.q_boff * p.dq_stride[0] +
                 (si.q_row0 + row) * p.dq_stride[1] + (int64_t)h * p.dq_stride[2] + x * DH;
 #pragma unroll
@@ -832,16 +859,30 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
-        if (row < si.q_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            v.x = Elem<T>::pack(__uint_as_float(r[i]) * cfg.scale, __uint_as_float(r[i + 1]) * cfg.scale);
-            v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * cfg.scale, __uint_as_float(r[i + 3]) * cfg.scale);
-            v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * cfg.scale, __uint_as_float(r[i + 5]) * cfg.scale);
-            v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * cfg.scale, __uint_as_float(r[i + 7]) * cfg.scale);
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = Elem<T>::pack(__uint_as_float(r[i]) * cfg.scale, __uint_as_float(r[i + 1]) * cfg.scale);
+          v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * cfg.scale, __uint_as_float(r[i + 3]) * cfg.scale);
+          v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * cfg.scale, __uint_as_float(r[i + 5]) * cfg.scale);
+          v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * cfg.scale, __uint_as_float(r[i + 7]) * cfg.scale);
+          if (via_tma) {
+            const int col = x * DH + cc * 32 + i;
+            st_shared_v4(sw128_addr(sQ + (col / 64) * (kT * 128), lrow, (col % 64) / 8), v);
+          } else if (row < si.q_len) {
             *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
           }
+        }
+      }
+      if (via_tma) {
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (tid == 0) {
+#pragma unroll
+          for (int bx = 0; bx < D / 64; ++bx)
+            tma_store_4d(&tmdQ, sQ + bx * (kT * 128), bx * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
+          tma_store_commit();
+          tma_store_wait_read();
         }
       }
     }
@@ -874,7 +915,7 @@ bool make_map4(CUtensorMap* m, const void* base, const int64_t* stride, int rows
   return encode_tmap(m, base, 2, 4, dims, strides, box);
 }
 
-struct Maps { CUtensorMap q, k, v, dout; };
+struct Maps { CUtensorMap q, k, v, dout, dq, dk, dv; };
 
 bool make_maps(Maps& m, const fa_attn_args& a) {
   const bool packed = a.cu_seqlens_q != nullptr;
@@ -883,7 +924,10 @@ bool make_maps(Maps& m, const fa_attn_args& a) {
   return make_map4(&m.q, a.q, a.q_stride, qr, a.heads_q, a.batch, D, packed) &&
          make_map4(&m.k, a.k, a.k_stride, kr, a.heads_kv, a.batch, D, packed) &&
          make_map4(&m.v, a.v, a.v_stride, kr, a.heads_kv, a.batch, D, packed) &&
-         make_map4(&m.dout, a.dout, a.do_stride, qr, a.heads_q, a.batch, D, packed);
+         make_map4(&m.dout, a.dout, a.do_stride, qr, a.heads_q, a.batch, D, packed) &&
+         (a.dq == nullptr || make_map4(&m.dq, a.dq, a.dq_stride, qr, a.heads_q, a.batch, D, packed)) &&
+         (a.dk == nullptr || make_map4(&m.dk, a.dk, a.dk_stride, kr, a.heads_kv, a.batch, D, packed)) &&
+         (a.dv == nullptr || make_map4(&m.dv, a.dv, a.dv_stride, kr, a.heads_kv, a.batch, D, packed));
 }
 
 template <typename K> int set_smem_attr(K kern, int bytes, const char* what) {
@@ -897,7 +941,7 @@ template <typename K> int set_smem_attr(K kern, int bytes, const char* what) {
 
 template <typename T, int D>
 int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
-  Maps m;
+  Maps m{};
   if (!make_maps(m, a)) {
     set_error("bwd_dkdv_sm100: cuTensorMapEncodeTiled failed");
     return FA_ERR_LAUNCH;
@@ -906,13 +950,13 @@ int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   auto kern = extras ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
   if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dkdv_sm100")) return r;
   dim3 grid((a.seqlen_k + kT - 1) / kT, a.heads_kv, a.batch);
-  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, a, cfg);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, m.dk, m.dv, a, cfg);
   return check_launch("bwd_dkdv_sm100");
 }
 
 template <typename T, int D>
 int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
-  Maps m;
+  Maps m{};
   if (!make_maps(m, a)) {
     set_error("bwd_dq_sm100: cuTensorMapEncodeTiled failed");
     return FA_ERR_LAUNCH;
@@ -921,7 +965,7 @@ int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   auto kern = extras ? bwd_dq_sm100_kernel<T, D, true> : bwd_dq_sm100_kernel<T, D, false>;
   if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dq_sm100")) return r;
   dim3 grid((a.seqlen_q + kT - 1) / kT, a.heads_q, a.batch);
-  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, a, cfg);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, m.dq, a, cfg);
   return check_launch("bwd_dq_sm100");
 }
 

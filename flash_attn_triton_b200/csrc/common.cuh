@@ -115,25 +115,31 @@ template <int kEvery> __device__ __forceinline__ float ex2_mixed(float x, int i)
   return ex2(x);
 }
 
-// tanh through one exp2: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.
+// tanh through one exp2 and one reciprocal: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.
 __device__ __forceinline__ float fast_tanh(float x) {
-  float e = exp2f(x * (2.f * FA_LOG2E));
+  const float e = ex2(x * (2.f * FA_LOG2E));
   return 1.f - __fdividef(2.f, e + 1.f);
 }
 
-// Raw dot product -> score in the log2 domain (unmasked).  `th` returns tanh(s/softcap)
-// when softcap is on (needed by the backward), else 0.
-__device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
-                                            int kpos, float& th) {
+// Raw dot product -> score in the log2 domain (unmasked).  `dist` = q position - key position
+// as a float (exact: positions are far below 2^24; the tcgen05 kernels derive it from one
+// conversion per tile instead of one per element).  `th` returns tanh(s/softcap) when softcap
+// is on (needed by the backward), else 0.
+__device__ __forceinline__ float score_log2_dist(const ScoreCfg& c, float slope, float dot, float dist,
+                                                 float& th) {
   th = 0.f;
   if (!c.has_alibi && c.softcap == 0.f) return dot * c.scale_log2;
   float s = dot * c.scale;
-  if (c.has_alibi) s -= slope * fabsf((float)(qpos - kpos));
+  if (c.has_alibi) s = fmaf(-slope, fabsf(dist), s);
   if (c.softcap > 0.f) {
     th = fast_tanh(s * c.inv_softcap);
     s = c.softcap * th;
   }
   return s * FA_LOG2E;
+}
+__device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
+                                            int kpos, float& th) {
+  return score_log2_dist(c, slope, dot, (float)(qpos - kpos), th);
 }
 
 __device__ __forceinline__ bool visible(const ScoreCfg& c, int qpos, int kpos, int k_len) {

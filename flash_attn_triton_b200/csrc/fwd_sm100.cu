@@ -34,6 +34,7 @@
 // Every mbarrier wait is bounded; on timeout the CTA raises a device-side status word,
 // releases its TMEM and returns.
 #include <cstring>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -83,6 +84,7 @@ constexpr float kRescaleThreshold = 8.0f;
 #endif
 constexpr int kPolyEvery = FA_POLY_FWD;
 constexpr int kMaxStages = 8;
+constexpr int kSkSlots = 4;       // INT8 variant: key-scale tiles staged ahead
 
 template <int D> struct Cfg {
   static constexpr int kTileBytes = kBN * D * 2;                    // one Q/K/V tile
@@ -103,9 +105,11 @@ struct Shared {
   uint32_t tmem_base;
   volatile int abort_flag;
   // INT8 variant: key scales of the current score tiles, staged by warp 10
-  uint64_t sk_full[2];     // [score buffer] scales written
-  uint64_t sk_empty[2];    // [score buffer] scales consumed (256 arrivals: both groups, active or not)
-  alignas(16) float skt[2][kBN];
+  // (a ring of kSkSlots key tiles: with a causal mask one stream runs a whole step ahead of the
+  // other, and a slot is only released when BOTH groups are done with it)
+  uint64_t sk_full[kSkSlots];   // scales of the key tile of step j (slot j % kSkSlots) written
+  uint64_t sk_empty[kSkSlots];  // scales consumed (256 arrivals: both groups, active or not)
+  alignas(16) float skt[kSkSlots][kBN];
 };
 
 // Bounded wait on an mbarrier phase; the common "already complete" case costs one try_wait.
@@ -185,7 +189,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(smem_u32(&sh->kv_full[i]), 1);
       mbar_init(smem_u32(&sh->kv_empty[i]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kSkSlots; ++i) {
       mbar_init(smem_u32(&sh->sk_full[i]), 1);
       mbar_init(smem_u32(&sh->sk_empty[i]), 256);
     }
@@ -209,13 +213,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (kInt8 && warp == 10) {
       const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
       for (int j = 0; j < nsteps; ++j) {
-        const int buf = j & 1;
+        const int buf = j % kSkSlots;
         bool w = true;
-        if (lane == 0) w = wait_bar(&sh->sk_empty[buf], ((j >> 1) & 1) ^ 1, sh, 12);
+        if (lane == 0) w = wait_bar(&sh->sk_empty[buf], ((j / kSkSlots) & 1) ^ 1, sh, 12);
         if (!__all_sync(0xffffffffu, w)) break;
+        // staged pre-multiplied by softmax_scale * log2(e), so the consumers need two products
         for (int i = lane; i < kBN; i += 32) {
           const int col = (n_hi - 1 - j) * kBN + i;
-          sh->skt[buf][i] = col < si.k_len ? sk[bh_rows + col] : 1.f;
+          sh->skt[buf][i] = (col < si.k_len ? sk[bh_rows + col] : 1.f) * (cfg.scale * 1.44269504f);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->sk_full[buf]));
@@ -387,7 +392,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // INT8: scale of this query row and the row of key scales of this (batch, head)
     const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
     const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
-    const float qk_scale = cfg.scale * 1.44269504f;
     const int my_jb = x ? jb1 : jb0, my_je = x ? je1 : je0;
 #ifdef FA_TRACE
     long long ph_t2 = 0;
@@ -396,8 +400,8 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = kInt8 ? 0 : my_jb; j < (kInt8 ? nsteps : my_je) && ok; ++j) {
       if (kInt8 && (j < my_jb || j >= my_je)) {
         // not this stream's tile, but the slot of its key scales is released by both groups
-        ok = wait_bar(&sh->sk_full[j & 1], (j >> 1) & 1, sh, 37 + x);
-        if (ok) mbar_arrive(smem_u32(&sh->sk_empty[j & 1]));
+        ok = wait_bar(&sh->sk_full[j % kSkSlots], (j / kSkSlots) & 1, sh, 37 + x);
+        if (ok) mbar_arrive(smem_u32(&sh->sk_empty[j % kSkSlots]));
         continue;
       }
       const int t = j - my_jb;                       // index of the tile inside this stream
@@ -425,31 +429,50 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
       const bool prescaled = kExtras || masked || kInt8;
       if (kInt8) {
-        // (float(acc) * (s_q * s_k)) * (softmax_scale * log2 e), in the reference's order.
+        // score = float(acc) * s_q * (s_k * softmax_scale * log2 e): the same product as the
+        // reference's (acc * (s_q * s_k)) * (scale * log2 e) up to the last rounding.
         // |acc| <= 128*127*127 < 2^22, so int -> float is exact through the 1.5*2^23 bias
-        // (an integer add and a float subtract instead of a quarter-rate I2F).
-        ok = wait_bar(&sh->sk_full[j & 1], (j >> 1) & 1, sh, 37 + x);
+        // (an integer add and a float subtract instead of a quarter-rate I2F); packed pairs.
+        ok = wait_bar(&sh->sk_full[j % kSkSlots], (j / kSkSlots) & 1, sh, 37 + x);
         if (!ok) break;
-        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[j & 1][0]);
+        if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 6);
+        const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[j % kSkSlots][0]);
+        const float2 sq2 = make_float2(sq_row, sq_row), nb2 = make_float2(-12582912.0f, -12582912.0f);
+        // Two copies of the loop: without the per-element mask test there are no branches inside,
+        // so the compiler can issue the shared-memory loads of the scales in batches (each one
+        // takes hundreds of cycles while the tensor pipe streams its operands).
+        auto scale_tile = [&](auto mask_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 s4 = S4[cc * 8 + i4];
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const float4 s4 = S4[cc * 8 + i4];
+              const int i = i4 * 4;
+              const float2 a01 = f2add(make_float2(__uint_as_float(0x4B400000u + r[cc][i]),
+                                                   __uint_as_float(0x4B400000u + r[cc][i + 1])), nb2);
+              const float2 a23 = f2add(make_float2(__uint_as_float(0x4B400000u + r[cc][i + 2]),
+                                                   __uint_as_float(0x4B400000u + r[cc][i + 3])), nb2);
+              const float2 v01 = f2mul(f2mul(a01, sq2), make_float2(s4.x, s4.y));
+              const float2 v23 = f2mul(f2mul(a23, sq2), make_float2(s4.z, s4.w));
+              float v[4] = {v01.x, v01.y, v23.x, v23.y};
+              if (kMask) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int i = i4 * 4 + e;
-              const float acc = __uint_as_float(0x4B400000u + r[cc][i]) - 12582912.0f;
-              float v = __fmul_rn(__fmul_rn(acc, __fmul_rn(sq_row, sv[e])), qk_scale);
-              if (masked && !visible(cfg, qpos, k0 + cc * 32 + i, si.k_len)) v = -INFINITY;
-              r[cc][i] = __float_as_uint(v);
+                for (int e = 0; e < 4; ++e)
+                  if (!visible(cfg, qpos, k0 + cc * 32 + i + e, si.k_len)) v[e] = -INFINITY;
+              }
+#pragma unroll
+              for (int e = 0; e < 4; ++e) r[cc][i + e] = __float_as_uint(v[e]);
             }
           }
-        }
-        mbar_arrive(smem_u32(&sh->sk_empty[j & 1]));
+        };
+        if (masked) scale_tile(std::true_type{});
+        else scale_tile(std::false_type{});
+        mbar_arrive(smem_u32(&sh->sk_empty[j % kSkSlots]));
+        if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 7);
       } else if (prescaled) {
         // score pipeline and mask applied once, in place; values end up in the log2 domain
+        const float dist0 = (float)(qpos - k0);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
@@ -458,7 +481,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int col = k0 + cc * 32 + i;
             if (kExtras) {
               float th;
-              v = score_log2(cfg, slope, v, qpos, col, th);
+              v = score_log2_dist(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
             } else {
               v *= cfg.scale_log2;
             }
@@ -525,22 +548,23 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // ---- P = exp2(s - m), row sum, P -> TMEM in place over S ----------------------------
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
       if (kInt8) {
+        // Outlier keys make the rows peaky; with a stale reference maximum the dominant
+        // probability is 2^x instead of exactly 1, so its rounding to T would not cancel
+        // in O / l unless l sums the ROUNDED values that enter P@V.
+        const float2 nm2 = make_float2(-m_safe, -m_safe);
+        float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2(__uint_as_float(r[cc][i]) - m_safe);
-            const float p1 = ex2(__uint_as_float(r[cc][i + 1]) - m_safe);
-            pk[i >> 1] = Elem<T>::pack(p0, p1);
-            // Outlier keys make the rows peaky; with a stale reference maximum the dominant
-            // probability is 2^x instead of exactly 1, so its rounding to T would not cancel
-            // in O / l unless l sums the ROUNDED values that enter P@V.
-            const float2 pr = Elem<T>::unpack(pk[i >> 1]);
-            ps[(i >> 1) & 3] += pr.x + pr.y;
+            const float2 a = f2add(make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), nm2);
+            pk[i >> 1] = Elem<T>::pack(ex2(a.x), ex2(a.y));
+            acc2[(i >> 1) & 1] = f2add(acc2[(i >> 1) & 1], Elem<T>::unpack(pk[i >> 1]));
           }
           tmem_st16(tSx + cc * 16, pk);
         }
+        ps[0] = acc2[0].x; ps[1] = acc2[0].y; ps[2] = acc2[1].x; ps[3] = acc2[1].y;
       } else {
         // packed pairs: one FMA, two exponentials, one conversion and one add per two scores
         const float2 mul2 = make_float2(mul, mul), nm2 = make_float2(-m_safe, -m_safe);
