@@ -34,6 +34,7 @@
 // All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
 // K-major (contraction over head_dim) or MN-major (contraction over its rows) through
 // different descriptors.  Every mbarrier wait is bounded.
+#include <cstddef>
 #include <type_traits>
 
 #include "common.cuh"
@@ -114,6 +115,15 @@ template <int D> struct BCfg {
   static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
   static constexpr int kSmemBytes = kSmemTiles + 1024 + 8192;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+  // dQ kernel: the K ring is one stage deeper than the V ring.  K(k+1) is needed by S(k+1) at
+  // the START of step k while K(k) is still read by dQ(k) at its end; with two stages the slot
+  // of K(k+1) is only freed by dQ(k-1), and the load's latency landed on the critical path.
+  // This kernel only touches the barriers of BShared (512 bytes), not its statistics arrays.
+  static constexpr int kStagesK = (D == 128) ? 3 : 4;
+  static constexpr int kStagesV = (D == 128) ? 2 : 4;
+  static constexpr int kSmemTilesDq = (2 + kStagesK + kStagesV) * kTileBytes;
+  static constexpr int kSmemBytesDq = kSmemTilesDq + 1024 + 512;
+  static_assert(kSmemBytesDq <= 227 * 1024, "shared memory budget (dQ)");
 };
 
 struct BShared {
@@ -134,6 +144,7 @@ struct BShared {
   alignas(16) float delta[4][kT];  //                                       MINUS delta
 };
 static_assert(sizeof(BShared) <= 8192, "BShared must fit its reserve");
+static_assert(offsetof(BShared, lse) <= 512, "the dQ kernel reserves 512 bytes for the barriers");
 
 template <typename T> struct BFmt;
 template <> struct BFmt<__half> { static constexpr int code = 0; };
@@ -600,9 +611,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
+  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTilesDq);
   const uint32_t sQ = smem_u32(tiles), sdO = sQ + C::kTileBytes;
-  const uint32_t sRingK = sdO + C::kTileBytes, sRingV = sRingK + C::kStages * C::kTileBytes;
+  const uint32_t sRingK = sdO + C::kTileBytes, sRingV = sRingK + C::kStagesK * C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -628,7 +639,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(smem_u32(&sh->p_ready), 256);
     mbar_init(smem_u32(&sh->ds_ready), 256);
     mbar_init(smem_u32(&sh->acc_done), 1);
-    for (int i = 0; i < C::kStages; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&sh->full_a[i]), 1);
       mbar_init(smem_u32(&sh->full_b[i]), 1);
       mbar_init(smem_u32(&sh->empty_a[i]), 1);
@@ -663,22 +674,27 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         load_tile<D>(sQ, &tmQ, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
         load_tile<D>(sdO, &tmdO, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
       }
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < total; ++j) {
-        if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 51)) break;
-        {
-          const uint32_t bar = smem_u32(&sh->full_a[stage]);
-          mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingK + stage * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
-        }
-        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 51)) break;
-        {
-          const uint32_t bar = smem_u32(&sh->full_b[stage]);
-          mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingV + stage * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
-        }
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      // K runs one tile ahead of V: K(j+1) is requested before V(j)
+      auto load_k = [&](int j) {
+        const int stg = j % C::kStagesK;
+        if (!bwait_relaxed(&sh->empty_a[stg], ((j / C::kStagesK) & 1) ^ 1, sh, 51)) return false;
+        const uint32_t bar = smem_u32(&sh->full_a[stg]);
+        mbar_expect_tx(bar, C::kTileBytes);
+        load_tile<D>(sRingK + stg * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
+        return true;
+      };
+      auto load_v = [&](int j) {
+        const int stg = j % C::kStagesV;
+        if (!bwait_relaxed(&sh->empty_b[stg], ((j / C::kStagesV) & 1) ^ 1, sh, 51)) return false;
+        const uint32_t bar = smem_u32(&sh->full_b[stg]);
+        mbar_expect_tx(bar, C::kTileBytes);
+        load_tile<D>(sRingV + stg * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
+        return true;
+      };
+      bool pok = load_k(0);
+      for (int j = 0; j < total && pok; ++j) {
+        if (j + 1 < total) pok = load_k(j + 1);
+        if (pok) pok = load_v(j);
       }
     }
   } else if (warp == 9) {
@@ -693,8 +709,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (ok) ok = bwait(bar, parity, sh, code);
         tc_fence_after();
       };
-      auto slotK = [&](int j) { return sRingK + (j % C::kStages) * C::kTileBytes; };
-      auto slotV = [&](int j) { return sRingV + (j % C::kStages) * C::kTileBytes; };
+      auto slotK = [&](int j) { return sRingK + (j % C::kStagesK) * C::kTileBytes; };
+      auto slotV = [&](int j) { return sRingV + (j % C::kStagesV) * C::kTileBytes; };
       wq(&sh->res_full, 0, 53);
       wq(&sh->full_a[0], 0, 54);
       if (ok) {
@@ -708,12 +724,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mma_commit_lp(smem_u32(&sh->empty_b[0]), leader);
       }
       for (int k = 0; k < total && ok; ++k) {
-        const int st = k % C::kStages, st1 = (k + 1) % C::kStages;
-        const uint32_t ph1 = ((k + 1) / C::kStages) & 1;
+        const int stK = k % C::kStagesK, stK1 = (k + 1) % C::kStagesK, stV1 = (k + 1) % C::kStagesV;
+        const uint32_t phK1 = ((k + 1) / C::kStagesK) & 1, phV1 = ((k + 1) / C::kStagesV) & 1;
         const bool more = k + 1 < total;
         FA_QTRACE(2, k, 0);
         if (more) {
-          wq(&sh->full_a[st1], ph1, 54);
+          wq(&sh->full_a[stK1], phK1, 54);
           if (!ok) break;
           mma_kmajor<D>(tS + ((k + 1) & 1) * kT, sQ, slotK(k + 1), idesc_s, leader);   // S(k+1)
           mma_commit_lp(smem_u32(&sh->s_full[(k + 1) & 1]), leader);
@@ -723,14 +739,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         FA_QTRACE(2, k, 2);
         mma_from_tmem<D>(tdQ, tdP, slotK(k), idesc_acc, k > 0, leader);        // dQ += dS(k) K(k)
-        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        mma_commit_lp(smem_u32(&sh->empty_a[stK]), leader);
         FA_QTRACE(2, k, 3);
         if (more) {
-          wq(&sh->full_b[st1], ph1, 54);
+          wq(&sh->full_b[stV1], phV1, 54);
           if (!ok) break;
           mma_kmajor<D>(tdP, sdO, slotV(k + 1), idesc_s, leader);              // dP(k+1)
           mma_commit_lp(smem_u32(&sh->dp_full), leader);
-          mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
+          mma_commit_lp(smem_u32(&sh->empty_b[stV1]), leader);
         }
         FA_QTRACE(2, k, 4);
       }
@@ -963,9 +979,9 @@ int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   }
   const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
   auto kern = extras ? bwd_dq_sm100_kernel<T, D, true> : bwd_dq_sm100_kernel<T, D, false>;
-  if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dq_sm100")) return r;
+  if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytesDq, "bwd_dq_sm100")) return r;
   dim3 grid((a.seqlen_q + kT - 1) / kT, a.heads_q, a.batch);
-  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, m.dq, a, cfg);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytesDq, st>>>(m.q, m.k, m.v, m.dout, m.dq, a, cfg);
   return check_launch("bwd_dq_sm100");
 }
 
