@@ -467,8 +467,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint32_t* rr = i < 32 ? r0 : r1;
             const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2,
                                    make_float2(st[i], st[i + 1]));
-            pf[i] = ex2_mixed<kPolyEvery>(a.x, i);
-            pf[i + 1] = ex2_mixed<kPolyEvery>(a.y, i + 1);
+            const float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
+            pf[i] = pe.x;
+            pf[i + 1] = pe.y;
           }
         }
       };
@@ -809,7 +810,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (kExtras && cfg.softcap > 0.f) pe *= (1.f - th * th);
             pf[i] = pe;
           } else {
-            pf[i] = ex2_mixed<kPolyEvery>(fmaf(sv, cfg.scale_log2, -l2), i);
+            pf[i] = ex2(fmaf(sv, cfg.scale_log2, -l2));
           }
         }
       };
@@ -819,8 +820,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int i = 0; i < kHalfT; i += 2) {
           const uint32_t* rr = i < 32 ? r0 : r1;
           const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2, nl);
-          pf[i] = ex2_mixed<kPolyEvery>(a.x, i);
-          pf[i + 1] = ex2_mixed<kPolyEvery>(a.y, i + 1);
+          const float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
+          pf[i] = pe.x;
+          pf[i + 1] = pe.y;
         }
       };
       if (kExtras || masked) exp_body(std::true_type{});

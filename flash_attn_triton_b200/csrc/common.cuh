@@ -95,24 +95,32 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// 2^x on the FMA pipe instead of the special-function unit (which is the scarcer resource next
-// to the tensor cores: 16 results per clock per SM): round-to-nearest split x = n + f with
+// 2^x of a pair on the FMA pipe instead of the special-function unit (16 results per clock per
+// SM, as scarce as the tensor cores in these kernels): round-to-nearest split x = n + f with
 // f in [-0.5, 0.5], a degree-3 minimax polynomial for 2^f (relative error 1.0e-4, below the
-// rounding of the 16-bit probabilities it feeds), n added into the exponent field.
-// Arguments below -125 return 2^-125 rather than 0, so masked (-inf) scores must not come here.
-__device__ __forceinline__ float ex2_fma(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(0.05500862f, f, 0.24221021f);
-  p = fmaf(p, f, 0.6932829f);
-  p = fmaf(p, f, 1.f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+// rounding of the 16-bit probabilities it feeds), n added into the exponent field; packed fp32,
+// about 5.5 issue slots per result.  Arguments below -125 return 2^-125 rather than 0, so masked
+// (-inf) scores must not come here.  Measured: no gain in any kernel (the element-wise warps are
+// short of issue slots too), so the kernels keep kEvery = 0.
+__device__ __forceinline__ float2 ex2_fma2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f), nmagic = make_float2(-12582912.f, -12582912.f);
+  const float2 t = f2add(x, magic);
+  const float2 n = f2add(t, nmagic);
+  const float2 f = f2fma(n, make_float2(-1.f, -1.f), x);
+  float2 p = f2fma(make_float2(0.05500862f, 0.05500862f), f, make_float2(0.24221021f, 0.24221021f));
+  p = f2fma(p, f, make_float2(0.6932829f, 0.6932829f));
+  p = f2fma(p, f, make_float2(1.f, 1.f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
 }
-// Every kEvery-th exponential of an unrolled loop (index i) goes to ex2_fma (0 = none).
-template <int kEvery> __device__ __forceinline__ float ex2_mixed(float x, int i) {
-  if (kEvery > 0 && (i % (kEvery > 0 ? kEvery : 1)) == (kEvery > 0 ? kEvery : 1) - 1) return ex2_fma(x);
-  return ex2(x);
+// Every kEvery-th PAIR (index pair) of an unrolled loop goes to ex2_fma2 (0 = none).
+template <int kEvery> __device__ __forceinline__ float2 ex2_pair(float2 a, int pair) {
+  if (kEvery > 0 && (pair % (kEvery > 0 ? kEvery : 1)) == (kEvery > 0 ? kEvery : 1) - 1) return ex2_fma2(a);
+  return make_float2(ex2(a.x), ex2(a.y));
 }
 
 // tanh through one exp2 and one reciprocal: 1 - 2/(exp(2x)+1); saturates cleanly to +-1.

@@ -576,9 +576,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int i = 0; i < 32; i += 2) {
             const float2 a = f2fma(make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), mul2, nm2);
             // the unmasked fast path holds no -inf scores: part of its exponentials may run on the FMA pipe
-            float2 pe;
-            pe.x = prescaled ? ex2(a.x) : ex2_mixed<kPolyEvery>(a.x, i);
-            pe.y = prescaled ? ex2(a.y) : ex2_mixed<kPolyEvery>(a.y, i + 1);
+            const float2 pe = prescaled ? make_float2(ex2(a.x), ex2(a.y)) : ex2_pair<kPolyEvery>(a, i >> 1);
             pk[i >> 1] = Elem<T>::pack(pe.x, pe.y);
             acc2[(i >> 1) & 1] = f2add(acc2[(i >> 1) & 1], pe);
           }
