@@ -12,11 +12,12 @@
 // Both kernels are software-pipelined through the ORDER in which the MMA warp feeds the (in-
 // order) tensor pipe, so that the element-wise warps always work while independent MMAs run:
 //
-//   dK/dV, per query tile i:   S(i+1) | dK += dS(i)^T Q(i) | dP(i+1) | dV += P(i+1)^T dO(i+1)
-//       exp phase  of tile i+1 (P = exp2(S - lse), stored over S) runs during dK(i), dP(i+1);
-//       dS  phase  of tile i+1 (dS = P (dP - delta), stored over dP) runs during dV(i+1), S(i+2).
-//       S(i+1) may overwrite P(i) and dP(i+1) may overwrite dS(i) because their last readers,
-//       dV(i) and dK(i), precede them in the pipe.
+//   dK/dV, per query tile i:   S(i) | dK += dS(i-1)^T Q(i-1) | dV += P(i-1)^T dO(i-1) | dP(i)
+//       S(i) and dP(i) take turns in ONE fp32 TMEM region, P and dS (16-bit) have regions of
+//       their own: the element-wise warps hand the fp32 region back as soon as its contents
+//       are in their registers, so S(i+1) does not wait for the MMA that consumes P(i).
+//       exp phase  of tile i (P = exp2(S - lse))   runs during dK(i-1), dV(i-1), dP(i);
+//       dS  phase  of tile i (dS = P (dP - delta)) runs during S(i+1).
 //   dQ, per key tile k:        S(k+1) -> other S buffer | dQ += dS(k) K(k) | dP(k+1)
 //       S is double-buffered (P is no MMA operand here, nothing orders a single buffer).
 //
@@ -29,7 +30,7 @@
 //                    tile into shared memory (dK/dV kernel only)
 //   warp 11          idle (completes the warpgroup for setmaxnreg)
 //
-// TMEM, dK/dV kernel: S^T | dP^T | dV | dK     (4 x 128 columns).
+// TMEM, dK/dV kernel: S^T or dP^T (128 columns) | P^T (64) | dS^T (64) | dV (128) | dK (128).
 // TMEM, dQ kernel:    S[0] | S[1] | dP | dQ    (4 x 128 columns).
 // All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
 // K-major (contraction over head_dim) or MN-major (contraction over its rows) through
@@ -113,7 +114,11 @@ template <int D> struct BCfg {
   static constexpr int kBoxes = D / 64;
   static constexpr int kStages = (D == 128) ? 2 : 4;  // depth of each streamed-tile ring
   static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
-  static constexpr int kSmemBytes = kSmemTiles + 1024 + 8192;
+  // dK/dV kernel: 128 x 16 operand tiles that carry the row statistics into the GEMMs
+  // (two constant ones on the key side, one per ring stage on the query side)
+  static constexpr int kAugBytes = kT * 16 * 2;
+  static constexpr int kAugTotal = (2 + kStages) * kAugBytes;
+  static constexpr int kSmemBytes = kSmemTiles + kAugTotal + 1024 + 8192;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   // dQ kernel: the K ring is one stage deeper than the V ring.  K(k+1) is needed by S(k+1) at
   // the START of step k while K(k) is still read by dQ(k) at its end; with two stages the slot
@@ -137,6 +142,9 @@ struct BShared {
   uint64_t dp_full;       // dP computed
   uint64_t p_ready;       // P written back (256 arrivals; dK/dV kernel)
   uint64_t ds_ready;      // dS written back (256 arrivals)
+  uint64_t r_free;        // dK/dV kernel: scores, then dP, read out of their shared TMEM region (256 arrivals)
+  uint64_t p_free;        // dK/dV kernel: dV MMA that read P finished
+  uint64_t ds_free;       // dK/dV kernel: dK MMA that read dS finished
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -188,14 +196,14 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_smem, uin
 
 // acc(128 x D) += A(128 x 128, fp16 pairs in TMEM) * B(128 rows x D, MN-major smem tile).
 // A is stored as two 32-column blocks (written by the two element-wise groups) at
-// a_tmem and a_tmem + 64.
-template <int D>
+// a_tmem and a_tmem + kGroupStride.
+template <int D, int kGroupStride = 64>
 __device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
                                               uint32_t idesc, bool accumulate, uint32_t leader) {
   const uint64_t db = make_smem_desc(b_smem, kT * 128, 1024);
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
-    const uint32_t a = a_tmem + (kk / 4) * 64 + (kk % 4) * 8;
+    const uint32_t a = a_tmem + (kk / 4) * kGroupStride + (kk % 4) * 8;
     mma_f16_ts_lp(d_tmem, a, db + ((kk * 2048) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u, leader);
   }
 }
@@ -215,9 +223,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles);
+  BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles + C::kAugTotal);
   const uint32_t sK = smem_u32(tiles), sV = sK + C::kTileBytes;
   const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStages * C::kTileBytes;
+  // statistics operands: [0] key side of the score GEMM, [1] key side of the dP GEMM,
+  // [2 + stage] query side (written per streamed query tile by the statistics warp)
+  unsigned char* aug = tiles + C::kSmemTiles;
+  const uint32_t sAug = sK + C::kSmemTiles;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -245,6 +257,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&sh->dp_full), 1);
     mbar_init(smem_u32(&sh->p_ready), 256);
     mbar_init(smem_u32(&sh->ds_ready), 256);
+    mbar_init(smem_u32(&sh->r_free), 256);
+    mbar_init(smem_u32(&sh->p_free), 1);
+    mbar_init(smem_u32(&sh->ds_free), 1);
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(smem_u32(&sh->full_a[i]), 1);
@@ -256,6 +271,27 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     sh->abort_flag = 0;
     fence_barrier_init();
   }
+  {
+    // Statistics operands, no-swizzle K-major layout: columns 0-7 of row r at
+    // (r / 8) * 128 + (r % 8) * 16, columns 8-15 (always zero) 2048 bytes further.
+    // Query side, per row:  [l_hi, l_hi, l_lo, l_lo, d_hi, d_lo, 0, 0]  with l = -lse2, d = -delta
+    // key side, scores:     [w_hi, w_lo, w_hi, w_lo, 0, 0, 0, 0]        with w = 1 / scale_log2
+    // key side, dP:         [0, 0, 0, 0, 1, 1, 0, 0]
+    // so the score GEMM yields S - lse2 / scale_log2 and the dP GEMM dP - delta.
+    const float w = 1.f / cfg.scale_log2;
+    const T w_hi = Elem<T>::from_f(w), w_lo = Elem<T>::from_f(w - Elem<T>::to_f(w_hi));
+    const uint32_t wp = (uint32_t)(*reinterpret_cast<const uint16_t*>(&w_hi)) |
+                        ((uint32_t)(*reinterpret_cast<const uint16_t*>(&w_lo)) << 16);
+    const uint32_t ones = Elem<T>::pack(1.f, 1.f);
+    uint4* a4 = reinterpret_cast<uint4*>(aug);
+    for (int i = tid; i < C::kAugTotal / 16; i += kBwdThreads) {
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (i < kT) val = make_uint4(wp, wp, 0u, 0u);
+      else if (i >= C::kAugBytes / 16 && i < C::kAugBytes / 16 + kT) val = make_uint4(0u, 0u, ones, 0u);
+      a4[i] = val;
+    }
+    fence_proxy_async();
+  }
   if (warp == 8) {
     tmem_alloc(smem_u32(&sh->tmem_base), 512);
     tmem_relinquish();
@@ -264,7 +300,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
+  // TMEM: R (128 fp32 columns, holds S^T then dP^T of a tile in turn) | P^T (64) | dS^T (64) | dV | dK
+  const uint32_t tR = tmem, tP = tmem + 128, tdS = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
 
   if (warp == 11) {
     reg_dealloc<kRegsService>();
@@ -286,18 +323,18 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-        // dO's slot frees first (after dV of the tile that held it), Q's after dK
-        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
-        {
-          const uint32_t bar = smem_u32(&sh->full_b[stage]);
-          mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
-        }
+        // Q's slot frees first (after dK of the tile that held it) and is needed first (by S)
         if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 41)) break;
         {
           const uint32_t bar = smem_u32(&sh->full_a[stage]);
           mbar_expect_tx(bar, C::kTileBytes);
           load_tile<D>(sRingQ + stage * C::kTileBytes, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        }
+        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
+        {
+          const uint32_t bar = smem_u32(&sh->full_b[stage]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
@@ -312,20 +349,28 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bool w = true;
       if (lane == 0) w = bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 42);
       if (!__all_sync(0xffffffffu, w)) break;
+      uint4* q4 = reinterpret_cast<uint4*>(aug + (2 + stage) * C::kAugBytes);
       for (int i = lane; i < kT; i += 32) {
         const int row = m * kT + i;
-        // stored NEGATED: the consumers add them with packed FMAs / adds
-        float nl2 = -INFINITY, ndl = 0.f;
+        // NEGATED; rows that do not exist or see no key get a large finite value instead of
+        // infinity (an infinity would meet the zeros of the other GEMM's key-side operand): P = 0
+        float nl2 = -60000.f, ndl = 0.f;
         if (row < si.q_len) {
           const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
                               (int64_t)hq * p.lse_stride[2];
           nl2 = -p.lse2[idx];
           ndl = -p.delta[idx];
-          if (nl2 == INFINITY) nl2 = -INFINITY;  // row without visible keys: P = 0
+          if (!(fabsf(nl2) < 60000.f)) nl2 = -60000.f;  // row without visible keys: P = 0
         }
-        sh->lse[stage][i] = nl2;
-        sh->delta[stage][i] = ndl;
+        if (kExtras) sh->lse[stage][i] = nl2 == -60000.f ? -INFINITY : nl2;  // added after the soft cap by the element-wise warps
+        const float lf = kExtras ? 0.f : nl2;
+        const T l_hi = Elem<T>::from_f(lf), l_lo = Elem<T>::from_f(lf - Elem<T>::to_f(l_hi));
+        const T d_hi = Elem<T>::from_f(ndl), d_lo = Elem<T>::from_f(ndl - Elem<T>::to_f(d_hi));
+        const uint32_t lh = *reinterpret_cast<const uint16_t*>(&l_hi), ll = *reinterpret_cast<const uint16_t*>(&l_lo);
+        const uint32_t dh = *reinterpret_cast<const uint16_t*>(&d_hi), dl = *reinterpret_cast<const uint16_t*>(&d_lo);
+        q4[i] = make_uint4(lh | (lh << 16), ll | (ll << 16), dh | (dl << 16), 0u);
       }
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->stat_full[stage]));
       if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -345,52 +390,63 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       };
       auto slotQ = [&](int it) { return sRingQ + (it % C::kStages) * C::kTileBytes; };
       auto slotO = [&](int it) { return sRingO + (it % C::kStages) * C::kTileBytes; };
+      // Issue order per tile i:  S(i) | dK(i-1) | dV(i-1) | dP(i).  S(i) and dP(i) take turns in
+      // one TMEM region: each is issued once the element-wise warps have read its predecessor
+      // into registers (r_free), so the exp2 phase of tile i runs under dK(i-1), dV(i-1), dP(i)
+      // and its dS phase under S(i+1).  dK goes first because it frees Q's ring slot, which the
+      // very next S needs again.
+      const uint64_t dstat_s = make_smem_desc_noswizzle(sAug, 2048, 128);
+      const uint64_t dstat_dp = make_smem_desc_noswizzle(sAug + C::kAugBytes, 2048, 128);
       wq(&sh->res_full, 0, 43);
-      wq(&sh->full_a[0], 0, 44);
-      if (ok) {
-        mma_kmajor<D>(tS, sK, slotQ(0), idesc_s, leader);                      // S^T(0) = K Q(0)^T
-        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
-      }
-      wq(&sh->full_b[0], 0, 44);
-      if (ok) {
-        mma_kmajor<D>(tdP, sV, slotO(0), idesc_s, leader);                     // dP^T(0) = V dO(0)^T
-        mma_commit_lp(smem_u32(&sh->dp_full), leader);
-      }
-      wq(&sh->p_ready, 0, 45);
-      if (ok) {
-        mma_from_tmem<D>(tdV, tS, slotO(0), idesc_acc, false, leader);         // dV = P(0)^T dO(0)
-        mma_commit_lp(smem_u32(&sh->empty_b[0]), leader);
-      }
       for (int i = 0; i < total && ok; ++i) {
-        const int st = i % C::kStages, st1 = (i + 1) % C::kStages;
-        const uint32_t ph1 = ((i + 1) / C::kStages) & 1;
-        const bool more = i + 1 < total;
+        const int st = i % C::kStages;
+        const uint32_t ph = (i / C::kStages) & 1;
         FA_BTRACE(2, i, 0);
-        if (more) {
-          wq(&sh->full_a[st1], ph1, 44);
-          if (!ok) break;
-          mma_kmajor<D>(tS, sK, slotQ(i + 1), idesc_s, leader);                // S^T(i+1)
-          mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
-        }
-        FA_BTRACE(2, i, 1);
-        wq(&sh->ds_ready, i & 1, 46);
+        wq(&sh->full_a[st], ph, 44);
+        wq(&sh->stat_full[st], ph, 47);
+        if (i > 0) wq(&sh->r_free, 1, 49);                                     // dP(i-1) read out
         if (!ok) break;
-        FA_BTRACE(2, i, 2);
-        mma_from_tmem<D>(tdK, tdP, slotQ(i), idesc_acc, i > 0, leader);        // dK += dS(i)^T Q(i)
-        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
-        FA_BTRACE(2, i, 3);
-        if (more) {
-          wq(&sh->full_b[st1], ph1, 44);
+        const uint64_t dstat = make_smem_desc_noswizzle(sAug + (2 + st) * C::kAugBytes, 2048, 128);
+        mma_kmajor<D>(tR, sK, slotQ(i), idesc_s, leader);                      // S^T(i) = K Q(i)^T
+        if (!kExtras) mma_f16_ss_lp(tR, dstat_s, dstat, idesc_s, 1u, leader);  //          - lse2 / scale_log2
+        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+        FA_BTRACE(2, i, 1);
+        if (i > 0) {
+          const int sp = (i - 1) % C::kStages;
+          wq(&sh->ds_ready, (i - 1) & 1, 46);
           if (!ok) break;
-          mma_kmajor<D>(tdP, sV, slotO(i + 1), idesc_s, leader);               // dP^T(i+1)
-          mma_commit_lp(smem_u32(&sh->dp_full), leader);
+          FA_BTRACE(2, i, 2);
+          mma_from_tmem<D, 32>(tdK, tdS, slotQ(i - 1), idesc_acc, i > 1, leader);  // dK += dS(i-1)^T Q(i-1)
+          mma_commit_lp(smem_u32(&sh->empty_a[sp]), leader);
+          mma_commit_lp(smem_u32(&sh->ds_free), leader);
+          FA_BTRACE(2, i, 3);
+          wq(&sh->p_ready, (i - 1) & 1, 45);
+          if (!ok) break;
+          mma_from_tmem<D, 32>(tdV, tP, slotO(i - 1), idesc_acc, i > 1, leader);   // dV += P(i-1)^T dO(i-1)
+          mma_commit_lp(smem_u32(&sh->empty_b[sp]), leader);
+          mma_commit_lp(smem_u32(&sh->p_free), leader);
           FA_BTRACE(2, i, 4);
-          wq(&sh->p_ready, (i + 1) & 1, 45);
-          if (!ok) break;
-          FA_BTRACE(2, i, 5);
-          mma_from_tmem<D>(tdV, tS, slotO(i + 1), idesc_acc, true, leader);    // dV += P(i+1)^T dO(i+1)
-          mma_commit_lp(smem_u32(&sh->empty_b[st1]), leader);
-          FA_BTRACE(2, i, 6);
+        }
+        wq(&sh->full_b[st], ph, 44);
+        wq(&sh->r_free, 0, 49);                                                // S(i) read out
+        if (!ok) break;
+        FA_BTRACE(2, i, 5);
+        mma_kmajor<D>(tR, sV, slotO(i), idesc_s, leader);                      // dP^T(i) = V dO(i)^T
+        mma_f16_ss_lp(tR, dstat_dp, dstat, idesc_s, 1u, leader);               //           - delta
+        mma_commit_lp(smem_u32(&sh->dp_full), leader);
+        FA_BTRACE(2, i, 6);
+      }
+      if (ok) {
+        const int i = total, sp = (i - 1) % C::kStages;
+        wq(&sh->ds_ready, (i - 1) & 1, 46);
+        if (ok) {
+          mma_from_tmem<D, 32>(tdK, tdS, slotQ(i - 1), idesc_acc, i > 1, leader);
+          mma_commit_lp(smem_u32(&sh->empty_a[sp]), leader);
+        }
+        wq(&sh->p_ready, (i - 1) & 1, 45);
+        if (ok) {
+          mma_from_tmem<D, 32>(tdV, tP, slotO(i - 1), idesc_acc, i > 1, leader);
+          mma_commit_lp(smem_u32(&sh->empty_b[sp]), leader);
         }
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
@@ -403,7 +459,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int lrow = (warp & 3) * 32 + lane;         // TMEM lane = key inside the tile
     const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tSx = tS + lane_addr + x * kHalfT, tdPx = tdP + lane_addr + x * kHalfT;
+    const uint32_t tRx = tR + lane_addr + x * kHalfT;            // fp32 scores / dP: this group's 64 columns
+    const uint32_t tPx = tP + lane_addr + x * (kHalfT / 2);      // P^T, dS^T as 16-bit pairs: 32 columns each
+    const uint32_t tdSx = tdS + lane_addr + x * (kHalfT / 2);
     bool ok = true;
     for (int it = 0; it < total && ok; ++it) {
       const int stage = it % C::kStages;
@@ -416,13 +474,14 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
 
       if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
-      // The statistics are fetched into registers BEFORE the wait for the scores: shared-memory
-      // loads issued while the tensor pipe streams its operands take hundreds of cycles, and
-      // here that latency hides behind the wait.
-      ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
-      if (!ok) break;
-      float st[kHalfT];                              // -lse, later -delta, of this thread's columns
-      {
+      // Only the feature path still needs the LSE per column (it is added after the soft cap);
+      // it is fetched into registers BEFORE the wait for the scores: shared-memory loads issued
+      // while the tensor pipe streams its operands take hundreds of cycles, and here that
+      // latency hides behind the wait.  Otherwise the GEMMs deliver S - lse and dP - delta.
+      float st[kHalfT];                              // -lse, later the soft cap's tanh factor
+      if (kExtras) {
+        ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
+        if (!ok) break;
         const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
 #pragma unroll
         for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
@@ -437,9 +496,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
       // ---- exp phase: P = exp2(score - lse), written back over S as T pairs -------------
       uint32_t r0[32], r1[32];
-      tmem_ld32(tSx, r0);
-      tmem_ld32(tSx + 32, r1);
+      tmem_ld32(tRx, r0);
+      tmem_ld32(tRx + 32, r1);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->r_free));            // the scores are in registers: dP may take the region
       if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
       float pf[kHalfT];                              // P in fp32, kept for the dS phase
       const float dist0 = (float)(q0 + off - key);   // query position - key position of column 0
@@ -453,7 +514,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             float th = 0.f;
             float sc;
             if (kExtras) sc = score_log2_dist(cfg, slope, sv, dist0 + (float)i, th) + st[i];
-            else sc = fmaf(sv, cfg.scale_log2, st[i]);
+            else sc = sv * cfg.scale_log2;
             float pe = ex2(sc);
             if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
             pf[i] = pe;
@@ -465,8 +526,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
           for (int i = 0; i < kHalfT; i += 2) {
             const uint32_t* rr = i < 32 ? r0 : r1;
-            const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2,
-                                   make_float2(st[i], st[i + 1]));
+            const float2 a = f2mul(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2);
             const float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
             pf[i] = pe.x;
             pf[i + 1] = pe.y;
@@ -476,13 +536,19 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (kExtras || masked) exp_body(std::true_type{});
       else exp_body(std::false_type{});
       if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
+      // P(it-1) is read by its dV MMA until p_free completes
+      if (it > 0) {
+        ok = bwait(&sh->p_free, (it - 1) & 1, sh, 50);
+        if (!ok) break;
+        tc_fence_after();
+      }
       {
         uint32_t pk[16];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
-          tmem_st16(tSx + c * 16, pk);
+          tmem_st16(tPx + c * 16, pk);
         }
       }
       if (kExtras && cfg.softcap > 0.f) {
@@ -494,36 +560,35 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->p_ready));
       if ((warp & 3) == 0) FA_BTRACE(x, it, 5);
-      {
-        // delta replaces lse in the same registers, again ahead of the wait it hides behind
-        const float4* D4 = reinterpret_cast<const float4*>(&sh->delta[stage][x * kHalfT]);
-#pragma unroll
-        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
-          const float4 d4 = D4[i4];
-          st[i4 * 4] = d4.x; st[i4 * 4 + 1] = d4.y; st[i4 * 4 + 2] = d4.z; st[i4 * 4 + 3] = d4.w;
-        }
-      }
 
       // ---- dS phase: dS = P (dP - delta), written back over dP ---------------------------
       ok = bwait(&sh->dp_full, it & 1, sh, 48);
       if (!ok) break;
       tc_fence_after();
       if ((warp & 3) == 0) FA_BTRACE(x, it, 6);
+      tmem_ld32(tRx, r0);
+      tmem_ld32(tRx + 32, r1);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->r_free));            // dP is in registers: the next S may take the region
+      uint32_t pk0[16], pk1[16];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tdPx + c * 32, r0);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int e = c * 32 + 2 * i;
-          const float2 d = f2add(make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])),
-                                 make_float2(st[e], st[e + 1]));
-          const float2 ds = f2mul(make_float2(pf[e], pf[e + 1]), d);
-          pk[i] = Elem<T>::pack(ds.x, ds.y);
-        }
-        tmem_st16(tdPx + c * 16, pk);
+      for (int i = 0; i < 32; ++i) {
+        const int e = 2 * i;
+        const uint32_t* rr = e < 32 ? r0 : r1;
+        const float2 ds = f2mul(make_float2(pf[e], pf[e + 1]),
+                                make_float2(__uint_as_float(rr[e & 31]), __uint_as_float(rr[(e & 31) + 1])));
+        if (i < 16) pk0[i] = Elem<T>::pack(ds.x, ds.y);
+        else pk1[i - 16] = Elem<T>::pack(ds.x, ds.y);
       }
+      // dS(it-1) is read by its dK MMA until ds_free completes
+      if (it > 0) {
+        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 51);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st16(tdSx, pk0);
+      tmem_st16(tdSx + 16, pk1);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->ds_ready));
@@ -964,7 +1029,10 @@ int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
     set_error("bwd_dkdv_sm100: cuTensorMapEncodeTiled failed");
     return FA_ERR_LAUNCH;
   }
-  const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
+  // The plain variant folds -lse2 / scale_log2 into the score GEMM through 16-bit operands; a
+  // scale so small that its reciprocal leaves the fp16 range takes the feature variant, whose
+  // element-wise warps add the LSE themselves.
+  const bool extras = cfg.has_alibi || cfg.softcap > 0.f || !(cfg.scale_log2 > 2e-5f);
   auto kern = extras ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
   if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dkdv_sm100")) return r;
   dim3 grid((a.seqlen_k + kT - 1) / kT, a.heads_kv, a.batch);

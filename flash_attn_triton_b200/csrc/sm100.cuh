@@ -234,6 +234,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
          ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | (uint64_t)((smem_addr >> 4) & 0x3FFF);
 }
 
+// Descriptor of a K-major operand WITHOUT swizzle: core matrices of 8 rows x 16 bytes stored
+// contiguously (128 bytes each); LBO = distance between core matrices that are neighbours along
+// K, SBO = distance between neighbours along M/N.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                            uint32_t sbo_bytes) {
+  return kDescVersion | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) |
+         ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | (uint64_t)((smem_addr >> 4) & 0x3FFF);
+}
+
 // Instruction descriptor for kind::f16 / kind::i8 (dense, no negate, no saturate).
 //   c_format: 0 f16, 1 f32, 2 s32;  ab_format: f16 kinds 0 = f16, 1 = bf16; i8 kind 1 = s8
 //   a_mn / b_mn: 1 when that operand is MN-major
