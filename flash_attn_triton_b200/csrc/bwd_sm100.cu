@@ -112,12 +112,16 @@ static_assert((kRegsEw - 168) * 256 <= (168 - kRegsService) * 128, "register spl
 template <int D> struct BCfg {
   static constexpr int kTileBytes = kT * D * 2;
   static constexpr int kBoxes = D / 64;
-  static constexpr int kStages = (D == 128) ? 2 : 4;  // depth of each streamed-tile ring
-  static constexpr int kSmemTiles = (2 + 2 * kStages) * kTileBytes;
+  // dK/dV kernel: V resident, a ring of Q tiles (one stage deeper than dO's: Q(i) lives from
+  // S(i) to dK(i), dO(i) only from dP(i) to dV(i)) whose last slot receives K first -- K moves to
+  // TMEM before the loop -- and a ring of dO tiles.
+  static constexpr int kStagesQ = (D == 128) ? 3 : 4;
+  static constexpr int kStagesO = (D == 128) ? 2 : 4;
+  static constexpr int kSmemTiles = (1 + kStagesQ + kStagesO) * kTileBytes;
   // dK/dV kernel: 128 x 16 operand tiles that carry the row statistics into the GEMMs
   // (two constant ones on the key side, one per ring stage on the query side)
   static constexpr int kAugBytes = kT * 16 * 2;
-  static constexpr int kAugTotal = (2 + kStages) * kAugBytes;
+  static constexpr int kAugTotal = (2 + kStagesQ) * kAugBytes;
   static constexpr int kSmemBytes = kSmemTiles + kAugTotal + 1024 + 8192;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   // dQ kernel: the K ring is one stage deeper than the V ring.  K(k+1) is needed by S(k+1) at
@@ -145,6 +149,7 @@ struct BShared {
   uint64_t r_free;        // dK/dV kernel: scores, then dP, read out of their shared TMEM region (256 arrivals)
   uint64_t p_free;        // dK/dV kernel: dV MMA that read P finished
   uint64_t ds_free;       // dK/dV kernel: dK MMA that read dS finished
+  uint64_t k_copied;      // dK/dV kernel: K copied from its landing slot into TMEM (256 arrivals)
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -194,6 +199,18 @@ __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_smem, uin
   }
 }
 
+// 128 x 128 x D product with A (128 rows x D, 16-bit pairs, D/2 columns) in TMEM and B a K-major tile.
+template <int D>
+__device__ __forceinline__ void mma_kmajor_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem,
+                                              uint32_t idesc, uint32_t leader) {
+  const uint64_t db = make_smem_desc(b_smem, 16, 1024);
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t o = ((kk / 4) * (kT * 128) + (kk % 4) * 32) >> 4;
+    mma_f16_ts_lp(d_tmem, a_tmem + kk * 8, db + o, idesc, kk > 0, leader);
+  }
+}
+
 // acc(128 x D) += A(128 x 128, fp16 pairs in TMEM) * B(128 rows x D, MN-major smem tile).
 // A is stored as two 32-column blocks (written by the two element-wise groups) at
 // a_tmem and a_tmem + kGroupStride.
@@ -224,12 +241,13 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles + C::kAugTotal);
-  const uint32_t sK = smem_u32(tiles), sV = sK + C::kTileBytes;
-  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStages * C::kTileBytes;
+  const uint32_t sV = smem_u32(tiles);
+  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStagesQ * C::kTileBytes;
+  const uint32_t sKland = sRingQ + (C::kStagesQ - 1) * C::kTileBytes;  // K lands in the last Q slot
   // statistics operands: [0] key side of the score GEMM, [1] key side of the dP GEMM,
   // [2 + stage] query side (written per streamed query tile by the statistics warp)
   unsigned char* aug = tiles + C::kSmemTiles;
-  const uint32_t sAug = sK + C::kSmemTiles;
+  const uint32_t sAug = sV + C::kSmemTiles;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -261,12 +279,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&sh->p_free), 1);
     mbar_init(smem_u32(&sh->ds_free), 1);
     mbar_init(smem_u32(&sh->acc_done), 1);
-    for (int i = 0; i < C::kStages; ++i) {
-      mbar_init(smem_u32(&sh->full_a[i]), 1);
+    mbar_init(smem_u32(&sh->k_copied), 256);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(smem_u32(&sh->full_a[i]), 2);   // the TMA load of Q and the statistics warp
       mbar_init(smem_u32(&sh->full_b[i]), 1);
-      mbar_init(smem_u32(&sh->empty_a[i]), 1);
-      mbar_init(smem_u32(&sh->empty_b[i]), 1);
-      mbar_init(smem_u32(&sh->stat_full[i]), 1);
+      mbar_init(smem_u32(&sh->empty_a[i]), 2);  // one commit from each of the two issuer warps
+      mbar_init(smem_u32(&sh->empty_b[i]), 2);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
@@ -300,12 +318,10 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  // TMEM: R (128 fp32 columns, holds S^T then dP^T of a tile in turn) | P^T (64) | dS^T (64) | dV | dK
-  const uint32_t tR = tmem, tP = tmem + 128, tdS = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
+  // TMEM: R (128 fp32 columns: S^T, then dP^T of a tile) | X (64: P^T, then dS^T) | K (64) | dV | dK
+  const uint32_t tR = tmem, tX = tmem + 128, tK = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
 
-  if (warp == 11) {
-    reg_dealloc<kRegsService>();
-  } else if (warp == 8) {
+  if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
     reg_dealloc<kRegsService>();
     if (lane == 0 && total > 0) {
@@ -316,27 +332,26 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       {
         const uint32_t bar = smem_u32(&sh->res_full);
         mbar_expect_tx(bar, 2 * C::kTileBytes);
-        load_tile<D>(sK, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
+        load_tile<D>(sKland, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
         load_tile<D>(sV, &tmV, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
       }
-      int stage = 0;
-      uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-        // Q's slot frees first (after dK of the tile that held it) and is needed first (by S)
-        if (!bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 41)) break;
+        const int sq = it % C::kStagesQ, so = it % C::kStagesO;
+        // Q's slot frees after dK of the tile that held it; the last slot holds K at first
+        if (!bwait_relaxed(&sh->empty_a[sq], ((it / C::kStagesQ) & 1) ^ 1, sh, 41)) break;
+        if (it == C::kStagesQ - 1 && !bwait_relaxed(&sh->k_copied, 0, sh, 41)) break;
         {
-          const uint32_t bar = smem_u32(&sh->full_a[stage]);
+          const uint32_t bar = smem_u32(&sh->full_a[sq]);
           mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingQ + stage * C::kTileBytes, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+          load_tile<D>(sRingQ + sq * C::kTileBytes, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
         }
-        if (!bwait_relaxed(&sh->empty_b[stage], phase ^ 1, sh, 41)) break;
+        if (!bwait_relaxed(&sh->empty_b[so], ((it / C::kStagesO) & 1) ^ 1, sh, 41)) break;
         {
-          const uint32_t bar = smem_u32(&sh->full_b[stage]);
+          const uint32_t bar = smem_u32(&sh->full_b[so]);
           mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingO + stage * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+          load_tile<D>(sRingO + so * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
         }
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 10) {
@@ -372,8 +387,8 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->stat_full[stage]));
-      if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[stage]));
+      if (++stage == C::kStagesQ) { stage = 0; phase ^= 1; }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
@@ -388,66 +403,75 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (ok) ok = bwait(bar, parity, sh, code);
         tc_fence_after();
       };
-      auto slotQ = [&](int it) { return sRingQ + (it % C::kStages) * C::kTileBytes; };
-      auto slotO = [&](int it) { return sRingO + (it % C::kStages) * C::kTileBytes; };
-      // Issue order per tile i:  S(i) | dK(i-1) | dV(i-1) | dP(i).  S(i) and dP(i) take turns in
-      // one TMEM region: each is issued once the element-wise warps have read its predecessor
-      // into registers (r_free), so the exp2 phase of tile i runs under dK(i-1), dV(i-1), dP(i)
-      // and its dS phase under S(i+1).  dK goes first because it frees Q's ring slot, which the
-      // very next S needs again.
+      auto slotQ = [&](int it) { return sRingQ + (it % C::kStagesQ) * C::kTileBytes; };
+      auto slotO = [&](int it) { return sRingO + (it % C::kStagesO) * C::kTileBytes; };
+      auto stat_desc = [&](int it) {
+        return make_smem_desc_noswizzle(sAug + (2 + it % C::kStagesQ) * C::kAugBytes, 2048, 128);
+      };
       const uint64_t dstat_s = make_smem_desc_noswizzle(sAug, 2048, 128);
       const uint64_t dstat_dp = make_smem_desc_noswizzle(sAug + C::kAugBytes, 2048, 128);
-      wq(&sh->res_full, 0, 43);
-      for (int i = 0; i < total && ok; ++i) {
-        const int st = i % C::kStages;
-        const uint32_t ph = (i / C::kStages) & 1;
-        FA_BTRACE(2, i, 0);
+      // S^T(i) = K Q(i)^T (K from TMEM) - lse2 / scale_log2; waits for Q(i) and its statistics
+      auto issue_s = [&](int i) {
+        const int st = i % C::kStagesQ;
+        const uint32_t ph = (i / C::kStagesQ) & 1;
         wq(&sh->full_a[st], ph, 44);
-        wq(&sh->stat_full[st], ph, 47);
         if (i > 0) wq(&sh->r_free, 1, 49);                                     // dP(i-1) read out
-        if (!ok) break;
-        const uint64_t dstat = make_smem_desc_noswizzle(sAug + (2 + st) * C::kAugBytes, 2048, 128);
-        mma_kmajor<D>(tR, sK, slotQ(i), idesc_s, leader);                      // S^T(i) = K Q(i)^T
-        if (!kExtras) mma_f16_ss_lp(tR, dstat_s, dstat, idesc_s, 1u, leader);  //          - lse2 / scale_log2
+        if (!ok) return;
+        mma_kmajor_ts<D>(tR, tK, slotQ(i), idesc_s, leader);
+        if (!kExtras) mma_f16_ss_lp(tR, dstat_s, stat_desc(i), idesc_s, 1u, leader);
         mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+      };
+      // This warp issues the GEMMs into the fp32 region R: dP(i), then S(i+1) -- each once the
+      // element-wise warps have read its predecessor out of R (r_free).  Warp 11 issues the
+      // accumulating GEMMs dV(i), dK(i) that read P, dS from region X.  The exp2 phase of tile
+      // i+1 runs under dK(i), dP(i+1); its dS phase under dV(i+1), S(i+2).
+      wq(&sh->res_full, 0, 43);
+      wq(&sh->k_copied, 0, 43);
+      issue_s(0);
+      for (int i = 0; i < total && ok; ++i) {
+        const int st = i % C::kStagesQ, so = i % C::kStagesO;
+        FA_BTRACE(2, i, 0);
+        wq(&sh->full_b[so], (i / C::kStagesO) & 1, 44);
         FA_BTRACE(2, i, 1);
-        if (i > 0) {
-          const int sp = (i - 1) % C::kStages;
-          wq(&sh->ds_ready, (i - 1) & 1, 46);
-          if (!ok) break;
-          FA_BTRACE(2, i, 2);
-          mma_from_tmem<D, 32>(tdK, tdS, slotQ(i - 1), idesc_acc, i > 1, leader);  // dK += dS(i-1)^T Q(i-1)
-          mma_commit_lp(smem_u32(&sh->empty_a[sp]), leader);
-          mma_commit_lp(smem_u32(&sh->ds_free), leader);
-          FA_BTRACE(2, i, 3);
-          wq(&sh->p_ready, (i - 1) & 1, 45);
-          if (!ok) break;
-          mma_from_tmem<D, 32>(tdV, tP, slotO(i - 1), idesc_acc, i > 1, leader);   // dV += P(i-1)^T dO(i-1)
-          mma_commit_lp(smem_u32(&sh->empty_b[sp]), leader);
-          mma_commit_lp(smem_u32(&sh->p_free), leader);
-          FA_BTRACE(2, i, 4);
-        }
-        wq(&sh->full_b[st], ph, 44);
         wq(&sh->r_free, 0, 49);                                                // S(i) read out
         if (!ok) break;
-        FA_BTRACE(2, i, 5);
+        FA_BTRACE(2, i, 2);
         mma_kmajor<D>(tR, sV, slotO(i), idesc_s, leader);                      // dP^T(i) = V dO(i)^T
-        mma_f16_ss_lp(tR, dstat_dp, dstat, idesc_s, 1u, leader);               //           - delta
+        mma_f16_ss_lp(tR, dstat_dp, stat_desc(i), idesc_s, 1u, leader);        //           - delta
         mma_commit_lp(smem_u32(&sh->dp_full), leader);
-        FA_BTRACE(2, i, 6);
+        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);   // this warp's last reads of dO(i) and of
+        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);   // Q(i) and its statistics
+        FA_BTRACE(2, i, 3);
+        if (i + 1 < total) issue_s(i + 1);
+        FA_BTRACE(2, i, 4);
       }
-      if (ok) {
-        const int i = total, sp = (i - 1) % C::kStages;
-        wq(&sh->ds_ready, (i - 1) & 1, 46);
-        if (ok) {
-          mma_from_tmem<D, 32>(tdK, tdS, slotQ(i - 1), idesc_acc, i > 1, leader);
-          mma_commit_lp(smem_u32(&sh->empty_a[sp]), leader);
-        }
-        wq(&sh->p_ready, (i - 1) & 1, 45);
-        if (ok) {
-          mma_from_tmem<D, 32>(tdV, tP, slotO(i - 1), idesc_acc, i > 1, leader);
-          mma_commit_lp(smem_u32(&sh->empty_b[sp]), leader);
-        }
+      __syncwarp();
+    }
+  } else if (warp == 11) {
+    // ------------------------------- MMA issuer, accumulations --------------------------
+    reg_dealloc<kRegsService>();
+    if (total > 0) {
+      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      bool ok = true;
+      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+        if (ok) ok = bwait(bar, parity, sh, code);
+        tc_fence_after();
+      };
+      for (int i = 0; i < total && ok; ++i) {
+        const int st = i % C::kStagesQ, so = i % C::kStagesO;
+        // dO(i) may land after P(i) is ready; Q(i) has been read by S(i) long before dS(i) exists
+        wq(&sh->full_b[so], (i / C::kStagesO) & 1, 44);
+        wq(&sh->p_ready, i & 1, 45);
+        if (!ok) break;
+        mma_from_tmem<D, 32>(tdV, tX, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader);  // dV += P(i)^T dO(i)
+        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
+        mma_commit_lp(smem_u32(&sh->p_free), leader);
+        wq(&sh->ds_ready, i & 1, 46);
+        if (!ok) break;
+        mma_from_tmem<D, 32>(tdK, tX, sRingQ + st * C::kTileBytes, idesc_acc, i > 0, leader);  // dK += dS(i)^T Q(i)
+        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        mma_commit_lp(smem_u32(&sh->ds_free), leader);
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
       __syncwarp();
@@ -460,11 +484,31 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tRx = tR + lane_addr + x * kHalfT;            // fp32 scores / dP: this group's 64 columns
-    const uint32_t tPx = tP + lane_addr + x * (kHalfT / 2);      // P^T, dS^T as 16-bit pairs: 32 columns each
-    const uint32_t tdSx = tdS + lane_addr + x * (kHalfT / 2);
+    const uint32_t tXx = tX + lane_addr + x * (kHalfT / 2);      // P^T, then dS^T, as 16-bit pairs: 32 columns
     bool ok = true;
+    if (total > 0) {
+      // K: from its landing slot (which then joins the Q ring) into TMEM, where the score GEMM
+      // reads it as the A operand.  This thread copies its key row, group x the x-th half of it.
+      ok = bwait(&sh->res_full, 0, sh, 43);
+      if (ok) {
+        constexpr int kChunks = D / 16;              // 16-byte chunks per group
+        uint32_t kr[kChunks / 4][16];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const int g = x * kChunks + c;
+          const uint4 v = ld_shared_v4(sw128_addr(sKland + (g / 8) * (kT * 128), lrow, g % 8));
+          kr[c / 4][(c % 4) * 4] = v.x; kr[c / 4][(c % 4) * 4 + 1] = v.y;
+          kr[c / 4][(c % 4) * 4 + 2] = v.z; kr[c / 4][(c % 4) * 4 + 3] = v.w;
+        }
+#pragma unroll
+        for (int c = 0; c < kChunks / 4; ++c) tmem_st16(tK + lane_addr + x * (D / 4) + c * 16, kr[c]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->k_copied));
+      }
+    }
     for (int it = 0; it < total && ok; ++it) {
-      const int stage = it % C::kStages;
+      const int stage = it % C::kStagesQ;
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
       const int q0 = m * kT + x * kHalfT;            // first query row of this thread's columns
       const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + hq] : 0.f;
@@ -480,7 +524,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // latency hides behind the wait.  Otherwise the GEMMs deliver S - lse and dP - delta.
       float st[kHalfT];                              // -lse, later the soft cap's tanh factor
       if (kExtras) {
-        ok = bwait(&sh->stat_full[stage], (it / C::kStages) & 1, sh, 47);
+        ok = bwait(&sh->full_a[stage], (it / C::kStagesQ) & 1, sh, 47);
         if (!ok) break;
         const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
 #pragma unroll
@@ -536,9 +580,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (kExtras || masked) exp_body(std::true_type{});
       else exp_body(std::false_type{});
       if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
-      // P(it-1) is read by its dV MMA until p_free completes
+      // X holds dS(it-1) until its dK MMA has finished (ds_free)
       if (it > 0) {
-        ok = bwait(&sh->p_free, (it - 1) & 1, sh, 50);
+        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 50);
         if (!ok) break;
         tc_fence_after();
       }
@@ -548,7 +592,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
-          tmem_st16(tPx + c * 16, pk);
+          tmem_st16(tXx + c * 16, pk);
         }
       }
       if (kExtras && cfg.softcap > 0.f) {
@@ -581,14 +625,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (i < 16) pk0[i] = Elem<T>::pack(ds.x, ds.y);
         else pk1[i - 16] = Elem<T>::pack(ds.x, ds.y);
       }
-      // dS(it-1) is read by its dK MMA until ds_free completes
-      if (it > 0) {
-        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 51);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      tmem_st16(tdSx, pk0);
-      tmem_st16(tdSx + 16, pk1);
+      // X holds P(it) until its dV MMA has finished (p_free)
+      ok = bwait(&sh->p_free, it & 1, sh, 51);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_st16(tXx, pk0);
+      tmem_st16(tXx + 16, pk1);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->ds_ready));
@@ -596,7 +638,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
 
     // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
-    // Each group stages its tile in shared memory (dV over V, dK over K: every MMA is done) in
+    // Each group stages its tile in shared memory (dV over V, dK over a Q slot: every MMA is done) in
     // the swizzled box layout and lets the TMA unit write full rows; a packed tile that reaches
     // past the end of its sequence is stored row by row instead.
     if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 49);
@@ -605,7 +647,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint32_t tsrc = (x == 0 ? tdV : tdK) + lane_addr;
       const float mul = (x == 0) ? 1.f : cfg.scale;
       const bool via_tma = (p.cu_seqlens_k == nullptr) || (n0 + kT <= si.k_len);
-      const uint32_t stg = (x == 0) ? sV : sK;
+      const uint32_t stg = (x == 0) ? sV : sRingQ;   // dV over V, dK over the first Q slot
       T* base = (x == 0) ? reinterpret_cast<T*>(p.dv) + si.k_boff * p.dv_stride[0] +
                                (si.k_row0 + key) * p.dv_stride[1] + (int64_t)hk * p.dv_stride[2]
                          : reinterpret_cast<T*>(p.dk) + si.k_boff * p.dk_stride[0] +

@@ -602,6 +602,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #endif
     const int my_tiles = my_je - my_jb;
     if (ok && my_tiles > 0) ok = wait_bar(&sh->o_ready[x], (my_tiles - 1) & 1, sh, 35 + x);
+    // A stream without key tiles writes zeros over its Q tile straight away: the TMA load of
+    // both Q tiles (issued whenever the CTA has steps) must have landed first, or it would
+    // overwrite the staged zeros.
+    if (ok && my_tiles == 0 && nsteps > 0) ok = wait_bar(&sh->q_full, 0, sh, 37);
     tc_fence_after();
     if (m0 < si.q_len && ok && sh->abort_flag == 0) {
       const float inv = l > 0.f ? 1.f / l : 0.f;

@@ -139,6 +139,12 @@ __device__ __forceinline__ void tma_store_wait_read() {
 __device__ __forceinline__ uint32_t sw128_addr(uint32_t box_base, int row, int chunk) {
   return box_base + (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
