@@ -356,28 +356,44 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
   } else if (warp == 10) {
     // ------------------------------- statistics loader ----------------------------------
+    // The loads of tile it+1 are ISSUED right after tile it has been written and only consumed
+    // after the wait for the next slot, so their latency hides behind that wait (nothing reads
+    // the registers in between: a scoreboard stall before the poll would serialise the two).
     reg_dealloc<kRegsService>();
     int stage = 0;
     uint32_t phase = 0;
-    for (int it = 0; it < total; ++it) {
+    float rl[kT / 32], rd[kT / 32];                  // statistics of rows lane, lane + 32, ... as loaded
+    auto fetch = [&](int it) {
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
+#pragma unroll
+      for (int k = 0; k < kT / 32; ++k) {
+        const int row = m * kT + lane + 32 * k;
+        rl[k] = INFINITY;
+        rd[k] = 0.f;
+        if (row < si.q_len) {
+          const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
+                              (int64_t)hq * p.lse_stride[2];
+          rl[k] = p.lse2[idx];
+          rd[k] = p.delta[idx];
+        }
+      }
+    };
+    if (total > 0) fetch(0);
+    for (int it = 0; it < total; ++it) {
       bool w = true;
       if (lane == 0) w = bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 42);
       if (!__all_sync(0xffffffffu, w)) break;
       uint4* q4 = reinterpret_cast<uint4*>(aug + (2 + stage) * C::kAugBytes);
-      for (int i = lane; i < kT; i += 32) {
-        const int row = m * kT + i;
+#pragma unroll
+      for (int k = 0; k < kT / 32; ++k) {
+        const int i = lane + 32 * k;
         // NEGATED; rows that do not exist or see no key get a large finite value instead of
         // infinity (an infinity would meet the zeros of the other GEMM's key-side operand): P = 0
-        float nl2 = -60000.f, ndl = 0.f;
-        if (row < si.q_len) {
-          const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
-                              (int64_t)hq * p.lse_stride[2];
-          nl2 = -p.lse2[idx];
-          ndl = -p.delta[idx];
-          if (!(fabsf(nl2) < 60000.f)) nl2 = -60000.f;  // row without visible keys: P = 0
-        }
-        if (kExtras) sh->lse[stage][i] = nl2 == -60000.f ? -INFINITY : nl2;  // added after the soft cap by the element-wise warps
+        float nl2 = -rl[k];
+        const float ndl = -rd[k];
+        if (!(fabsf(nl2) < 60000.f)) nl2 = -60000.f;
+        // the feature variant adds the LSE after the soft cap, in the element-wise warps
+        if (kExtras) sh->lse[stage][i] = nl2 == -60000.f ? -INFINITY : nl2;
         const float lf = kExtras ? 0.f : nl2;
         const T l_hi = Elem<T>::from_f(lf), l_lo = Elem<T>::from_f(lf - Elem<T>::to_f(l_hi));
         const T d_hi = Elem<T>::from_f(ndl), d_lo = Elem<T>::from_f(ndl - Elem<T>::to_f(d_hi));
@@ -389,6 +405,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[stage]));
       if (++stage == C::kStagesQ) { stage = 0; phase ^= 1; }
+      if (it + 1 < total) fetch(it + 1);
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
