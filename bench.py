@@ -414,7 +414,7 @@ def run_ours(args, rank, world, local_rank):
     top = max(("fwd", "bwd_dq", "bwd_dkdv"), key=lambda n: kernels[n])
     # DRAM traffic per launch of each kernel from the ncu captures summarised in profiles/
     # (B=2 capture scaled x8 by batch, profiles/fwd_bwd_sm100_B2_H16_S4096_D128_causal.md)
-    traffic = {"fwd": 0.96e9, "bwd_dq": 1.24e9, "bwd_dkdv": 1.42e9}
+    traffic = {"fwd": 0.94e9, "bwd_dq": 1.24e9, "bwd_dkdv": 1.41e9}
     roofline = {"kernel": top, "bound": "tensor", "achieved": algo[top] / kernels[top] / 1e9,
                 "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": algo[top] / kernels[top] / 1e9 / peaks["bf16"],
                 "peak_source": peaks["source"] + " cuBLAS bf16 burst", "traffic": traffic[top],
