@@ -89,7 +89,7 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
 }
 
 // ---------------------------------------------------------------------------------------
-// TMA (tiled tensor maps, no multicast)
+// TMA (tiled tensor maps; every load is addressed to the issuing CTA only)
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
