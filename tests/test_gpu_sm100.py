@@ -92,3 +92,22 @@ def test_tcgen05_agrees_with_mma_at_full_size():
     assert maxdiff(a[1], b[1]) <= util.FWD_TOL
     for x, y in zip(a[2:], b[2:]):
         assert (x.float() - y.float()).abs().max().item() <= util.GRAD_TOL
+
+
+def test_tcgen05_forward_query_tile_without_keys():
+    """A 256-row CTA whose second query tile sees no key at all (window far left of the rows):
+    that tile's output must be exactly zero and its LSE -inf, whatever the output buffer held
+    before -- the zeros are staged over the tile's Q slot and must not race with the Q load."""
+    from flash_attn_triton_b200 import _native as N, _ops
+    B, Sq, Sk, Hq, Hkv, D = 2, 1000, 777, 4, 2, 128
+    q, k, v, _ = cases.dense_case(2003, B, Sq, Sk, Hq, Hkv, D)
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    args = (0.1, False, 50, 70, 0.0, None, 0)
+    for _ in range(4):
+        junk = torch.full((B, Sq, Hq, D), 7.0, dtype=torch.float16, device=DEV)
+        del junk  # the caching allocator hands this block to the forward's output
+        o, lse, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+        assert N.lib().fa_device_wait_status(0) == 0
+        empty_rows = slice(Sk + 50, Sq)  # query positions whose window [q-50, q+70] lies past the last key
+        assert torch.count_nonzero(o[:, empty_rows]).item() == 0
+        assert torch.isinf(lse[:, :, empty_rows]).all() and (lse[:, :, empty_rows] < 0).all()
