@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # FA_B200_LIB selects another build of the same library (e.g. a variant made with FA_BUILD_TAG)
 LIB_PATH = os.environ.get("FA_B200_LIB") or os.path.join(_HERE, "libfa_b200.so")
 
-FA_F16, FA_BF16 = 0, 1
+FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 IMPL_AUTO, IMPL_MMA, IMPL_TCGEN05 = 0, 1, 2
 _I64x3 = C.c_int64 * 3
 
@@ -68,6 +68,19 @@ class Int8Args(C.Structure):
         ("o", C.c_void_p), ("lse2", C.c_void_p),
         ("softmax_scale", C.c_float), ("causal", C.c_int32),
         ("q8_scratch", C.c_void_p), ("sq_scratch", C.c_void_p),
+        ("seqlen_k_valid", C.c_int32), ("q_pos_offset", C.c_int32),
+    ]
+
+
+class RotaryArgs(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32), ("device", C.c_int32),
+        ("batch", C.c_int32), ("seqlen", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("x", C.c_void_p), ("out", C.c_void_p), ("x_stride", _I64x3), ("out_stride", _I64x3),
+        ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("rotary_dim", C.c_int32), ("rotary_seqlen", C.c_int32),
+        ("interleaved", C.c_int32), ("conjugate", C.c_int32),
+        ("seqlen_offset", C.c_int32), ("seqlen_offsets", C.c_void_p), ("cu_seqlens", C.c_void_p),
     ]
 
 
@@ -86,10 +99,18 @@ EXPORTS = {
     "fa_quantize_k_int8": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                      C.c_int32, C.c_void_p]),
     "fa_fwd_int8": (C.c_int, [C.POINTER(Int8Args), C.c_void_p]),
+    "fa_rotary": (C.c_int, [C.POINTER(RotaryArgs), C.c_void_p]),
+    "fa_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                 C.c_int32, C.c_void_p]),
+    "fa_scatter_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                  C.c_int32, C.c_int32, C.c_void_p]),
     "fa_version": (C.c_char_p, []),
     "fa_last_error": (C.c_char_p, []),
     "fa_fwd_uses_tcgen05": (C.c_int, [C.POINTER(AttnArgs)]),
     "fa_device_wait_status": (C.c_int, [C.c_int]),
+    "fa_device_wait_clear": (C.c_int, [C.c_int]),
+    "fa_wait_probe": (C.c_int, [C.c_int32, C.c_int64, C.c_void_p]),
+    "fa_debug_set_wait_status": (C.c_int, [C.c_int32, C.c_int32]),
     "fa_sizeof_args": (C.c_size_t, [C.c_int]),
 }
 
@@ -109,7 +130,7 @@ def lib():
             fn = getattr(l, name)
             fn.restype = res
             fn.argtypes = args
-        for which, st in ((0, AttnArgs), (1, DecodeArgs), (2, Int8Args)):
+        for which, st in ((0, AttnArgs), (1, DecodeArgs), (2, Int8Args), (3, RotaryArgs)):
             if l.fa_sizeof_args(which) != C.sizeof(st):
                 raise RuntimeError(f"ABI mismatch for {st.__name__}: library "
                                    f"{l.fa_sizeof_args(which)} vs binding {C.sizeof(st)}")
@@ -117,11 +138,19 @@ def lib():
     return _lib
 
 
+class DeviceWaitError(RuntimeError):
+    """A bounded wait inside a kernel ran out earlier on this device (FA_ERR_DEVICE_WAIT): the
+    kernel that hit it left its outputs incomplete and the tcgen05 kernels refuse to launch
+    until `lib().fa_device_wait_clear(device)`."""
+
+
 def check(status, what):
     if status != 0:
         msg = lib().fa_last_error().decode(errors="replace")
         if status == -1:
             raise ValueError(f"{what}: {msg}")
+        if status == -5:
+            raise DeviceWaitError(f"{what}: {msg}")
         raise RuntimeError(f"{what} failed (status {status}): {msg}")
 
 

@@ -224,7 +224,7 @@ def quantize_k_int8(k):
     return k8, s_k
 
 
-def int8_forward(q, k, v, causal, scale, impl=N.IMPL_AUTO):
+def int8_forward(q, k, v, causal, scale, impl=N.IMPL_AUTO, k_valid=0, q_pos_offset=0):
     B, H, S, D = q.shape
     k8, s_k = quantize_k_int8(k)
     o = torch.empty_like(q)
@@ -237,6 +237,7 @@ def int8_forward(q, k, v, causal, scale, impl=N.IMPL_AUTO):
                                            v.data_ptr(), o.data_ptr(), lse.data_ptr())
     a.softmax_scale = float(scale)
     a.causal = int(bool(causal))
+    a.seqlen_k_valid, a.q_pos_offset = int(k_valid), int(q_pos_offset)
     if D == 128 and impl != N.IMPL_MMA:
         q8 = torch.empty(q.shape, dtype=torch.int8, device=q.device)
         s_q = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
@@ -250,19 +251,28 @@ class Int8Attention(torch.autograd.Function):
     """INT8-QK^T forward, fp16 backward (attention_kernel_int8.py:220-267).  [B,H,S,D]."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, impl):
-        o, lse, _, _ = int8_forward(q, k, v, causal, scale, impl)
+    def forward(ctx, q, k, v, causal, scale, impl, k_valid=0, q_pos_offset=0):
+        o, lse, _, _ = int8_forward(q, k, v, causal, scale, impl, k_valid, q_pos_offset)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.cfg = (causal, scale)
+        ctx.cfg = (causal, scale, k_valid, q_pos_offset)
         return o
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, o, lse = ctx.saved_tensors
-        causal, scale = ctx.cfg
-        dq, dk, dv = dense_backward(q, k, v, o, lse, dout, scale, causal, -1, -1, 0.0, None, 0,
-                                    N.IMPL_AUTO, "bhsd")
-        return dq, dk, dv, None, None, None
+        causal, scale, k_valid, off = ctx.cfg
+        S = k.shape[2]
+        if k_valid and k_valid < S:
+            # padded call: the keys past k_valid take no part; their gradients are zero
+            dq, dk_s, dv_s = dense_backward(q, k[:, :, :k_valid], v[:, :, :k_valid], o, lse, dout, scale,
+                                            causal, -1, -1, 0.0, None, off, N.IMPL_AUTO, "bhsd")
+            dk, dv = torch.zeros_like(k), torch.zeros_like(v)
+            dk[:, :, :k_valid] = dk_s
+            dv[:, :, :k_valid] = dv_s
+        else:
+            dq, dk, dv = dense_backward(q, k, v, o, lse, dout, scale, causal, -1, -1, 0.0, None, off,
+                                        N.IMPL_AUTO, "bhsd")
+        return dq, dk, dv, None, None, None, None, None
 
 
 # ----------------------------------------------------------------------------------------

@@ -22,9 +22,6 @@ LIB = os.path.join(HERE, "libfa_b200" + ("_" + TAG if TAG else "") + ".so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
-# which tcgen05 families are present (each defines its FA_HAVE_* so the stubs step aside)
-HAVE = {"fwd_sm100.cu": "FA_HAVE_FWD_SM100", "bwd_sm100.cu": "FA_HAVE_BWD_SM100",
-        "int8_sm100.cu": "FA_HAVE_INT8_SM100"}
 
 
 def _sources():
@@ -58,10 +55,7 @@ def _compile(src, defs, force, verbose):
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     srcs = _sources()
-    defs = [f"-D{HAVE[s]}" for s in srcs if s in HAVE]
-    if os.environ.get("FA_TRACE"):
-        defs.append("-DFA_TRACE")
-    defs += os.environ.get("FA_BUILD_DEFS", "").split()
+    defs = os.environ.get("FA_BUILD_DEFS", "").split()
     rebuilt = False
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         for src, log, did in ex.map(lambda s: _compile(s, defs, force, verbose), srcs):

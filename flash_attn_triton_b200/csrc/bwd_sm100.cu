@@ -1,36 +1,42 @@
 // Backward attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), as two
-// kernels with one writer per output element (no atomics, deterministic):
+// PERSISTENT kernels with one writer per output element (no atomics, deterministic):
 //
-//   bwd_dkdv_sm100_kernel  CTA = 128 keys of one (batch, kv head); loops over the query
+//   bwd_dkdv_sm100_kernel  work item = 128 keys of one (batch, kv head); loops over the query
 //                          tiles (and the query heads of the GQA group) that can see them.
 //                          Works on the TRANSPOSED tiles  S^T = K Q^T,  dP^T = V dO^T  so
 //                          that a TMEM lane is a key: P^T and dS^T are written back to TMEM
-//                          in place and feed  dV += P^T dO,  dK += dS^T Q  as the A operand.
-//   bwd_dq_sm100_kernel    CTA = 128 query rows of one (batch, head); loops over key tiles:
-//                          S = Q K^T, dP = dO V^T, dS in place over dP, dQ += dS K.
+//                          and feed  dV += P^T dO,  dK += dS^T Q  as the A operand.
+//   bwd_dq_sm100_kernel    work item = 128 query rows of one (batch, head); loops over key
+//                          tiles: S = Q K^T, dP = dO V^T, dS in place over dP, dQ += dS K.
 //
-// Both kernels are software-pipelined through the ORDER in which the MMA warp feeds the (in-
+// One CTA per SM takes work items from a queue: a counter in global memory hands out candidates
+// in an order in which the CTAs that run together work on the same heads (the tiles they stream
+// stay in L2) and in which the heavy items of a causal mask come first.  The producer thread
+// draws from the counter, one item ahead, and publishes what it drew to the other roles through
+// a small ring in shared memory.  Barriers, tensor memory and tensor maps are set up once per CTA.  Every role runs ahead into the next item on
+// its own: the producer fetches the next item's tiles as ring slots free up, the MMA warps issue
+// its first products while the element-wise warps still store the previous item's result.  The
+// result tiles are staged over the LAST streamed tiles of the item, whose ring slots are released
+// by the store instead of by the MMAs that read them: the next item's first tiles are already in
+// the other slots by then.
+//
+// Both kernels are software-pipelined through the ORDER in which the MMA warps feed the (in-
 // order) tensor pipe, so that the element-wise warps always work while independent MMAs run:
 //
 //   dK/dV, per query tile i:   S(i) | dK += dS(i-1)^T Q(i-1) | dV += P(i-1)^T dO(i-1) | dP(i)
-//       S(i) and dP(i) take turns in ONE fp32 TMEM region, P and dS (16-bit) have regions of
-//       their own: the element-wise warps hand the fp32 region back as soon as its contents
-//       are in their registers, so S(i+1) does not wait for the MMA that consumes P(i).
-//       exp phase  of tile i (P = exp2(S - lse))   runs during dK(i-1), dV(i-1), dP(i);
-//       dS  phase  of tile i (dS = P (dP - delta)) runs during S(i+1).
+//       S(i) and dP(i) take turns in ONE fp32 TMEM region, P and dS (16-bit) share a second one.
 //   dQ, per key tile k:        S(k+1) -> other S buffer | dQ += dS(k) K(k) | dP(k+1)
-//       S is double-buffered (P is no MMA operand here, nothing orders a single buffer).
 //
 // Roles (384 threads):
 //   warps 0-3 / 4-7  element-wise groups A / B: columns 0..63 / 64..127 of the 128 x 128
 //                    tiles, one TMEM lane (row) per thread
-//   warp 8           TMA producer (resident tiles once, then two rings of streamed tiles)
+//   warp 8           TMA producer
 //   warp 9           MMA issuer (uniform control flow, one elected lane issues)
-//   warp 10          loads the per-row statistics (base-2 LSE, delta) of the streamed query
-//                    tile into shared memory (dK/dV kernel only)
-//   warp 11          idle (completes the warpgroup for setmaxnreg)
+//   warp 10          dK/dV kernel: loads the per-row statistics (base-2 LSE, delta) of the
+//                    streamed query tile and writes them as a 16-column GEMM operand
+//   warp 11          dK/dV kernel: second MMA issuer (the accumulating GEMMs)
 //
-// TMEM, dK/dV kernel: S^T or dP^T (128 columns) | P^T (64) | dS^T (64) | dV (128) | dK (128).
+// TMEM, dK/dV kernel: S^T or dP^T (128 columns) | P^T or dS^T (64) | K (64) | dV (128) | dK (128).
 // TMEM, dQ kernel:    S[0] | S[1] | dP | dQ    (4 x 128 columns).
 // All operand tiles are written by TMA with the 128-byte swizzle; the same tile is read
 // K-major (contraction over head_dim) or MN-major (contraction over its rows) through
@@ -39,6 +45,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+#define PROF_TAG bwd
+#include "prof.cuh"
 #include "sm100.cuh"
 
 namespace fa {
@@ -47,56 +55,12 @@ using namespace sm100;
 
 __device__ int g_bwd_sm100_status = 0;
 
-#ifdef FA_TRACE
-#ifndef FA_TRACE_Y
-#define FA_TRACE_Y 0
-#define FA_TRACE_Z 0
-#endif
-// Timeline of one CTA (blockIdx.x 0) of the dK/dV kernel -- of the dQ kernel when FA_TRACE_DQ is
-// defined -- for tuning: clock64 per role/step.
-__device__ long long g_bwd_trace[3][32][8];
-#define FA_TRACE_REC(role, step, ev)                                                          \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == FA_TRACE_Y && blockIdx.z == FA_TRACE_Z &&           \
-        (step) < 32 && (threadIdx.x & 31) == 0)                                              \
-      g_bwd_trace[role][step][ev] = clock64();                                               \
-  } while (0)
-// per-launch totals over all CTAs of the dK/dV kernel: [0] clock64 cycles, [1] tiles, [2] CTAs,
-// [3] globaltimer ns of the first start, [4] of the last end
-__device__ unsigned long long g_bwd_cta_stats[8];
-extern "C" int fa_debug_bwd_cta_stats(unsigned long long* out, int reset) {
-  int r = (int)cudaMemcpyFromSymbol(out, g_bwd_cta_stats, sizeof(unsigned long long) * 8);
-  if (reset) {
-    unsigned long long z[8] = {0, 0, 0, ~0ull, 0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_bwd_cta_stats, z, sizeof(z));
-  }
-  return r;
-}
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-extern "C" int fa_debug_bwd_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * 3 * 32 * 8);
-}
-#ifdef FA_TRACE_DQ
-#define FA_QTRACE(role, step, ev) FA_TRACE_REC(role, step, ev)
-#define FA_BTRACE(role, step, ev) do {} while (0)
-#else
-#define FA_QTRACE(role, step, ev) do {} while (0)
-#define FA_BTRACE(role, step, ev) FA_TRACE_REC(role, step, ev)
-#endif
-#else
-#define FA_BTRACE(role, step, ev) do {} while (0)
-#define FA_QTRACE(role, step, ev) do {} while (0)
-#endif
-
 namespace {
 
 constexpr int kT = 128;        // tile edge: rows of Q / keys of K,V per tile
 constexpr int kHalfT = 64;     // columns per element-wise group
 constexpr int kBwdThreads = 384;
+constexpr int kSched = 4;      // depth of the in-CTA ring of work-queue entries
 // Register re-balancing (setmaxnreg): the CTA starts with 168 registers per thread; the four
 // service warps drop to kRegsService and the eight element-wise warps grow to kRegsEw.
 // setmaxnreg.inc blocks until the registers exist, so the split has to satisfy
@@ -112,9 +76,9 @@ static_assert((kRegsEw - 168) * 256 <= (168 - kRegsService) * 128, "register spl
 template <int D> struct BCfg {
   static constexpr int kTileBytes = kT * D * 2;
   static constexpr int kBoxes = D / 64;
-  // dK/dV kernel: V resident, a ring of Q tiles (one stage deeper than dO's: Q(i) lives from
-  // S(i) to dK(i), dO(i) only from dP(i) to dV(i)) whose last slot receives K first -- K moves to
-  // TMEM before the loop -- and a ring of dO tiles.
+  // dK/dV kernel: V resident, ring A of K / Q entries (Q(i) lives from S(i) to dK(i); dK is
+  // staged over the last Q), ring B of dO entries (dO(i) lives from dP(i) to dV(i); dV is
+  // staged over the last dO).
   static constexpr int kStagesQ = (D == 128) ? 3 : 4;
   static constexpr int kStagesO = (D == 128) ? 2 : 4;
   static constexpr int kSmemTiles = (1 + kStagesQ + kStagesO) * kTileBytes;
@@ -122,26 +86,25 @@ template <int D> struct BCfg {
   // (two constant ones on the key side, one per ring stage on the query side)
   static constexpr int kAugBytes = kT * 16 * 2;
   static constexpr int kAugTotal = (2 + kStagesQ) * kAugBytes;
-  static constexpr int kSmemBytes = kSmemTiles + kAugTotal + 1024 + 8192;
+  static constexpr int kSmemBytes = kSmemTiles + kAugTotal + 1024 + 4096;
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-  // dQ kernel: the K ring is one stage deeper than the V ring.  K(k+1) is needed by S(k+1) at
-  // the START of step k while K(k) is still read by dQ(k) at its end; with two stages the slot
-  // of K(k+1) is only freed by dQ(k-1), and the load's latency landed on the critical path.
-  // This kernel only touches the barriers of BShared (512 bytes), not its statistics arrays.
+  // dQ kernel: Q and dO resident, ring A of K tiles (dQ is staged over the last one), ring B of V tiles.  The K
+  // ring is one stage deeper than the V ring: K(k+1) is needed by S(k+1) at the START of step k
+  // while K(k) is still read by dQ(k) at its end.
   static constexpr int kStagesK = (D == 128) ? 3 : 4;
   static constexpr int kStagesV = (D == 128) ? 2 : 4;
   static constexpr int kSmemTilesDq = (2 + kStagesK + kStagesV) * kTileBytes;
-  static constexpr int kSmemBytesDq = kSmemTilesDq + 1024 + 512;
+  static constexpr int kSmemBytesDq = kSmemTilesDq + 1024 + 1024;
   static_assert(kSmemBytesDq <= 227 * 1024, "shared memory budget (dQ)");
 };
 
 struct BShared {
-  uint64_t res_full;      // resident tiles (K,V or Q,dO) landed
-  uint64_t full_a[4];     // streamed tile A (Q in dK/dV, K in dQ) landed
-  uint64_t full_b[4];     // streamed tile B (dO in dK/dV, V in dQ) landed
-  uint64_t empty_a[4];    // last MMA reading tile A (and its statistics) finished
-  uint64_t empty_b[4];    // last MMA reading tile B finished
-  uint64_t stat_full[4];  // statistics of the streamed query tile written (dK/dV kernel)
+  uint64_t full_a[4];     // ring A entry landed (dK/dV: K, Q + statistics; dQ: K)
+  uint64_t full_b[4];     // ring B entry landed (dK/dV: dO; dQ: V)
+  uint64_t empty_a[4];    // ring A entry released
+  uint64_t empty_b[4];    // ring B entry released
+  uint64_t res_full;      // resident tiles of the item landed (dK/dV: V; dQ: Q and dO)
+  uint64_t res_free;      // last MMA reading the resident tiles of the item finished
   uint64_t s_full[2];     // S computed ([buffer] in the dQ kernel, [0] in the dK/dV kernel)
   uint64_t dp_full;       // dP computed
   uint64_t p_ready;       // P written back (256 arrivals; dK/dV kernel)
@@ -149,15 +112,22 @@ struct BShared {
   uint64_t r_free;        // dK/dV kernel: scores, then dP, read out of their shared TMEM region (256 arrivals)
   uint64_t p_free;        // dK/dV kernel: dV MMA that read P finished
   uint64_t ds_free;       // dK/dV kernel: dK MMA that read dS finished
-  uint64_t k_copied;      // dK/dV kernel: K copied from its landing slot into TMEM (256 arrivals)
-  uint64_t acc_done;      // every accumulation MMA finished
+  uint64_t k_copied;      // dK/dV kernel: K of the item copied from its ring slot into TMEM (256 arrivals)
+  uint64_t acc_done;      // every accumulation MMA of the item finished
+  uint64_t sched_full[kSched];   // work-queue entry published by the producer thread
+  uint64_t sched_empty[kSched];  // ... read by every consuming warp
+  int4 sched_item[kSched][3];    // the item, decoded once by the producer thread (KItem / QItem)
+  uint64_t stg_ready[2];  // [group] result tile of an item staged for the store lane (and its message written)
+  uint64_t stg_taken[2];  // [group] the store lane has read the message
+  // [group] message to the store lane: shared-memory address of the staged tile (0 = nothing to
+  // store, -1 = no more items), tensor-map coordinates head / row / batch, barrier to release
+  volatile int stg_msg[2][5];
   uint32_t tmem_base;
   volatile int abort_flag;
-  alignas(16) float lse[4][kT];  // [stage][row of the streamed query tile]: MINUS the base-2 LSE
-  alignas(16) float delta[4][kT];  //                                       MINUS delta
+  alignas(16) float lse[4][kT];  // [stage][row of the streamed query tile]: MINUS the base-2 LSE (feature variant)
 };
-static_assert(sizeof(BShared) <= 8192, "BShared must fit its reserve");
-static_assert(offsetof(BShared, lse) <= 512, "the dQ kernel reserves 512 bytes for the barriers");
+static_assert(sizeof(BShared) <= 4096, "BShared must fit its reserve");
+static_assert(offsetof(BShared, lse) <= 1024, "the dQ kernel reserves 1024 bytes for the barriers and the work queue");
 
 template <typename T> struct BFmt;
 template <> struct BFmt<__half> { static constexpr int code = 0; };
@@ -176,6 +146,126 @@ __device__ __forceinline__ bool bwait_relaxed(uint64_t* bar, uint32_t parity, BS
     __nanosleep(100);
   }
   return bwait(bar, parity, sh, code);
+}
+
+// Work queue.  `counter[0]` hands out candidate indices, `counter[1]` counts the CTAs that have
+// finished; the last one to finish puts both back to zero, so a launch always finds them at zero.
+// The producer thread draws a candidate, decodes it into an item (12 ints: KItem / QItem) and
+// publishes the item to the other roles; entry number i of this CTA travels in ring slot
+// i % kSched.  Candidates outside their sequence are skipped; an item with total < 0 ends the queue.
+template <typename Item, typename F>
+__device__ __forceinline__ Item sched_publish(BShared* sh, unsigned int* counter, int ncand, int& fidx, bool& ok,
+                                              F decode) {
+  static_assert(sizeof(Item) == 48, "an item travels as three 16-byte words");
+  Item w;
+  for (;;) {
+    const unsigned int u = atomicAdd(&counter[0], 1u);
+    if (u >= (unsigned int)ncand) {
+      w.total = -1;
+      break;
+    }
+    if (decode((int)u, w)) break;
+  }
+  const int slot = fidx % kSched;
+  if (!bwait_relaxed(&sh->sched_empty[slot], ((fidx / kSched) & 1) ^ 1, sh, 60)) {
+    ok = false;
+    w.total = -1;
+    return w;
+  }
+  const int4* src = reinterpret_cast<const int4*>(&w);
+  sh->sched_item[slot][0] = src[0];
+  sh->sched_item[slot][1] = src[1];
+  sh->sched_item[slot][2] = src[2];
+  mbar_arrive(smem_u32(&sh->sched_full[slot]));
+  ++fidx;
+  return w;
+}
+// Entry number idx as seen by a consuming warp (all lanes call this together).  `consume` releases
+// the entry; without it the call only looks at an entry that will be consumed later.
+template <typename Item>
+__device__ __forceinline__ Item sched_get(BShared* sh, int idx, bool consume, bool& ok) {
+  Item w;
+  const int slot = idx % kSched;
+  if (!bwait(&sh->sched_full[slot], (idx / kSched) & 1, sh, 61)) {
+    ok = false;
+    w.total = -1;
+    return w;
+  }
+  int4* dst = reinterpret_cast<int4*>(&w);
+  dst[0] = sh->sched_item[slot][0];
+  dst[1] = sh->sched_item[slot][1];
+  dst[2] = sh->sched_item[slot][2];
+  if (consume) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&sh->sched_empty[slot]));
+  }
+  return w;
+}
+// Releases an entry that this warp has already looked at.
+__device__ __forceinline__ void sched_release(BShared* sh, int idx) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&sh->sched_empty[idx % kSched]));
+}
+
+// Store lane: one thread that writes the result tiles the element-wise warps stage, so that none of
+// them has to wait for the TMA unit.  Per item it waits for the tile (and the message that
+// describes it), issues the store, waits until the unit has read the tile and releases the ring
+// entry the tile was staged over (two stand-in arrivals, or one in the dQ kernel).
+template <int D>
+__device__ __forceinline__ void store_lane(BShared* sh, int x, const CUtensorMap* tm, uint32_t release_count) {
+  for (uint32_t n = 0;; ++n) {
+    // an item takes tens of microseconds: sleep between polls instead of spinning next to the
+    // producer lane (a spinning lane of the same warp takes its issue slots)
+    {
+      const uint32_t bar = smem_u32(&sh->stg_ready[x]);
+      const long long t0 = clock64();
+      bool done = false;
+      while (!(done = mbar_try_wait(bar, n & 1))) {
+        __nanosleep(400);
+        if (sh->abort_flag || *reinterpret_cast<volatile int*>(&g_bwd_sm100_status) != 0) break;
+        if (clock64() - t0 > 4 * FA_WAIT_CLOCKS) {   // items differ in length by orders of magnitude
+          sh->abort_flag = 62;
+          atomicCAS(&g_bwd_sm100_status, 0, 62);
+          break;
+        }
+      }
+      if (!done) return;
+    }
+    const int addr = sh->stg_msg[x][0], head = sh->stg_msg[x][1], row = sh->stg_msg[x][2],
+              batch = sh->stg_msg[x][3], rel = sh->stg_msg[x][4];
+    mbar_arrive(smem_u32(&sh->stg_taken[x]));
+    if (addr == -1) return;
+    if (addr > 0) {
+#pragma unroll
+      for (int bx = 0; bx < D / 64; ++bx) tma_store_4d(tm, (uint32_t)addr + bx * (kT * 128), bx * 64, head, row, batch);
+      tma_store_commit();
+      tma_store_wait_read();
+    }
+    mbar_arrive_cnt((uint32_t)rel, release_count);
+  }
+}
+// Element-wise side: thread `poster` of the group writes the message for item number n (after the
+// store lane has taken the previous one); every thread of the group then arrives on stg_ready
+// once its part of the tile is staged.
+__device__ __forceinline__ bool post_store(BShared* sh, int x, int n, int addr, int head, int row, int batch,
+                                           uint32_t release_bar) {
+  if (n > 0 && !bwait(&sh->stg_taken[x], (n - 1) & 1, sh, 63)) return false;
+  sh->stg_msg[x][0] = addr;
+  sh->stg_msg[x][1] = head;
+  sh->stg_msg[x][2] = row;
+  sh->stg_msg[x][3] = batch;
+  sh->stg_msg[x][4] = (int)release_bar;
+  return true;
+}
+
+__device__ __forceinline__ void sched_finish(unsigned int* counter) {
+  __threadfence();
+  const unsigned int done = atomicAdd(&counter[1], 1u);
+  if (done == gridDim.x - 1) {
+    counter[0] = 0u;
+    counter[1] = 0u;
+    __threadfence();
+  }
 }
 
 // TMA loads of one 128 x D tile (D/64 boxes) at (row, head, batch)
@@ -225,6 +315,96 @@ __device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t a_tmem, 
   }
 }
 
+// TMEM accumulator (128 lanes x kCols fp32 columns starting at tsrc, this thread's lane) scaled
+// by `mul`, converted to T and either staged in the swizzled box layout at `stg` (column
+// `col0 + c` of the tile) or, when `direct` is set, stored to the row pointer `grow` (null = skip).
+template <typename T, int kCols>
+__device__ __forceinline__ void drain_acc(uint32_t tsrc, float mul, bool staged, uint32_t stg, int lrow,
+                                          int col0, T* grow) {
+#pragma unroll
+  for (int cc = 0; cc < kCols / 32; ++cc) {
+    uint32_t r[32];
+    tmem_ld32(tsrc + cc * 32, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 v;
+      v.x = Elem<T>::pack(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+      v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+      v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+      v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+      const int col = col0 + cc * 32 + i;
+      if (staged) st_shared_v4(sw128_addr(stg + (col / 64) * (kT * 128), lrow, (col % 64) / 8), v);
+      else if (grow != nullptr) *reinterpret_cast<uint4*>(grow + cc * 32 + i) = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// work items
+// ---------------------------------------------------------------------------------------
+struct Geo {          // one sequence's geometry, as ints (tensor-map coordinates are 32-bit)
+  int q_len, k_len, q_row0, k_row0, q_boff, k_boff;
+};
+__device__ __forceinline__ Geo geo_of(const fa_attn_args& p, int b) {
+  const SeqInfo si = seq_info(p, b);
+  Geo g;
+  g.q_len = si.q_len; g.k_len = si.k_len;
+  g.q_row0 = (int)si.q_row0; g.k_row0 = (int)si.k_row0;
+  g.q_boff = (int)si.q_boff; g.k_boff = (int)si.k_boff;
+  return g;
+}
+
+// dK/dV: candidate c = ((b * heads_kv + hk) * key_blocks + key block); key block 0 sees the most
+// query tiles under a causal mask.  Returns false when the key block lies outside its sequence.
+struct KItem {
+  Geo g;
+  int n0, hk, b;
+  int m_lo, ntiles, total;   // query tiles [m_lo, m_lo + ntiles) per query head; total = ntiles * group
+};
+__device__ __forceinline__ bool dkdv_item(const fa_attn_args& p, const ScoreCfg& cfg, int cand, int nkb, KItem& w) {
+  const int nblk = cand % nkb, rem = cand / nkb;
+  w.hk = rem % p.heads_kv;
+  w.b = rem / p.heads_kv;
+  w.n0 = nblk * kT;
+  w.g = geo_of(p, w.b);
+  w.m_lo = w.ntiles = w.total = 0;
+  if (w.n0 >= w.g.k_len) return false;
+  const int off = p.q_pos_offset;
+  int qlo, qhi;
+  visible_query_range(cfg, w.n0, min(w.n0 + kT, w.g.k_len) - 1, off, w.g.q_len + off, qlo, qhi);
+  w.m_lo = max(qlo - off, 0) / kT;
+  const int m_hi = (max(qhi - off, 0) + kT - 1) / kT;
+  w.ntiles = max(m_hi - w.m_lo, 0);
+  w.total = w.ntiles * (p.heads_q / p.heads_kv);
+  return true;
+}
+
+// dQ: candidate c = ((b * heads_q + h) * query_blocks + i); with a causal mask block i counts
+// down from the last (heaviest) query block.  Returns false when the block lies outside its sequence.
+struct QItem {
+  Geo g;
+  int m0, h, b;
+  int n_hi, total;           // step j works on key tile n_hi - 1 - j (masked tiles first)
+  int pad;
+};
+__device__ __forceinline__ bool dq_item(const fa_attn_args& p, const ScoreCfg& cfg, int cand, int nmb, QItem& w) {
+  const int i = cand % nmb, rem = cand / nmb;
+  w.h = rem % p.heads_q;
+  w.b = rem / p.heads_q;
+  w.m0 = (cfg.causal ? (nmb - 1 - i) : i) * kT;
+  w.g = geo_of(p, w.b);
+  w.n_hi = w.total = w.pad = 0;
+  if (w.m0 >= w.g.q_len) return false;
+  const int off = p.q_pos_offset;
+  int klo, khi;
+  visible_key_range(cfg, w.m0 + off, min(w.m0 + kT, w.g.q_len) - 1 + off, w.g.k_len, klo, khi);
+  const int n_lo = klo / kT;
+  w.n_hi = (khi + kT - 1) / kT;
+  w.total = max(w.n_hi - n_lo, 0);
+  return true;
+}
+
 }  // namespace
 
 // =======================================================================================
@@ -235,41 +415,32 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                       const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
-                      const fa_attn_args p, const ScoreCfg cfg) {
+                      const fa_attn_args p, const ScoreCfg cfg, const int nkb, const int ncand,
+                      unsigned int* const queue, int* const host_status) {
   using C = BCfg<D>;
+  constexpr int SQ = C::kStagesQ, SO = C::kStagesO;
+  constexpr int kConsumers = 11;   // warps that read the work queue: 8 element-wise, 2 issuers, statistics
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles + C::kAugTotal);
   const uint32_t sV = smem_u32(tiles);
-  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStagesQ * C::kTileBytes;
-  const uint32_t sKland = sRingQ + (C::kStagesQ - 1) * C::kTileBytes;  // K lands in the last Q slot
+  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + SQ * C::kTileBytes;
   // statistics operands: [0] key side of the score GEMM, [1] key side of the dP GEMM,
   // [2 + stage] query side (written per streamed query tile by the statistics warp)
   unsigned char* aug = tiles + C::kSmemTiles;
   const uint32_t sAug = sV + C::kSmemTiles;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nblk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const SeqInfo si = seq_info(p, b);
-  const int n0 = nblk * kT;
-  if (n0 >= si.k_len) return;
   const int G = p.heads_q / p.heads_kv;
   const int off = p.q_pos_offset;
 
-  int qlo, qhi;
-  visible_query_range(cfg, n0, min(n0 + kT, si.k_len) - 1, off, si.q_len + off, qlo, qhi);
-  const int m_lo = max(qlo - off, 0) / kT;
-  const int m_hi = (max(qhi - off, 0) + kT - 1) / kT;
-  const int ntiles = max(m_hi - m_lo, 0);
-  const int total = ntiles * G;
-#ifdef FA_TRACE
-  const long long cta_c0 = clock64();
-  const unsigned long long cta_g0 = gtimer();
-#endif
+  auto slotA = [&](int pos) { return sRingQ + (pos % SQ) * C::kTileBytes; };
+  auto slotB = [&](int pos) { return sRingO + (pos % SO) * C::kTileBytes; };
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
+    mbar_init(smem_u32(&sh->res_free), 1);
     mbar_init(smem_u32(&sh->s_full[0]), 1);
     mbar_init(smem_u32(&sh->s_full[1]), 1);
     mbar_init(smem_u32(&sh->dp_full), 1);
@@ -281,11 +452,17 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&sh->acc_done), 1);
     mbar_init(smem_u32(&sh->k_copied), 256);
     for (int i = 0; i < 4; ++i) {
-      mbar_init(smem_u32(&sh->full_a[i]), 2);   // the TMA load of Q and the statistics warp
+      mbar_init(smem_u32(&sh->full_a[i]), 2);   // the TMA load and the statistics warp (or two stand-in arrivals)
       mbar_init(smem_u32(&sh->full_b[i]), 1);
-      mbar_init(smem_u32(&sh->empty_a[i]), 2);  // one commit from each of the two issuer warps
+      mbar_init(smem_u32(&sh->empty_a[i]), 2);  // one commit from each of the two issuer warps (or a stand-in)
       mbar_init(smem_u32(&sh->empty_b[i]), 2);
     }
+    for (int i = 0; i < kSched; ++i) {
+      mbar_init(smem_u32(&sh->sched_full[i]), 1);
+      mbar_init(smem_u32(&sh->sched_empty[i]), kConsumers);
+    }
+    mbar_init(smem_u32(&sh->stg_ready[0]), 128);
+    mbar_init(smem_u32(&sh->stg_ready[1]), 128);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -321,407 +498,600 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // TMEM: R (128 fp32 columns: S^T, then dP^T of a tile) | X (64: P^T, then dS^T) | K (64) | dV | dK
   const uint32_t tR = tmem, tX = tmem + 128, tK = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
 
+  // Ring bookkeeping shared by every role.  An item with `total` query tiles takes, in order,
+  //   ring A:  K | Q(0) ... Q(total-1)        (total + 1 entries)
+  //   ring B:  dO(0) ... dO(total-1)          (total entries)
+  // and every role advances the same two position counters; entry `pos` lives in slot
+  // pos % stages and completes phase (pos / stages) & 1 of that slot's barriers.  The entries of
+  // the LAST tile are released by the epilogue (which stages dK and dV over them), the others
+  // by the commits of the two issuer warps.
+
   if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
     reg_dealloc<kRegsService>();
-    if (lane == 0 && total > 0) {
+    if (lane == 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
       prefetch_tmap(&tmdO);
-      {
-        const uint32_t bar = smem_u32(&sh->res_full);
-        mbar_expect_tx(bar, 2 * C::kTileBytes);
-        load_tile<D>(sKland, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
-        load_tile<D>(sV, &tmV, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
-      }
-      for (int it = 0; it < total; ++it) {
-        const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-        const int sq = it % C::kStagesQ, so = it % C::kStagesO;
-        // Q's slot frees after dK of the tile that held it; the last slot holds K at first
-        if (!bwait_relaxed(&sh->empty_a[sq], ((it / C::kStagesQ) & 1) ^ 1, sh, 41)) break;
-        if (it == C::kStagesQ - 1 && !bwait_relaxed(&sh->k_copied, 0, sh, 41)) break;
+      prefetch_tmap(&tmdK);
+      prefetch_tmap(&tmdV);
+      int posA = 0, posB = 0, wi = 0, fidx = 0;
+      bool ok = true;
+      auto acquire_a = [&]() { return bwait_relaxed(&sh->empty_a[posA % SQ], ((posA / SQ) & 1) ^ 1, sh, 41); };
+      auto acquire_b = [&]() { return bwait_relaxed(&sh->empty_b[posB % SO], ((posB / SO) & 1) ^ 1, sh, 41); };
+      auto decode = [&](int c, KItem& w) { return dkdv_item(p, cfg, c, nkb, w); };
+      // An item is drawn from the queue as late as possible -- when the loads of the previous one
+      // are all issued, a tile or two before it ends -- so that the CTAs share the work evenly;
+      // the other roles look one entry ahead only at the end of an item.
+      PROF_VARS(4);
+      for (;;) {
+        PROF_T0();
+        const KItem w = sched_publish<KItem>(sh, queue, ncand, fidx, ok, decode);
+        PROF_ADD(0);
+        if (!ok || w.total < 0) break;
+        if (w.total == 0) continue;
+        PROF_T0();
+        // K: a ring A entry; the second arrival of its barrier is made here
+        if (!(ok = acquire_a())) break;
         {
-          const uint32_t bar = smem_u32(&sh->full_a[sq]);
+          const uint32_t bar = smem_u32(&sh->full_a[posA % SQ]);
           mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingQ + sq * C::kTileBytes, &tmQ, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+          load_tile<D>(slotA(posA), &tmK, bar, w.g.k_row0 + w.n0, w.hk, w.g.k_boff);
+          mbar_arrive(bar);
+          ++posA;
         }
-        if (!bwait_relaxed(&sh->empty_b[so], ((it / C::kStagesO) & 1) ^ 1, sh, 41)) break;
-        {
-          const uint32_t bar = smem_u32(&sh->full_b[so]);
-          mbar_expect_tx(bar, C::kTileBytes);
-          load_tile<D>(sRingO + so * C::kTileBytes, &tmdO, bar, (int)si.q_row0 + m * kT, hq, (int)si.q_boff);
+        for (int it = 0; it < w.total; ++it) {
+          const int hq = w.hk * G + it / w.ntiles, m = w.m_lo + it % w.ntiles;
+          if (!(ok = acquire_a())) break;
+          {
+            const uint32_t bar = smem_u32(&sh->full_a[posA % SQ]);
+            mbar_expect_tx(bar, C::kTileBytes);
+            load_tile<D>(slotA(posA), &tmQ, bar, w.g.q_row0 + m * kT, hq, w.g.q_boff);
+            ++posA;
+          }
+          if (!(ok = acquire_b())) break;
+          {
+            const uint32_t bar = smem_u32(&sh->full_b[posB % SO]);
+            mbar_expect_tx(bar, C::kTileBytes);
+            load_tile<D>(slotB(posB), &tmdO, bar, w.g.q_row0 + m * kT, hq, w.g.q_boff);
+            ++posB;
+          }
+          if (it == 0) {
+            // V (first needed by dP(0), after the first score tile): its slot is free once the last
+            // dP GEMM of the previous item has read it.  Requested after the first Q and dO tiles so
+            // that those never queue behind this wait.
+            if (wi > 0 && !(ok = bwait_relaxed(&sh->res_free, (wi - 1) & 1, sh, 41))) break;
+            const uint32_t bar = smem_u32(&sh->res_full);
+            mbar_expect_tx(bar, C::kTileBytes);
+            load_tile<D>(sV, &tmV, bar, w.g.k_row0 + w.n0, w.hk, w.g.k_boff);
+          }
         }
+        if (!ok) break;
+        ++wi;
+        PROF_ADD(1);
       }
+      PROF_FLUSH(true, 28, 4);
     }
   } else if (warp == 10) {
     // ------------------------------- statistics loader ----------------------------------
-    // The loads of tile it+1 are ISSUED right after tile it has been written and only consumed
-    // after the wait for the next slot, so their latency hides behind that wait (nothing reads
-    // the registers in between: a scoreboard stall before the poll would serialise the two).
+    // The loads of the next tile are ISSUED right after the current one has been written and only
+    // consumed after the wait for the next slot, so their latency hides behind that wait.
     reg_dealloc<kRegsService>();
-    int stage = 0;
-    uint32_t phase = 0;
     float rl[kT / 32], rd[kT / 32];                  // statistics of rows lane, lane + 32, ... as loaded
-    auto fetch = [&](int it) {
-      const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
+    auto fetch = [&](const KItem& w, int it) {
+      const int hq = w.hk * G + it / w.ntiles, m = w.m_lo + it % w.ntiles;
 #pragma unroll
       for (int k = 0; k < kT / 32; ++k) {
         const int row = m * kT + lane + 32 * k;
         rl[k] = INFINITY;
         rd[k] = 0.f;
-        if (row < si.q_len) {
-          const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
+        if (row < w.g.q_len) {
+          const int64_t idx = (int64_t)w.g.q_boff * p.lse_stride[0] + (int64_t)(w.g.q_row0 + row) * p.lse_stride[1] +
                               (int64_t)hq * p.lse_stride[2];
           rl[k] = p.lse2[idx];
           rd[k] = p.delta[idx];
         }
       }
     };
-    if (total > 0) fetch(0);
-    for (int it = 0; it < total; ++it) {
-      bool w = true;
-      if (lane == 0) w = bwait_relaxed(&sh->empty_a[stage], phase ^ 1, sh, 42);
-      if (!__all_sync(0xffffffffu, w)) break;
-      uint4* q4 = reinterpret_cast<uint4*>(aug + (2 + stage) * C::kAugBytes);
-#pragma unroll
-      for (int k = 0; k < kT / 32; ++k) {
-        const int i = lane + 32 * k;
-        // NEGATED; rows that do not exist or see no key get a large finite value instead of
-        // infinity (an infinity would meet the zeros of the other GEMM's key-side operand): P = 0
-        float nl2 = -rl[k];
-        const float ndl = -rd[k];
-        if (!(fabsf(nl2) < 60000.f)) nl2 = -60000.f;
-        // the feature variant adds the LSE after the soft cap, in the element-wise warps
-        if (kExtras) sh->lse[stage][i] = nl2 == -60000.f ? -INFINITY : nl2;
-        const float lf = kExtras ? 0.f : nl2;
-        const T l_hi = Elem<T>::from_f(lf), l_lo = Elem<T>::from_f(lf - Elem<T>::to_f(l_hi));
-        const T d_hi = Elem<T>::from_f(ndl), d_lo = Elem<T>::from_f(ndl - Elem<T>::to_f(d_hi));
-        const uint32_t lh = *reinterpret_cast<const uint16_t*>(&l_hi), ll = *reinterpret_cast<const uint16_t*>(&l_lo);
-        const uint32_t dh = *reinterpret_cast<const uint16_t*>(&d_hi), dl = *reinterpret_cast<const uint16_t*>(&d_lo);
-        q4[i] = make_uint4(lh | (lh << 16), ll | (ll << 16), dh | (dl << 16), 0u);
+    int posA = 0, sidx = 0;
+    bool ok = true, fetched = false;                 // fetched: tile 0 of the item about to run is in rl/rd
+    KItem w = sched_get<KItem>(sh, sidx++, true, ok);
+    while (ok && w.total >= 0) {
+      if (w.total == 0) {
+        w = sched_get<KItem>(sh, sidx++, true, ok);
+        continue;
       }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[stage]));
-      if (++stage == C::kStagesQ) { stage = 0; phase ^= 1; }
-      if (it + 1 < total) fetch(it + 1);
+      bool haven = false;
+      if (!fetched) fetch(w, 0);
+      ++posA;                                        // the K entry
+      for (int it = 0; it < w.total; ++it, ++posA) {
+        const int stage = posA % SQ;
+        bool wt = true;
+        if (lane == 0) wt = bwait_relaxed(&sh->empty_a[stage], ((posA / SQ) & 1) ^ 1, sh, 42);
+        if (!__all_sync(0xffffffffu, wt)) { ok = false; break; }
+        uint4* q4 = reinterpret_cast<uint4*>(aug + (2 + stage) * C::kAugBytes);
+#pragma unroll
+        for (int k = 0; k < kT / 32; ++k) {
+          const int i = lane + 32 * k;
+          // NEGATED; rows that do not exist or see no key get a large finite value instead of
+          // infinity (an infinity would meet the zeros of the other GEMM's key-side operand): P = 0.
+          // delta is clamped into the 16-bit range for the same reason.
+          float nl2 = -rl[k];
+          float ndl = fminf(fmaxf(-rd[k], -60000.f), 60000.f);
+          if (!(fabsf(nl2) < 60000.f)) nl2 = -60000.f;
+          // the feature variant adds the LSE after the soft cap, in the element-wise warps
+          if (kExtras) sh->lse[stage][i] = nl2 == -60000.f ? -INFINITY : nl2;
+          const float lf = kExtras ? 0.f : nl2;
+          const T l_hi = Elem<T>::from_f(lf), l_lo = Elem<T>::from_f(lf - Elem<T>::to_f(l_hi));
+          const T d_hi = Elem<T>::from_f(ndl), d_lo = Elem<T>::from_f(ndl - Elem<T>::to_f(d_hi));
+          const uint32_t lh = *reinterpret_cast<const uint16_t*>(&l_hi), ll = *reinterpret_cast<const uint16_t*>(&l_lo);
+          const uint32_t dh = *reinterpret_cast<const uint16_t*>(&d_hi), dl = *reinterpret_cast<const uint16_t*>(&d_lo);
+          q4[i] = make_uint4(lh | (lh << 16), ll | (ll << 16), dh | (dl << 16), 0u);
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[stage]));
+        if (it + 1 < w.total) {
+          fetch(w, it + 1);
+        } else {
+          // the entry after this one (published once the loads of this item are issued), if it
+          // has work, gets its first tile fetched ahead
+          const KItem wn = sched_get<KItem>(sh, sidx, false, ok);
+          if (!ok) break;
+          haven = wn.total > 0;
+          if (haven) fetch(wn, 0);
+        }
+      }
+      if (!ok) break;
+      fetched = haven;
+      w = sched_get<KItem>(sh, sidx++, true, ok);
     }
   } else if (warp == 9) {
-    // ------------------------------- MMA issuer -----------------------------------------
+    // ------------------------------- MMA issuer, GEMMs into the fp32 region -------------
+    // This warp issues dP(i), then S(i+1) -- each once the element-wise warps have read its
+    // predecessor out of R (r_free).  Warp 11 issues the accumulating GEMMs dV(i), dK(i) that
+    // read P, dS from region X.
     reg_dealloc<kRegsService>();
-    if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
-      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
-      const uint32_t leader = elect_one() ? 1u : 0u;
-      bool ok = true;
-      // every lane polls (uniform control flow, no vote needed: a completed phase is seen by all)
-      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
-        if (ok) ok = bwait(bar, parity, sh, code);
-        tc_fence_after();
-      };
-      auto slotQ = [&](int it) { return sRingQ + (it % C::kStagesQ) * C::kTileBytes; };
-      auto slotO = [&](int it) { return sRingO + (it % C::kStagesO) * C::kTileBytes; };
-      auto stat_desc = [&](int it) {
-        return make_smem_desc_noswizzle(sAug + (2 + it % C::kStagesQ) * C::kAugBytes, 2048, 128);
-      };
-      const uint64_t dstat_s = make_smem_desc_noswizzle(sAug, 2048, 128);
-      const uint64_t dstat_dp = make_smem_desc_noswizzle(sAug + C::kAugBytes, 2048, 128);
-      // S^T(i) = K Q(i)^T (K from TMEM) - lse2 / scale_log2; waits for Q(i) and its statistics
-      auto issue_s = [&](int i) {
-        const int st = i % C::kStagesQ;
-        const uint32_t ph = (i / C::kStagesQ) & 1;
-        wq(&sh->full_a[st], ph, 44);
-        if (i > 0) wq(&sh->r_free, 1, 49);                                     // dP(i-1) read out
-        if (!ok) return;
-        mma_kmajor_ts<D>(tR, tK, slotQ(i), idesc_s, leader);
-        if (!kExtras) mma_f16_ss_lp(tR, dstat_s, stat_desc(i), idesc_s, 1u, leader);
-        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
-      };
-      // This warp issues the GEMMs into the fp32 region R: dP(i), then S(i+1) -- each once the
-      // element-wise warps have read its predecessor out of R (r_free).  Warp 11 issues the
-      // accumulating GEMMs dV(i), dK(i) that read P, dS from region X.  The exp2 phase of tile
-      // i+1 runs under dK(i), dP(i+1); its dS phase under dV(i+1), S(i+2).
-      wq(&sh->res_full, 0, 43);
-      wq(&sh->k_copied, 0, 43);
-      issue_s(0);
-      for (int i = 0; i < total && ok; ++i) {
-        const int st = i % C::kStagesQ, so = i % C::kStagesO;
-        FA_BTRACE(2, i, 0);
-        wq(&sh->full_b[so], (i / C::kStagesO) & 1, 44);
-        FA_BTRACE(2, i, 1);
-        wq(&sh->r_free, 0, 49);                                                // S(i) read out
-        if (!ok) break;
-        FA_BTRACE(2, i, 2);
-        mma_kmajor<D>(tR, sV, slotO(i), idesc_s, leader);                      // dP^T(i) = V dO(i)^T
-        mma_f16_ss_lp(tR, dstat_dp, stat_desc(i), idesc_s, 1u, leader);        //           - delta
-        mma_commit_lp(smem_u32(&sh->dp_full), leader);
-        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);   // this warp's last reads of dO(i) and of
-        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);   // Q(i) and its statistics
-        FA_BTRACE(2, i, 3);
-        if (i + 1 < total) issue_s(i + 1);
-        FA_BTRACE(2, i, 4);
-      }
+    constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    bool ok = true;
+    // every lane polls (uniform control flow, no vote needed: a completed phase is seen by all)
+    auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (ok) ok = bwait(bar, parity, sh, code);
+      tc_fence_after();
+    };
+    const uint64_t dstat_s = make_smem_desc_noswizzle(sAug, 2048, 128);
+    const uint64_t dstat_dp = make_smem_desc_noswizzle(sAug + C::kAugBytes, 2048, 128);
+    auto stat_desc = [&](int pos) {
+      return make_smem_desc_noswizzle(sAug + (2 + pos % SQ) * C::kAugBytes, 2048, 128);
+    };
+    PROF_VARS(8);
+    int posA = 0, posB = 0, wi = 0, tg = 0;          // tg: tiles issued so far by this CTA
+    // S^T = K Q^T (K from TMEM) - lse2 / scale_log2 for the tile at ring position qpos
+    auto issue_s = [&](int qpos, int tile_no) {
+      PROF_T0();
+      wq(&sh->full_a[qpos % SQ], (qpos / SQ) & 1, 44);
+      PROF_ADD(1);
+      PROF_T0();
+      if (tile_no > 0) wq(&sh->r_free, 1, 49);                                  // the previous dP read out
+      PROF_ADD(2);
+      if (!ok) return;
+      mma_kmajor_ts<D>(tR, tK, slotA(qpos), idesc_s, leader);
+      if (!kExtras) mma_f16_ss_lp(tR, dstat_s, stat_desc(qpos), idesc_s, 1u, leader);
+      mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+    };
+    int sidx = 0;
+    for (;;) {
+      PROF_T0();
+      const KItem w = sched_get<KItem>(sh, sidx++, true, ok);
+      if (!ok || w.total < 0) break;
+      PROF_ADD(6);
+      if (w.total == 0) continue;
+      // K is in TMEM: its ring slot may be refilled (stand-in for the two MMA commits of a Q entry)
+      PROF_T0();
+      wq(&sh->k_copied, wi & 1, 43);
+      PROF_ADD(0);
+      if (!ok) break;
+      if (leader) mbar_arrive_cnt(smem_u32(&sh->empty_a[posA % SQ]), 2);
       __syncwarp();
+      const int q0pos = posA + 1;
+      issue_s(q0pos, tg);
+      for (int i = 0; i < w.total && ok; ++i, ++tg) {
+        const int qpos = q0pos + i, opos = posB + i;
+        PROF_T0();
+        wq(&sh->full_b[opos % SO], (opos / SO) & 1, 44);
+        PROF_ADD(3);
+        PROF_T0();
+        if (i == 0) wq(&sh->res_full, wi & 1, 43);                              // V of this item
+        PROF_ADD(4);
+        PROF_T0();
+        wq(&sh->r_free, 0, 49);                                                 // S(i) read out
+        PROF_ADD(5);
+        if (!ok) break;
+        mma_kmajor<D>(tR, sV, slotB(opos), idesc_s, leader);                    // dP^T(i) = V dO(i)^T
+        mma_f16_ss_lp(tR, dstat_dp, stat_desc(qpos), idesc_s, 1u, leader);      //           - delta
+        mma_commit_lp(smem_u32(&sh->dp_full), leader);
+        if (i + 1 < w.total) {
+          mma_commit_lp(smem_u32(&sh->empty_b[opos % SO]), leader);   // this warp's last reads of dO(i) and of
+          mma_commit_lp(smem_u32(&sh->empty_a[qpos % SQ]), leader);   // Q(i) and its statistics
+          issue_s(qpos + 1, tg + 1);
+        } else {
+          mma_commit_lp(smem_u32(&sh->res_free), leader);             // ... and of V (the epilogue releases
+        }                                                             // the last tile's ring entries)
+      }
+      posA += w.total + 1;
+      posB += w.total;
+      ++wi;
     }
+    PROF_FLUSH(lane == 0, 16, 8);
+    __syncwarp();
   } else if (warp == 11) {
     // ------------------------------- MMA issuer, accumulations --------------------------
     reg_dealloc<kRegsService>();
-    if (total > 0) {
-      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
-      const uint32_t leader = elect_one() ? 1u : 0u;
-      bool ok = true;
-      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
-        if (ok) ok = bwait(bar, parity, sh, code);
-        tc_fence_after();
-      };
-      for (int i = 0; i < total && ok; ++i) {
-        const int st = i % C::kStagesQ, so = i % C::kStagesO;
+    constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    bool ok = true;
+    auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (ok) ok = bwait(bar, parity, sh, code);
+      tc_fence_after();
+    };
+    int posA = 0, posB = 0, tg = 0, sidx = 0, wi = 0;
+    PROF_VARS(4);
+    for (;;) {
+      PROF_T0();
+      const KItem w = sched_get<KItem>(sh, sidx++, true, ok);
+      if (!ok || w.total < 0) break;
+      PROF_ADD(3);
+      if (w.total == 0) continue;
+      for (int i = 0; i < w.total && ok; ++i, ++tg) {
+        const int qpos = posA + 1 + i, opos = posB + i;
         // dO(i) may land after P(i) is ready; Q(i) has been read by S(i) long before dS(i) exists
-        wq(&sh->full_b[so], (i / C::kStagesO) & 1, 44);
-        wq(&sh->p_ready, i & 1, 45);
+        PROF_T0();
+        wq(&sh->full_b[opos % SO], (opos / SO) & 1, 44);
+        PROF_ADD(0);
+        PROF_T0();
+        wq(&sh->p_ready, tg & 1, 45);
+        PROF_ADD(1);
         if (!ok) break;
-        mma_from_tmem<D, 32>(tdV, tX, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader);  // dV += P(i)^T dO(i)
-        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
+        const bool last = i + 1 == w.total;          // its ring entries are released by the epilogue
+        mma_from_tmem<D, 32>(tdV, tX, slotB(opos), idesc_acc, i > 0, leader);   // dV += P(i)^T dO(i)
+        if (!last) mma_commit_lp(smem_u32(&sh->empty_b[opos % SO]), leader);
         mma_commit_lp(smem_u32(&sh->p_free), leader);
-        wq(&sh->ds_ready, i & 1, 46);
+        PROF_T0();
+        wq(&sh->ds_ready, tg & 1, 46);
+        PROF_ADD(2);
         if (!ok) break;
-        mma_from_tmem<D, 32>(tdK, tX, sRingQ + st * C::kTileBytes, idesc_acc, i > 0, leader);  // dK += dS(i)^T Q(i)
-        mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
+        mma_from_tmem<D, 32>(tdK, tX, slotA(qpos), idesc_acc, i > 0, leader);   // dK += dS(i)^T Q(i)
+        if (!last) mma_commit_lp(smem_u32(&sh->empty_a[qpos % SQ]), leader);
         mma_commit_lp(smem_u32(&sh->ds_free), leader);
       }
-      mma_commit_lp(smem_u32(&sh->acc_done), leader);
-      __syncwarp();
+      if (ok) mma_commit_lp(smem_u32(&sh->acc_done), leader);
+      // The element-wise warps now stage dV and dK over the item's last dO and Q tiles.  This warp
+      // has nothing to issue until the first P of the next item exists, so it hands the staged
+      // tiles to the TMA unit and releases the two ring entries once the unit has read them.
+      {
+        const int stgA = posA + w.total, stgB = posB + w.total - 1;
+#ifdef FA_X_DIRECT
+        const bool via_tma = false;
+#else
+        const bool via_tma = (p.cu_seqlens_k == nullptr) || (w.n0 + kT <= w.g.k_len);
+#endif
+        wq(&sh->stg_ready[0], wi & 1, 62);
+        if (ok && via_tma && leader) {
+#pragma unroll
+          for (int bx = 0; bx < D / 64; ++bx)
+            tma_store_4d(&tmdV, slotB(stgB) + bx * (kT * 128), bx * 64, w.hk, w.g.k_row0 + w.n0, w.g.k_boff);
+        }
+        wq(&sh->stg_ready[1], wi & 1, 62);
+        if (ok && leader) {
+          if (via_tma) {
+#pragma unroll
+            for (int bx = 0; bx < D / 64; ++bx)
+              tma_store_4d(&tmdK, slotA(stgA) + bx * (kT * 128), bx * 64, w.hk, w.g.k_row0 + w.n0, w.g.k_boff);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+          // released like tiles whose two readers have finished
+          mbar_arrive_cnt(smem_u32(&sh->empty_b[stgB % SO]), 2);
+          mbar_arrive_cnt(smem_u32(&sh->empty_a[stgA % SQ]), 2);
+        }
+        __syncwarp();
+      }
+      posA += w.total + 1;
+      posB += w.total;
+      ++wi;
     }
+    PROF_FLUSH(lane == 0, 24, 4);
+    __syncwarp();
   } else {
     // ------------------------------- element-wise groups --------------------------------
     reg_alloc<kRegsEw>();
     const int x = warp >> 2;                         // column half
     const int lrow = (warp & 3) * 32 + lane;         // TMEM lane = key inside the tile
-    const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tRx = tR + lane_addr + x * kHalfT;            // fp32 scores / dP: this group's 64 columns
     const uint32_t tXx = tX + lane_addr + x * (kHalfT / 2);      // P^T, then dS^T, as 16-bit pairs: 32 columns
     bool ok = true;
-    if (total > 0) {
-      // K: from its landing slot (which then joins the Q ring) into TMEM, where the score GEMM
-      // reads it as the A operand.  This thread copies its key row, group x the x-th half of it.
-      ok = bwait(&sh->res_full, 0, sh, 43);
-      if (ok) {
-        constexpr int kChunks = D / 16;              // 16-byte chunks per group
-        uint32_t kr[kChunks / 4][16];
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int g = x * kChunks + c;
-          const uint4 v = ld_shared_v4(sw128_addr(sKland + (g / 8) * (kT * 128), lrow, g % 8));
-          kr[c / 4][(c % 4) * 4] = v.x; kr[c / 4][(c % 4) * 4 + 1] = v.y;
-          kr[c / 4][(c % 4) * 4 + 2] = v.z; kr[c / 4][(c % 4) * 4 + 3] = v.w;
-        }
-#pragma unroll
-        for (int c = 0; c < kChunks / 4; ++c) tmem_st16(tK + lane_addr + x * (D / 4) + c * 16, kr[c]);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&sh->k_copied));
-      }
-    }
-    for (int it = 0; it < total && ok; ++it) {
-      const int stage = it % C::kStagesQ;
-      const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
-      const int q0 = m * kT + x * kHalfT;            // first query row of this thread's columns
-      const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + hq] : 0.f;
-      bool masked = false;
-      if (cfg.causal) masked |= (n0 + kT - 1 > q0 + off);
-      if (cfg.wl >= 0) masked |= (n0 < q0 + kHalfT - 1 + off - cfg.wl);
-      if (cfg.wr >= 0) masked |= (n0 + kT - 1 > q0 + off + cfg.wr);
+    int posA = 0, posB = 0, wi = 0, tg = 0, sidx = 0;
+    bool k_in_tmem = false;                          // K of the item about to run is already in TMEM
+    PROF_VARS(16);
+#ifdef FA_PROF
+    const long long prof_start = clock64();
+    long long prof_t1 = 0;
+#endif
 
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 0);
-      // Only the feature path still needs the LSE per column (it is added after the soft cap);
-      // it is fetched into registers BEFORE the wait for the scores: shared-memory loads issued
-      // while the tensor pipe streams its operands take hundreds of cycles, and here that
-      // latency hides behind the wait.  Otherwise the GEMMs deliver S - lse and dP - delta.
-      float st[kHalfT];                              // -lse, later the soft cap's tanh factor
-      if (kExtras) {
-        ok = bwait(&sh->full_a[stage], (it / C::kStagesQ) & 1, sh, 47);
-        if (!ok) break;
-        const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
+    // K of an item: from its ring slot into TMEM, where the score GEMM reads it as the A operand.
+    // This thread copies its key row, group x the x-th half of it.
+    auto copy_k = [&](int kpos) {
+      ok = bwait(&sh->full_a[kpos % SQ], (kpos / SQ) & 1, sh, 43);
+      if (!ok) return;
+      constexpr int kChunks = D / 16;                // 16-byte chunks per group
+      const uint32_t src = slotA(kpos);
+      uint32_t kr[kChunks / 4][16];
 #pragma unroll
-        for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
-          const float4 l4 = L4[i4];
-          st[i4 * 4] = l4.x; st[i4 * 4 + 1] = l4.y; st[i4 * 4 + 2] = l4.z; st[i4 * 4 + 3] = l4.w;
-        }
+      for (int c = 0; c < kChunks; ++c) {
+        const int g = x * kChunks + c;
+        const uint4 v = ld_shared_v4(sw128_addr(src + (g / 8) * (kT * 128), lrow, g % 8));
+        kr[c / 4][(c % 4) * 4] = v.x; kr[c / 4][(c % 4) * 4 + 1] = v.y;
+        kr[c / 4][(c % 4) * 4 + 2] = v.z; kr[c / 4][(c % 4) * 4 + 3] = v.w;
       }
-      ok = bwait(&sh->s_full[0], it & 1, sh, 46);
-      if (!ok) break;
-      tc_fence_after();
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 1);
-
-      // ---- exp phase: P = exp2(score - lse), written back over S as T pairs -------------
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tRx, r0);
-      tmem_ld32(tRx + 32, r1);
-      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < kChunks / 4; ++c) tmem_st16(tK + lane_addr + x * (D / 4) + c * 16, kr[c]);
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->r_free));            // the scores are in registers: dP may take the region
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 2);
-      float pf[kHalfT];                              // P in fp32, kept for the dS phase
-      const float dist0 = (float)(q0 + off - key);   // query position - key position of column 0
-      auto exp_body = [&](auto slow_tag) {
-        constexpr bool kSlow = decltype(slow_tag)::value;
-        if (kSlow) {
+      mbar_arrive(smem_u32(&sh->k_copied));
+    };
+
+    KItem w, wn;                                     // wn: the entry after the current one, once looked at
+    bool peeked = false;
+    for (;;) {
+      PROF_T0();
+      if (peeked) {
+        sched_release(sh, sidx++);
+        w = wn;
+      } else {
+        w = sched_get<KItem>(sh, sidx++, true, ok);
+      }
+      if (!ok || w.total < 0) break;
+      peeked = false;
+      PROF_ADD(7);
+      const int key = w.n0 + lrow;
+      // group A stores dV, group B stores dK * softmax_scale
+      T* grow = nullptr;
+      if (key < w.g.k_len)
+        grow = (x == 0) ? reinterpret_cast<T*>(p.dv) + (int64_t)w.g.k_boff * p.dv_stride[0] +
+                              (int64_t)(w.g.k_row0 + key) * p.dv_stride[1] + (int64_t)w.hk * p.dv_stride[2]
+                        : reinterpret_cast<T*>(p.dk) + (int64_t)w.g.k_boff * p.dk_stride[0] +
+                              (int64_t)(w.g.k_row0 + key) * p.dk_stride[1] + (int64_t)w.hk * p.dk_stride[2];
+      if (w.total == 0) {
+        // no query can see these keys: their gradients are zero
+        if (grow != nullptr) {
 #pragma unroll
-          for (int i = 0; i < kHalfT; ++i) {
-            const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
-            const int qp = q0 + i + off;
-            float th = 0.f;
-            float sc;
-            if (kExtras) sc = score_log2_dist(cfg, slope, sv, dist0 + (float)i, th) + st[i];
-            else sc = sv * cfg.scale_log2;
-            float pe = ex2(sc);
-            if (masked && !visible(cfg, qp, key, 0x7fffffff)) pe = 0.f;
-            pf[i] = pe;
-            // the tanh factor of the soft cap is folded into the copy kept for dS
-            if (kExtras && cfg.softcap > 0.f) st[i] = 1.f - th * th;
-          }
-        } else {
-          const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2);
+          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(grow)[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      int vq_lo, vq_hi;                              // query positions that see this thread's key
+      visible_q_interval(cfg, key, vq_lo, vq_hi);
+      PROF_T0();
+      if (!k_in_tmem) copy_k(posA);
+      PROF_ADD(4);
+      if (!ok) break;
+      const int q0pos = posA + 1;
+      PROF_COUNT(9, w.total);
+      PROF_COUNT(10, 1);
+
+      for (int it = 0; it < w.total && ok; ++it, ++tg) {
+        const int stage = (q0pos + it) % SQ;
+        const int hq = w.hk * G + it / w.ntiles, m = w.m_lo + it % w.ntiles;
+        const int q0 = m * kT + x * kHalfT;            // first query row of this thread's columns
+        const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[w.b * p.heads_q + hq] : 0.f;
+        bool masked = false;
+        if (cfg.causal) masked |= (w.n0 + kT - 1 > q0 + off);
+        if (cfg.wl >= 0) masked |= (w.n0 < q0 + kHalfT - 1 + off - cfg.wl);
+        if (cfg.wr >= 0) masked |= (w.n0 + kT - 1 > q0 + off + cfg.wr);
+
+        // Only the feature path still needs the LSE per column (it is added after the soft cap);
+        // it is fetched into registers BEFORE the wait for the scores: shared-memory loads issued
+        // while the tensor pipe streams its operands take hundreds of cycles, and here that
+        // latency hides behind the wait.  Otherwise the GEMMs deliver S - lse and dP - delta.
+        float st[kHalfT];                              // -lse, later the soft cap's tanh factor
+        if (kExtras) {
+          ok = bwait(&sh->full_a[stage], ((q0pos + it) / SQ) & 1, sh, 47);
+          if (!ok) break;
+          const float4* L4 = reinterpret_cast<const float4*>(&sh->lse[stage][x * kHalfT]);
 #pragma unroll
-          for (int i = 0; i < kHalfT; i += 2) {
-            const uint32_t* rr = i < 32 ? r0 : r1;
-            const float2 a = f2mul(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2);
-            const float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
-            pf[i] = pe.x;
-            pf[i + 1] = pe.y;
+          for (int i4 = 0; i4 < kHalfT / 4; ++i4) {
+            const float4 l4 = L4[i4];
+            st[i4 * 4] = l4.x; st[i4 * 4 + 1] = l4.y; st[i4 * 4 + 2] = l4.z; st[i4 * 4 + 3] = l4.w;
           }
         }
-      };
-      if (kExtras || masked) exp_body(std::true_type{});
-      else exp_body(std::false_type{});
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 3);
-      // X holds dS(it-1) until its dK MMA has finished (ds_free)
-      if (it > 0) {
-        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 50);
+        PROF_T0();
+        ok = bwait(&sh->s_full[0], tg & 1, sh, 46);
+#ifdef FA_PROF
+        if (it == 0) PROF_ADD(11); else PROF_ADD(0);
+        prof_t1 = clock64();
+#endif
         if (!ok) break;
         tc_fence_after();
-      }
-      {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
-          tmem_st16(tXx + c * 16, pk);
-        }
-      }
-      if (kExtras && cfg.softcap > 0.f) {
-#pragma unroll
-        for (int i = 0; i < kHalfT; ++i) pf[i] *= st[i];
-      }
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 4);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh->p_ready));
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 5);
 
-      // ---- dS phase: dS = P (dP - delta), written back over dP ---------------------------
-      ok = bwait(&sh->dp_full, it & 1, sh, 48);
-      if (!ok) break;
-      tc_fence_after();
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 6);
-      tmem_ld32(tRx, r0);
-      tmem_ld32(tRx + 32, r1);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh->r_free));            // dP is in registers: the next S may take the region
-      uint32_t pk0[16], pk1[16];
+        // ---- exp phase: P = exp2(score - lse), written back as T pairs ---------------------
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tRx, r0);
+        tmem_ld32(tRx + 32, r1);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->r_free));            // the scores are in registers: dP may take the region
+        float pf[kHalfT];                              // P in fp32, kept for the dS phase
+        const float dist0 = (float)(q0 + off - key);   // query position - key position of column 0
+        // columns (query rows) of this tile that see this thread's key
+        const ColMask cm = make_col_mask(vq_lo - (q0 + off), vq_hi - (q0 + off));
+        // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
+        auto exp_body = [&](auto mask_tag, auto cap_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
+          constexpr bool kCap = decltype(cap_tag)::value;
+          if (kExtras) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int e = 2 * i;
-        const uint32_t* rr = e < 32 ? r0 : r1;
-        const float2 ds = f2mul(make_float2(pf[e], pf[e + 1]),
-                                make_float2(__uint_as_float(rr[e & 31]), __uint_as_float(rr[(e & 31) + 1])));
-        if (i < 16) pk0[i] = Elem<T>::pack(ds.x, ds.y);
-        else pk1[i - 16] = Elem<T>::pack(ds.x, ds.y);
-      }
-      // X holds P(it) until its dV MMA has finished (p_free)
-      ok = bwait(&sh->p_free, it & 1, sh, 51);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_st16(tXx, pk0);
-      tmem_st16(tXx + 16, pk1);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh->ds_ready));
-      if ((warp & 3) == 0) FA_BTRACE(x, it, 7);
-    }
-
-    // ---- epilogue: group A stores dV, group B stores dK * softmax_scale -------------------
-    // Each group stages its tile in shared memory (dV over V, dK over a Q slot: every MMA is done) in
-    // the swizzled box layout and lets the TMA unit write full rows; a packed tile that reaches
-    // past the end of its sequence is stored row by row instead.
-    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 49);
-    if (ok) {
-      tc_fence_after();
-      const uint32_t tsrc = (x == 0 ? tdV : tdK) + lane_addr;
-      const float mul = (x == 0) ? 1.f : cfg.scale;
-      const bool via_tma = (p.cu_seqlens_k == nullptr) || (n0 + kT <= si.k_len);
-      const uint32_t stg = (x == 0) ? sV : sRingQ;   // dV over V, dK over the first Q slot
-      T* base = (x == 0) ? reinterpret_cast<T*>(p.dv) + si.k_boff * p.dv_stride[0] +
-                               (si.k_row0 + key) * p.dv_stride[1] + (int64_t)hk * p.dv_stride[2]
-                         : reinterpret_cast<T*>(p.dk) + si.k_boff * p.dk_stride[0] +
-                               (si.k_row0 + key) * p.dk_stride[1] + (int64_t)hk * p.dk_stride[2];
+            for (int i = 0; i < kHalfT; ++i) {
+              const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
+              float th;
+              float pe = ex2(score_log2_feat<kCap>(cfg, slope, sv, dist0 + (float)i, th) + st[i]);
+              if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
+              pf[i] = pe;
+              // the tanh factor of the soft cap is folded into the copy kept for dS
+              if (kCap) st[i] = 1.f - th * th;
+            }
+          } else {
+            const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2);
 #pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t r[32];
-        if (total > 0) {
-          tmem_ld32(tsrc + cc * 32, r);
-          tmem_wait_ld();
+            for (int i = 0; i < kHalfT; i += 2) {
+              const uint32_t* rr = i < 32 ? r0 : r1;
+              const float2 a = f2mul(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2);
+              float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
+              if (kMask) {
+                pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+              }
+              pf[i] = pe.x;
+              pf[i + 1] = pe.y;
+            }
+          }
+        };
+        const bool cap = kExtras && cfg.softcap > 0.f;
+        if (masked) {
+          if (cap) exp_body(std::true_type{}, std::true_type{});
+          else exp_body(std::true_type{}, std::false_type{});
         } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          if (cap) exp_body(std::false_type{}, std::true_type{});
+          else exp_body(std::false_type{}, std::false_type{});
         }
+#ifdef FA_PROF
+        prof_acc[masked ? 13 : 12] += (unsigned int)(clock64() - prof_t1);
+        if (masked) prof_acc[14] += 1;
+#endif
+        // X holds dS of the previous tile until its dK MMA has finished (ds_free)
+        if (tg > 0) {
+          PROF_T0();
+          ok = bwait(&sh->ds_free, (tg - 1) & 1, sh, 50);
+          PROF_ADD(1);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          v.x = Elem<T>::pack(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
-          v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
-          v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
-          v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
-          if (via_tma) {
-            const int col = cc * 32 + i;
-            st_shared_v4(sw128_addr(stg + (col / 64) * (kT * 128), lrow, (col % 64) / 8), v);
-          } else if (key < si.k_len) {
-            *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
+          for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
+            tmem_st16(tXx + c * 16, pk);
           }
         }
-      }
-      if (via_tma) {
-        fence_proxy_async();
-        if (x == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        else asm volatile("bar.sync 2, 128;\n" ::: "memory");
-        if ((tid & 127) == 0) {
-          const CUtensorMap* tm = (x == 0) ? &tmdV : &tmdK;
+        if (kExtras && cfg.softcap > 0.f) {
 #pragma unroll
-          for (int bx = 0; bx < D / 64; ++bx)
-            tma_store_4d(tm, stg + bx * (kT * 128), bx * 64, hk, (int)si.k_row0 + n0, (int)si.k_boff);
-          tma_store_commit();
-          tma_store_wait_read();
+          for (int i = 0; i < kHalfT; ++i) pf[i] *= st[i];
         }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->p_ready));
+
+        // ---- dS phase: dS = P (dP - delta) -------------------------------------------------
+        PROF_T0();
+        ok = bwait(&sh->dp_full, tg & 1, sh, 48);
+        PROF_ADD(2);
+#ifdef FA_PROF
+        prof_t1 = clock64();
+#endif
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tRx, r0);
+        tmem_ld32(tRx + 32, r1);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->r_free));            // dP is in registers: the next S may take the region
+        uint32_t pk0[16], pk1[16];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int e = 2 * i;
+          const uint32_t* rr = e < 32 ? r0 : r1;
+          const float2 ds = f2mul(make_float2(pf[e], pf[e + 1]),
+                                  make_float2(__uint_as_float(rr[e & 31]), __uint_as_float(rr[(e & 31) + 1])));
+          if (i < 16) pk0[i] = Elem<T>::pack(ds.x, ds.y);
+          else pk1[i - 16] = Elem<T>::pack(ds.x, ds.y);
+        }
+#ifdef FA_PROF
+        prof_acc[15] += (unsigned int)(clock64() - prof_t1);
+#endif
+        // X holds P of this tile until its dV MMA has finished (p_free)
+        PROF_T0();
+        ok = bwait(&sh->p_free, tg & 1, sh, 51);
+        PROF_ADD(3);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_st16(tXx, pk0);
+        tmem_st16(tXx + 16, pk1);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->ds_ready));
       }
+      if (!ok) break;
+
+      // ---- end of the item ------------------------------------------------------------------
+      // K of the next item goes into TMEM first (every score GEMM of this item has finished, and
+      // the last dK GEMM still runs), so that the issuer can start on it during the epilogue.
+      const int stgA = posA + w.total, stgB = posB + w.total - 1;   // the last Q and dO tiles of the item
+      {
+        PROF_T0();
+        wn = sched_get<KItem>(sh, sidx, false, ok);
+        if (!ok) break;
+        peeked = true;
+        k_in_tmem = wn.total > 0;
+        PROF_ADD(7);
+        PROF_T0();
+        if (k_in_tmem) copy_k(stgA + 1);
+        PROF_ADD(4);
+        if (!ok) break;
+      }
+      // Epilogue: each group stages its tile over the item's last dO / Q tile (every MMA is done;
+      // swizzled box layout) and hands it to the second issuer warp, which lets the TMA unit write
+      // full rows; a packed tile that reaches past the end of its sequence is stored row by row instead.
+      PROF_T0();
+      ok = bwait(&sh->acc_done, wi & 1, sh, 49);
+      PROF_ADD(5);
+      if (!ok) break;
+      tc_fence_after();
+      PROF_T0();
+      const uint32_t stg = (x == 0) ? slotB(stgB) : slotA(stgA);
+#ifdef FA_X_DIRECT
+      const bool via_tma = false;
+#else
+      const bool via_tma = (p.cu_seqlens_k == nullptr) || (w.n0 + kT <= w.g.k_len);
+#endif
+      drain_acc<T, D>((x == 0 ? tdV : tdK) + lane_addr, (x == 0) ? 1.f : cfg.scale, via_tma, stg, lrow, 0, grow);
+      tc_fence_before();
+      if (via_tma) fence_proxy_async();
+      mbar_arrive(smem_u32(&sh->stg_ready[x]));
+      PROF_ADD(6);
+      posA += w.total + 1;
+      posB += w.total;
+      ++wi;
     }
+#ifdef FA_PROF
+    prof_acc[8] = (unsigned int)(clock64() - prof_start);
+#endif
+    PROF_FLUSH(tid == 0, 0, 12);
+#ifdef FA_PROF
+    if (tid == 0) for (int pi = 11; pi < 16; ++pi) atomicAdd(&PROF_ARRAY[32 + pi], (unsigned long long)prof_acc[pi]);
+#endif
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, 512);
-#ifdef FA_TRACE
   if (tid == 0) {
-    atomicAdd(&g_bwd_cta_stats[0], (unsigned long long)(clock64() - cta_c0));
-    atomicAdd(&g_bwd_cta_stats[1], (unsigned long long)total);
-    atomicAdd(&g_bwd_cta_stats[2], 1ull);
-    atomicMin(&g_bwd_cta_stats[3], cta_g0);
-    atomicMax(&g_bwd_cta_stats[4], gtimer());
+    if (sh->abort_flag == 0) sched_finish(queue);
+    report_abort(sh->abort_flag, host_status);
   }
-#endif
 }
 
 // =======================================================================================
@@ -731,37 +1101,31 @@ template <typename T, int D, bool kExtras>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const __grid_constant__ CUtensorMap tmdQ, const fa_attn_args p, const ScoreCfg cfg) {
+                    const __grid_constant__ CUtensorMap tmdQ, const fa_attn_args p, const ScoreCfg cfg,
+                    const int nmb, const int ncand, unsigned int* const queue,
+                    int* const host_status) {
   using C = BCfg<D>;
+  constexpr int SK = C::kStagesK, SV = C::kStagesV;
+  constexpr int kConsumers = 9;    // warps that read the work queue: 8 element-wise and the issuer
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTilesDq);
   const uint32_t sQ = smem_u32(tiles), sdO = sQ + C::kTileBytes;
-  const uint32_t sRingK = sdO + C::kTileBytes, sRingV = sRingK + C::kStagesK * C::kTileBytes;
+  const uint32_t sRingK = sdO + C::kTileBytes, sRingV = sRingK + SK * C::kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int mblk = cfg.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heavy blocks first
-  const SeqInfo si = seq_info(p, b);
-  const int m0 = mblk * kT;
-  if (m0 >= si.q_len) return;
-  const int hk = h / (p.heads_q / p.heads_kv);
   const int off = p.q_pos_offset;
 
-  int klo, khi;
-  visible_key_range(cfg, m0 + off, min(m0 + kT, si.q_len) - 1 + off, si.k_len, klo, khi);
-  const int n_lo = klo / kT;
-  const int n_hi = (khi + kT - 1) / kT;
-  // step j works on key tile n_hi - 1 - j: the masked tiles (diagonal, ragged end) come first
-  const int total = max(n_hi - n_lo, 0);
+  auto slotK = [&](int pos) { return sRingK + (pos % SK) * C::kTileBytes; };
+  auto slotV = [&](int pos) { return sRingV + (pos % SV) * C::kTileBytes; };
 
   if (tid == 0) {
     mbar_init(smem_u32(&sh->res_full), 1);
+    mbar_init(smem_u32(&sh->res_free), 2);    // the last S GEMM and the last dP GEMM of the item
     mbar_init(smem_u32(&sh->s_full[0]), 1);
     mbar_init(smem_u32(&sh->s_full[1]), 1);
     mbar_init(smem_u32(&sh->dp_full), 1);
-    mbar_init(smem_u32(&sh->p_ready), 256);
     mbar_init(smem_u32(&sh->ds_ready), 256);
     mbar_init(smem_u32(&sh->acc_done), 1);
     for (int i = 0; i < 4; ++i) {
@@ -770,6 +1134,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(smem_u32(&sh->empty_a[i]), 1);
       mbar_init(smem_u32(&sh->empty_b[i]), 1);
     }
+    for (int i = 0; i < kSched; ++i) {
+      mbar_init(smem_u32(&sh->sched_full[i]), 1);
+      mbar_init(smem_u32(&sh->sched_empty[i]), kConsumers);
+    }
+    mbar_init(smem_u32(&sh->stg_ready[0]), 256);
+    mbar_init(smem_u32(&sh->stg_taken[0]), 1);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -783,256 +1153,314 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem = sh->tmem_base;
   const uint32_t tS = tmem /* + buffer * 128 */, tdP = tmem + 256, tdQ = tmem + 384;
 
+  // Ring bookkeeping: an item with `total` key tiles takes ring A entries K(0) ... K(total-1) and
+  // ring B entries V(0) ... V(total-1); the last K entry is released by the epilogue, which
+  // stages dQ over it.
+
   if (warp >= 10) {
     reg_dealloc<kRegsService>();
+    if (warp == 10 && lane == 0) {
+      prefetch_tmap(&tmdQ);
+      store_lane<D>(sh, 0, &tmdQ, 1);                 // the store lane of dQ
+    }
   } else if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
     reg_dealloc<kRegsService>();
-    if (lane == 0 && total > 0) {
+    if (lane == 0) {
       prefetch_tmap(&tmQ);
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
       prefetch_tmap(&tmdO);
-      {
-        const uint32_t bar = smem_u32(&sh->res_full);
-        mbar_expect_tx(bar, 2 * C::kTileBytes);
-        load_tile<D>(sQ, &tmQ, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
-        load_tile<D>(sdO, &tmdO, bar, (int)si.q_row0 + m0, h, (int)si.q_boff);
-      }
-      // K runs one tile ahead of V: K(j+1) is requested before V(j)
-      auto load_k = [&](int j) {
-        const int stg = j % C::kStagesK;
-        if (!bwait_relaxed(&sh->empty_a[stg], ((j / C::kStagesK) & 1) ^ 1, sh, 51)) return false;
-        const uint32_t bar = smem_u32(&sh->full_a[stg]);
-        mbar_expect_tx(bar, C::kTileBytes);
-        load_tile<D>(sRingK + stg * C::kTileBytes, &tmK, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
-        return true;
-      };
-      auto load_v = [&](int j) {
-        const int stg = j % C::kStagesV;
-        if (!bwait_relaxed(&sh->empty_b[stg], ((j / C::kStagesV) & 1) ^ 1, sh, 51)) return false;
-        const uint32_t bar = smem_u32(&sh->full_b[stg]);
-        mbar_expect_tx(bar, C::kTileBytes);
-        load_tile<D>(sRingV + stg * C::kTileBytes, &tmV, bar, (int)si.k_row0 + (n_hi - 1 - j) * kT, hk, (int)si.k_boff);
-        return true;
-      };
-      bool pok = load_k(0);
-      for (int j = 0; j < total && pok; ++j) {
-        if (j + 1 < total) pok = load_k(j + 1);
-        if (pok) pok = load_v(j);
+      int posA = 0, posB = 0, wi = 0, fidx = 0;
+      bool ok = true;
+      auto decode = [&](int c, QItem& w) { return dq_item(p, cfg, c, nmb, w); };
+      // an item is drawn from the queue only when the loads of the previous one are all issued
+      for (;;) {
+        const QItem w = sched_publish<QItem>(sh, queue, ncand, fidx, ok, decode);
+        if (!ok || w.total < 0) break;
+        if (w.total == 0) continue;
+        const int hk = w.h / (p.heads_q / p.heads_kv);
+        // Q and dO: their slots are free once the last S and dP GEMMs of the previous item are done
+        if (wi > 0 && !(ok = bwait_relaxed(&sh->res_free, (wi - 1) & 1, sh, 51))) break;
+        {
+          const uint32_t bar = smem_u32(&sh->res_full);
+          mbar_expect_tx(bar, 2 * C::kTileBytes);
+          load_tile<D>(sQ, &tmQ, bar, w.g.q_row0 + w.m0, w.h, w.g.q_boff);
+          load_tile<D>(sdO, &tmdO, bar, w.g.q_row0 + w.m0, w.h, w.g.q_boff);
+        }
+        // K runs one tile ahead of V: K(j+1) is requested before V(j)
+        auto load_k = [&](int j) {
+          const int pos = posA + j;
+          if (!bwait_relaxed(&sh->empty_a[pos % SK], ((pos / SK) & 1) ^ 1, sh, 51)) return false;
+          const uint32_t bar = smem_u32(&sh->full_a[pos % SK]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(slotK(pos), &tmK, bar, w.g.k_row0 + (w.n_hi - 1 - j) * kT, hk, w.g.k_boff);
+          return true;
+        };
+        auto load_v = [&](int j) {
+          const int pos = posB + j;
+          if (!bwait_relaxed(&sh->empty_b[pos % SV], ((pos / SV) & 1) ^ 1, sh, 51)) return false;
+          const uint32_t bar = smem_u32(&sh->full_b[pos % SV]);
+          mbar_expect_tx(bar, C::kTileBytes);
+          load_tile<D>(slotV(pos), &tmV, bar, w.g.k_row0 + (w.n_hi - 1 - j) * kT, hk, w.g.k_boff);
+          return true;
+        };
+        ok = load_k(0);
+        for (int j = 0; j < w.total && ok; ++j) {
+          if (j + 1 < w.total) ok = load_k(j + 1);
+          if (ok) ok = load_v(j);
+        }
+        if (!ok) break;
+        posA += w.total;
+        posB += w.total;
+        ++wi;
       }
     }
   } else if (warp == 9) {
     // ------------------------------- MMA issuer -----------------------------------------
     reg_dealloc<kRegsService>();
-    if (total > 0) {
-      constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
-      constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
-      const uint32_t leader = elect_one() ? 1u : 0u;
-      bool ok = true;
-      auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
-        if (ok) ok = bwait(bar, parity, sh, code);
-        tc_fence_after();
-      };
-      auto slotK = [&](int j) { return sRingK + (j % C::kStagesK) * C::kTileBytes; };
-      auto slotV = [&](int j) { return sRingV + (j % C::kStagesV) * C::kTileBytes; };
-      wq(&sh->res_full, 0, 53);
-      wq(&sh->full_a[0], 0, 54);
+    constexpr uint32_t idesc_s = make_idesc(1, BFmt<T>::code, 0, 0, kT, kT);
+    constexpr uint32_t idesc_acc = make_idesc(1, BFmt<T>::code, 0, 1, kT, D);
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    bool ok = true;
+    auto wq = [&](uint64_t* bar, uint32_t parity, int code) {
+      if (ok) ok = bwait(bar, parity, sh, code);
+      tc_fence_after();
+    };
+    int posA = 0, posB = 0, wi = 0, tg = 0, sidx = 0; // tg: key tiles issued so far by this CTA
+    for (;;) {
+      const QItem w = sched_get<QItem>(sh, sidx++, true, ok);
+      if (!ok || w.total < 0) break;
+      if (w.total == 0) continue;
+      const int last = w.total - 1;
+      wq(&sh->res_full, wi & 1, 53);
+      wq(&sh->full_a[posA % SK], (posA / SK) & 1, 54);
       if (ok) {
-        mma_kmajor<D>(tS, sQ, slotK(0), idesc_s, leader);                      // S(0) = Q K(0)^T
-        mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
+        mma_kmajor<D>(tS + (tg & 1) * kT, sQ, slotK(posA), idesc_s, leader);      // S(0) = Q K(0)^T
+        mma_commit_lp(smem_u32(&sh->s_full[tg & 1]), leader);
+        if (last == 0) mma_commit_lp(smem_u32(&sh->res_free), leader);
       }
-      wq(&sh->full_b[0], 0, 54);
+      wq(&sh->full_b[posB % SV], (posB / SV) & 1, 54);
       if (ok) {
-        mma_kmajor<D>(tdP, sdO, slotV(0), idesc_s, leader);                    // dP(0) = dO V(0)^T
+        mma_kmajor<D>(tdP, sdO, slotV(posB), idesc_s, leader);                    // dP(0) = dO V(0)^T
         mma_commit_lp(smem_u32(&sh->dp_full), leader);
-        mma_commit_lp(smem_u32(&sh->empty_b[0]), leader);
+        mma_commit_lp(smem_u32(&sh->empty_b[posB % SV]), leader);
+        if (last == 0) mma_commit_lp(smem_u32(&sh->res_free), leader);
       }
-      for (int k = 0; k < total && ok; ++k) {
-        const int stK = k % C::kStagesK, stK1 = (k + 1) % C::kStagesK, stV1 = (k + 1) % C::kStagesV;
-        const uint32_t phK1 = ((k + 1) / C::kStagesK) & 1, phV1 = ((k + 1) / C::kStagesV) & 1;
-        const bool more = k + 1 < total;
-        FA_QTRACE(2, k, 0);
+      for (int k = 0; k < w.total && ok; ++k, ++tg) {
+        const int kpos = posA + k, k1pos = kpos + 1, v1pos = posB + k + 1;
+        const bool more = k < last;
         if (more) {
-          wq(&sh->full_a[stK1], phK1, 54);
+          wq(&sh->full_a[k1pos % SK], (k1pos / SK) & 1, 54);
           if (!ok) break;
-          mma_kmajor<D>(tS + ((k + 1) & 1) * kT, sQ, slotK(k + 1), idesc_s, leader);   // S(k+1)
-          mma_commit_lp(smem_u32(&sh->s_full[(k + 1) & 1]), leader);
+          mma_kmajor<D>(tS + ((tg + 1) & 1) * kT, sQ, slotK(k1pos), idesc_s, leader);   // S(k+1)
+          mma_commit_lp(smem_u32(&sh->s_full[(tg + 1) & 1]), leader);
+          if (k + 1 == last) mma_commit_lp(smem_u32(&sh->res_free), leader);      // Q's last reader
         }
-        FA_QTRACE(2, k, 1);
-        wq(&sh->ds_ready, k & 1, 55);
+        wq(&sh->ds_ready, tg & 1, 55);
         if (!ok) break;
-        FA_QTRACE(2, k, 2);
-        mma_from_tmem<D>(tdQ, tdP, slotK(k), idesc_acc, k > 0, leader);        // dQ += dS(k) K(k)
-        mma_commit_lp(smem_u32(&sh->empty_a[stK]), leader);
-        FA_QTRACE(2, k, 3);
+        mma_from_tmem<D>(tdQ, tdP, slotK(kpos), idesc_acc, k > 0, leader);        // dQ += dS(k) K(k)
+        if (more) mma_commit_lp(smem_u32(&sh->empty_a[kpos % SK]), leader);       // (the epilogue releases the last)
         if (more) {
-          wq(&sh->full_b[stV1], phV1, 54);
+          wq(&sh->full_b[v1pos % SV], (v1pos / SV) & 1, 54);
           if (!ok) break;
-          mma_kmajor<D>(tdP, sdO, slotV(k + 1), idesc_s, leader);              // dP(k+1)
+          mma_kmajor<D>(tdP, sdO, slotV(v1pos), idesc_s, leader);                 // dP(k+1)
           mma_commit_lp(smem_u32(&sh->dp_full), leader);
-          mma_commit_lp(smem_u32(&sh->empty_b[stV1]), leader);
+          mma_commit_lp(smem_u32(&sh->empty_b[v1pos % SV]), leader);
+          if (k + 1 == last) mma_commit_lp(smem_u32(&sh->res_free), leader);      // dO's last reader
         }
-        FA_QTRACE(2, k, 4);
       }
-      mma_commit_lp(smem_u32(&sh->acc_done), leader);
-      __syncwarp();
+      if (ok) mma_commit_lp(smem_u32(&sh->acc_done), leader);
+      posA += w.total;
+      posB += w.total;
+      ++wi;
     }
+    __syncwarp();
   } else {
     // ------------------------------- element-wise groups --------------------------------
     reg_alloc<kRegsEw>();
     const int x = warp >> 2;
     const int lrow = (warp & 3) * 32 + lane;  // TMEM lane = query row inside the tile
-    const int row = m0 + lrow;
-    const int qpos = row + off;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tdPx = tdP + lane_addr + x * kHalfT;
-    const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[b * p.heads_q + h] : 0.f;
-    float l2 = INFINITY, dl = 0.f;
-    if (row < si.q_len) {
-      const int64_t idx = si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
-                          (int64_t)h * p.lse_stride[2];
-      l2 = p.lse2[idx];
-      dl = p.delta[idx];
-      if (l2 == -INFINITY) l2 = INFINITY;
-    }
+    constexpr int DH = D / 2;                 // each group stores half of the head_dim columns
     bool ok = true;
-    for (int j = 0; j < total && ok; ++j) {
-      const int k0 = (n_hi - 1 - j) * kT + x * kHalfT;   // first key of this thread's columns
-      bool masked = (k0 + kHalfT > si.k_len);
-      if (cfg.causal) masked |= (k0 + kHalfT - 1 > m0 + off);
-      if (cfg.wl >= 0) masked |= (k0 < m0 + kT - 1 + off - cfg.wl);
-      if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > m0 + off + cfg.wr);
+    int posA = 0, wi = 0, tg = 0, sidx = 0;
+    // statistics of this thread's row: base-2 LSE (+inf for rows that do not exist or see no
+    // key: P = 0) and delta; those of the next item are fetched before the epilogue of this one
+    auto row_stats = [&](const QItem& w, float& l2, float& dl) {
+      l2 = INFINITY;
+      dl = 0.f;
+      const int row = w.m0 + lrow;
+      if (row < w.g.q_len) {
+        const int64_t idx = (int64_t)w.g.q_boff * p.lse_stride[0] + (int64_t)(w.g.q_row0 + row) * p.lse_stride[1] +
+                            (int64_t)w.h * p.lse_stride[2];
+        l2 = p.lse2[idx];
+        dl = p.delta[idx];
+        if (l2 == -INFINITY) l2 = INFINITY;
+      }
+    };
+    float l2n = INFINITY, dln = 0.f;
+    bool stats_ready = false;
 
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 0);
-      ok = bwait(&sh->s_full[j & 1], (j >> 1) & 1, sh, 56);
-      if (!ok) break;
-      tc_fence_after();
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 1);
-      uint32_t r0[32], r1[32];
-      const uint32_t tSx = tS + (j & 1) * kT + lane_addr + x * kHalfT;
-      tmem_ld32(tSx, r0);
-      tmem_ld32(tSx + 32, r1);
-      tmem_wait_ld();
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 2);
-      // ---- exp phase: P (times the soft cap's tanh factor) in fp32 registers -------------
-      const float dist0 = (float)(qpos - k0);        // query position - key position of column 0
-      float pf[kHalfT];
-      auto exp_body = [&](auto slow_tag) {
-        constexpr bool kSlow = decltype(slow_tag)::value;
+    QItem w, wn;                                     // wn: the entry after the current one, once looked at
+    bool peeked = false;
+    for (;;) {
+      if (peeked) {
+        sched_release(sh, sidx++);
+        w = wn;
+      } else {
+        w = sched_get<QItem>(sh, sidx++, true, ok);
+      }
+      if (!ok || w.total < 0) break;
+      peeked = false;
+      const int row = w.m0 + lrow;
+      const int qpos = row + off;
+      T* grow = nullptr;
+      if (row < w.g.q_len)
+        grow = reinterpret_cast<T*>(p.dq) + (int64_t)w.g.q_boff * p.dq_stride[0] +
+               (int64_t)(w.g.q_row0 + row) * p.dq_stride[1] + (int64_t)w.h * p.dq_stride[2] + x * DH;
+      if (w.total == 0) {
+        // no key is visible from these rows: their gradient is zero
+        if (grow != nullptr) {
 #pragma unroll
-        for (int i = 0; i < kHalfT; ++i) {
-          const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
-          if (kSlow) {
-            const int col = k0 + i;
-            float th = 0.f;
-            float sc;
-            if (kExtras) sc = score_log2_dist(cfg, slope, sv, dist0 - (float)i, th) - l2;
-            else sc = fmaf(sv, cfg.scale_log2, -l2);
-            float pe = ex2(sc);
-            if (masked && !visible(cfg, qpos, col, si.k_len)) pe = 0.f;
-            if (kExtras && cfg.softcap > 0.f) pe *= (1.f - th * th);
-            pf[i] = pe;
+          for (int c = 0; c < DH / 8; ++c) reinterpret_cast<uint4*>(grow)[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      float l2, dl;
+      if (stats_ready) { l2 = l2n; dl = dln; }
+      else row_stats(w, l2, dl);
+      const float slope = (kExtras && cfg.has_alibi) ? p.alibi_slopes[w.b * p.heads_q + w.h] : 0.f;
+      int vk_lo, vk_hi;                              // key positions this thread's query row sees
+      visible_k_interval(cfg, qpos, w.g.k_len, vk_lo, vk_hi);
+
+      for (int j = 0; j < w.total && ok; ++j, ++tg) {
+        const int k0 = (w.n_hi - 1 - j) * kT + x * kHalfT;   // first key of this thread's columns
+        bool masked = (k0 + kHalfT > w.g.k_len);
+        if (cfg.causal) masked |= (k0 + kHalfT - 1 > w.m0 + off);
+        if (cfg.wl >= 0) masked |= (k0 < w.m0 + kT - 1 + off - cfg.wl);
+        if (cfg.wr >= 0) masked |= (k0 + kHalfT - 1 > w.m0 + off + cfg.wr);
+
+        ok = bwait(&sh->s_full[tg & 1], (tg >> 1) & 1, sh, 56);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        const uint32_t tSx = tS + (tg & 1) * kT + lane_addr + x * kHalfT;
+        tmem_ld32(tSx, r0);
+        tmem_ld32(tSx + 32, r1);
+        tmem_wait_ld();
+        // ---- exp phase: P (times the soft cap's tanh factor) in fp32 registers -------------
+        const float dist0 = (float)(qpos - k0);        // query position - key position of column 0
+        float pf[kHalfT];
+        // columns (keys) of this tile that this thread's query row sees
+        const ColMask cm = make_col_mask(vk_lo - k0, vk_hi - k0);
+        // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
+        auto exp_body = [&](auto mask_tag, auto cap_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
+          constexpr bool kCap = decltype(cap_tag)::value;
+          if (kExtras) {
+#pragma unroll
+            for (int i = 0; i < kHalfT; ++i) {
+              const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
+              float th;
+              float pe = ex2(score_log2_feat<kCap>(cfg, slope, sv, dist0 - (float)i, th) - l2);
+              if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
+              if (kCap) pe *= (1.f - th * th);
+              pf[i] = pe;
+            }
           } else {
-            pf[i] = ex2(fmaf(sv, cfg.scale_log2, -l2));
-          }
-        }
-      };
-      auto exp_fast = [&]() {
-        const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2), nl = make_float2(-l2, -l2);
+            const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2), nl = make_float2(-l2, -l2);
 #pragma unroll
-        for (int i = 0; i < kHalfT; i += 2) {
-          const uint32_t* rr = i < 32 ? r0 : r1;
-          const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2, nl);
-          const float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
-          pf[i] = pe.x;
-          pf[i + 1] = pe.y;
+            for (int i = 0; i < kHalfT; i += 2) {
+              const uint32_t* rr = i < 32 ? r0 : r1;
+              const float2 a = f2fma(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2, nl);
+              float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
+              if (kMask) {
+                pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+              }
+              pf[i] = pe.x;
+              pf[i + 1] = pe.y;
+            }
+          }
+        };
+        const bool cap = kExtras && cfg.softcap > 0.f;
+        if (masked) {
+          if (cap) exp_body(std::true_type{}, std::true_type{});
+          else exp_body(std::true_type{}, std::false_type{});
+        } else {
+          if (cap) exp_body(std::false_type{}, std::true_type{});
+          else exp_body(std::false_type{}, std::false_type{});
         }
-      };
-      if (kExtras || masked) exp_body(std::true_type{});
-      else exp_fast();
 
-      // ---- dS phase --------------------------------------------------------------------
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 3);
-      ok = bwait(&sh->dp_full, j & 1, sh, 57);
+        // ---- dS phase --------------------------------------------------------------------
+        ok = bwait(&sh->dp_full, tg & 1, sh, 57);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tdPx, r0);
+        tmem_ld32(tdPx + 32, r1);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+          const uint32_t* rr = c == 0 ? r0 : r1;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 d = f2add(make_float2(__uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1])),
+                                   make_float2(-dl, -dl));
+            const float2 ds = f2mul(make_float2(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]), d);
+            pk[i] = Elem<T>::pack(ds.x, ds.y);
+          }
+          tmem_st16(tdPx + c * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sh->ds_ready));
+      }
+      if (!ok) break;
+
+      // ---- end of the item: fetch the next item's row statistics, then store dQ * softmax_scale --
+      {
+        wn = sched_get<QItem>(sh, sidx, false, ok);
+        if (!ok) break;
+        peeked = true;
+        stats_ready = wn.total > 0;
+        if (stats_ready) row_stats(wn, l2n, dln);
+      }
+      // The tile is staged over the item's last K tile (every MMA is done) and handed to the store
+      // lane, which lets the TMA unit write it; a packed tile that crosses the end of its sequence
+      // is stored row by row instead.
+      const int spos = posA + w.total - 1;
+      ok = bwait(&sh->acc_done, wi & 1, sh, 58);
       if (!ok) break;
       tc_fence_after();
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 4);
-      tmem_ld32(tdPx, r0);
-      tmem_ld32(tdPx + 32, r1);
-      tmem_wait_ld();
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 5);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
-        const uint32_t* rr = c == 0 ? r0 : r1;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 d = f2add(make_float2(__uint_as_float(rr[2 * i]), __uint_as_float(rr[2 * i + 1])),
-                                 make_float2(-dl, -dl));
-          const float2 ds = f2mul(make_float2(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]), d);
-          pk[i] = Elem<T>::pack(ds.x, ds.y);
-        }
-        tmem_st16(tdPx + c * 16, pk);
-      }
-      tmem_wait_st();
+      const bool via_tma = (p.cu_seqlens_q == nullptr) || (w.m0 + kT <= w.g.q_len);
+      const uint32_t stg = slotK(spos);
+      if (tid == 0)
+        ok = post_store(sh, 0, wi, via_tma ? (int)stg : 0, w.h, w.g.q_row0 + w.m0, w.g.q_boff,
+                        smem_u32(&sh->empty_a[spos % SK]));
+      drain_acc<T, DH>(tdQ + lane_addr + x * DH, cfg.scale, via_tma, stg, lrow, x * DH, grow);
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->ds_ready));
-      if ((warp & 3) == 0) FA_QTRACE(x, j, 6);
+      if (via_tma) fence_proxy_async();
+      mbar_arrive(smem_u32(&sh->stg_ready[0]));
+      posA += w.total;
+      ++wi;
     }
-
-    // ---- epilogue: dQ * softmax_scale; each group handles half of the head_dim columns -----
-    // The tile is staged over the resident Q tile (every MMA is done) and stored by the TMA
-    // unit; a packed tile that crosses the end of its sequence is stored row by row instead.
-    if (ok && total > 0) ok = bwait(&sh->acc_done, 0, sh, 58);
+    // no more items: the store lane may leave
     if (ok) {
-      tc_fence_after();
-      constexpr int DH = D / 2;
-      const bool via_tma = (p.cu_seqlens_q == nullptr) || (m0 + kT <= si.q_len);
-      T* base = reinterpret_cast<T*>(p.dq) + si.q_boff * p.dq_stride[0] +
-                (si.q_row0 + row) * p.dq_stride[1] + (int64_t)h * p.dq_stride[2] + x * DH;
-#pragma unroll
-      for (int cc = 0; cc < DH / 32; ++cc) {
-        uint32_t r[32];
-        if (total > 0) {
-          tmem_ld32(tdQ + lane_addr + x * DH + cc * 32, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 v;
-          v.x = Elem<T>::pack(__uint_as_float(r[i]) * cfg.scale, __uint_as_float(r[i + 1]) * cfg.scale);
-          v.y = Elem<T>::pack(__uint_as_float(r[i + 2]) * cfg.scale, __uint_as_float(r[i + 3]) * cfg.scale);
-          v.z = Elem<T>::pack(__uint_as_float(r[i + 4]) * cfg.scale, __uint_as_float(r[i + 5]) * cfg.scale);
-          v.w = Elem<T>::pack(__uint_as_float(r[i + 6]) * cfg.scale, __uint_as_float(r[i + 7]) * cfg.scale);
-          if (via_tma) {
-            const int col = x * DH + cc * 32 + i;
-            st_shared_v4(sw128_addr(sQ + (col / 64) * (kT * 128), lrow, (col % 64) / 8), v);
-          } else if (row < si.q_len) {
-            *reinterpret_cast<uint4*>(base + cc * 32 + i) = v;
-          }
-        }
-      }
-      if (via_tma) {
-        fence_proxy_async();
-        asm volatile("bar.sync 1, 256;\n" ::: "memory");
-        if (tid == 0) {
-#pragma unroll
-          for (int bx = 0; bx < D / 64; ++bx)
-            tma_store_4d(&tmdQ, sQ + bx * (kT * 128), bx * 64, h, (int)si.q_row0 + m0, (int)si.q_boff);
-          tma_store_commit();
-          tma_store_wait_read();
-        }
-      }
+      if (tid == 0) ok = post_store(sh, 0, wi, -1, 0, 0, 0, 0);
+      mbar_arrive(smem_u32(&sh->stg_ready[0]));
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, 512);
+  if (tid == 0) {
+    if (sh->abort_flag == 0) sched_finish(queue);
+    report_abort(sh->abort_flag, host_status);
+  }
 }
 
 // =======================================================================================
@@ -1081,6 +1509,14 @@ template <typename K> int set_smem_attr(K kern, int bytes, const char* what) {
   return FA_OK;
 }
 
+// candidates of a launch: blocks x heads x batch must stay a 32-bit count
+bool candidate_count(int64_t blocks, int64_t heads, int64_t batch, int* out) {
+  const int64_t n = blocks * heads * batch;
+  if (n <= 0 || n > 0x7fffffff) return false;
+  *out = (int)n;
+  return true;
+}
+
 template <typename T, int D>
 int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   Maps m{};
@@ -1094,8 +1530,17 @@ int launch_dkdv(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   const bool extras = cfg.has_alibi || cfg.softcap > 0.f || !(cfg.scale_log2 > 2e-5f);
   auto kern = extras ? bwd_dkdv_sm100_kernel<T, D, true> : bwd_dkdv_sm100_kernel<T, D, false>;
   if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytes, "bwd_dkdv_sm100")) return r;
-  dim3 grid((a.seqlen_k + kT - 1) / kT, a.heads_kv, a.batch);
-  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, m.dk, m.dv, a, cfg);
+  const int nkb = (a.seqlen_k + kT - 1) / kT;
+  int ncand = 0;
+  if (!candidate_count(nkb, a.heads_kv, a.batch, &ncand)) {
+    set_error("bwd_dkdv_sm100: too many work items");
+    return FA_ERR_UNSUPPORTED;
+  }
+  unsigned int* queue = work_queue(a.device);
+  if (queue == nullptr) return FA_ERR_LAUNCH;
+  const int grid = ncand < sm_count(a.device) ? ncand : sm_count(a.device);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytes, st>>>(m.q, m.k, m.v, m.dout, m.dk, m.dv, a, cfg, nkb, ncand, queue,
+                                                           host_wait_word(a.device));
   return check_launch("bwd_dkdv_sm100");
 }
 
@@ -1109,14 +1554,46 @@ int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
   auto kern = extras ? bwd_dq_sm100_kernel<T, D, true> : bwd_dq_sm100_kernel<T, D, false>;
   if (int r = set_smem_attr(kern, BCfg<D>::kSmemBytesDq, "bwd_dq_sm100")) return r;
-  dim3 grid((a.seqlen_q + kT - 1) / kT, a.heads_q, a.batch);
-  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytesDq, st>>>(m.q, m.k, m.v, m.dout, m.dq, a, cfg);
+  const int nmb = (a.seqlen_q + kT - 1) / kT;
+  int ncand = 0;
+  if (!candidate_count(nmb, a.heads_q, a.batch, &ncand)) {
+    set_error("bwd_dq_sm100: too many work items");
+    return FA_ERR_UNSUPPORTED;
+  }
+  unsigned int* queue = work_queue(a.device);
+  if (queue == nullptr) return FA_ERR_LAUNCH;
+  const int grid = ncand < sm_count(a.device) ? ncand : sm_count(a.device);
+  kern<<<grid, kBwdThreads, BCfg<D>::kSmemBytesDq, st>>>(m.q, m.k, m.v, m.dout, m.dq, a, cfg, nmb, ncand, queue,
+                                                             host_wait_word(a.device));
   return check_launch("bwd_dq_sm100");
 }
 
 }  // namespace
 
+int bwd_dkdv_cta_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st);
+
+// Average number of query tiles a block of 128 keys meets (times the GQA group): what one work
+// item of the dK/dV kernels amounts to.  Dense layout only (the lengths of a packed batch live
+// on the device).
+static double dkdv_tiles_per_item(const fa_attn_args& a, const ScoreCfg& cfg) {
+  const int nkb = (a.seqlen_k + kT - 1) / kT, off = a.q_pos_offset;
+  long long sum = 0;
+  for (int n = 0; n < nkb; ++n) {
+    int qlo, qhi;
+    const int k_last = (n * kT + kT < a.seqlen_k ? n * kT + kT : a.seqlen_k) - 1;
+    visible_query_range(cfg, n * kT, k_last, off, a.seqlen_q + off, qlo, qhi);
+    const int m_lo = (qlo - off > 0 ? qlo - off : 0) / kT, m_hi = ((qhi - off > 0 ? qhi - off : 0) + kT - 1) / kT;
+    if (m_hi > m_lo) sum += m_hi - m_lo;
+  }
+  return (double)sum / nkb * (a.heads_q / a.heads_kv);
+}
+
 int bwd_dkdv_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  // Two kernels (see bwd_dkdv_cta_sm100.cu): short work items of a plain dense problem go to the
+  // one-CTA-per-key-block kernel, everything else to the persistent one.
+  const bool features = cfg.has_alibi || cfg.softcap > 0.f || !(cfg.scale_log2 > 2e-5f);
+  if (!features && a.cu_seqlens_q == nullptr && dkdv_tiles_per_item(a, cfg) < 24.0)
+    return bwd_dkdv_cta_sm100(a, cfg, st);
   if (a.head_dim == 128)
     return a.dtype == FA_BF16 ? launch_dkdv<__nv_bfloat16, 128>(a, cfg, st) : launch_dkdv<__half, 128>(a, cfg, st);
   return a.dtype == FA_BF16 ? launch_dkdv<__nv_bfloat16, 64>(a, cfg, st) : launch_dkdv<__half, 64>(a, cfg, st);
@@ -1128,10 +1605,19 @@ int bwd_dq_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
   return a.dtype == FA_BF16 ? launch_dq<__nv_bfloat16, 64>(a, cfg, st) : launch_dq<__half, 64>(a, cfg, st);
 }
 
+int bwd_dkdv_cta_status();
+void bwd_dkdv_cta_clear_status();
+
+void bwd_sm100_clear_status() {
+  const int z = 0;
+  cudaMemcpyToSymbol(g_bwd_sm100_status, &z, sizeof(int));
+  bwd_dkdv_cta_clear_status();
+}
+
 int bwd_sm100_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_bwd_sm100_status, sizeof(int));
-  return v;
+  return v != 0 ? v : bwd_dkdv_cta_status();
 }
 
 }  // namespace fa

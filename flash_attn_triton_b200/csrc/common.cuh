@@ -18,6 +18,19 @@ namespace fa {
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 int ensure_device(int device);
+int sm_count(int device);
+// Counter pair for one launch of a persistent kernel (work queue: [0] next candidate, [1] CTAs
+// finished; both zero between launches).  Pairs come from a fixed array inside the library and
+// are handed out in rotation, so launches that overlap on the GPU use different pairs as long as
+// fewer than kWorkQueues of them are in flight on one device.  Null (with the error set) on failure.
+// Time-outs of bounded device-side waits.  host_wait_word(): the word (in mapped host memory, as
+// a device-visible pointer; null when the mapping is unavailable) that a kernel of `device` sets
+// when one of its waits runs out.  host_wait_status(): its current value, read without touching
+// the GPU; the tcgen05 launchers refuse to launch while it is non-zero.
+int* host_wait_word(int device);
+int host_wait_status(int device);
+constexpr int kWorkQueues = 64;
+unsigned int* work_queue(int device);  // streaming multiprocessors of `device` (the persistent kernels launch one CTA each)
 
 #define FA_REQUIRE(cond, ...)      \
   do {                             \
@@ -145,6 +158,18 @@ __device__ __forceinline__ float score_log2_dist(const ScoreCfg& c, float slope,
   }
   return s * FA_LOG2E;
 }
+// The same for the kernels that are compiled per feature set: ALiBi always applied (a zero slope
+// leaves the score unchanged, exactly), the soft cap selected at compile time.
+template <bool kCap>
+__device__ __forceinline__ float score_log2_feat(const ScoreCfg& c, float slope, float dot, float dist, float& th) {
+  float s = fmaf(-slope, fabsf(dist), dot * c.scale);
+  th = 0.f;
+  if (kCap) {
+    th = fast_tanh(s * c.inv_softcap);
+    s = c.softcap * th;
+  }
+  return s * FA_LOG2E;
+}
 __device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
                                             int kpos, float& th) {
   return score_log2_dist(c, slope, dot, (float)(qpos - kpos), th);
@@ -157,6 +182,45 @@ __device__ __forceinline__ bool visible(const ScoreCfg& c, int qpos, int kpos, i
   if (c.wr >= 0) ok = ok && (kpos <= qpos + c.wr);
   return ok;
 }
+
+// The mask as intervals.  For one key the query positions that see it, and for one query the
+// key positions it sees, are contiguous: a per-element test inside an unrolled loop is then two
+// integer instructions and a select instead of a chain of short-circuit branches (which the
+// compiler turns into divergent control flow: measured at more than 200 cycles per element).
+__device__ __forceinline__ void visible_q_interval(const ScoreCfg& c, int kpos, int& lo, int& hi) {
+  lo = -(1 << 30);
+  hi = 1 << 30;
+  if (c.causal) lo = kpos;                       // kpos <= qpos
+  if (c.wr >= 0) lo = max(lo, kpos - c.wr);      // kpos <= qpos + wr
+  if (c.wl >= 0) hi = kpos + c.wl;               // kpos >= qpos - wl
+}
+__device__ __forceinline__ void visible_k_interval(const ScoreCfg& c, int qpos, int k_len, int& lo, int& hi) {
+  lo = 0;
+  hi = k_len - 1;
+  if (c.causal) hi = min(hi, qpos);
+  if (c.wr >= 0) hi = min(hi, qpos + c.wr);
+  if (c.wl >= 0) lo = max(lo, qpos - c.wl);
+}
+// Columns [first, last] of a tile (relative to its first column; any integers, possibly empty):
+// column j is inside iff (unsigned)(j - lo) <= span.
+struct ColMask {
+  int lo;
+  unsigned int span;
+};
+__device__ __forceinline__ ColMask make_col_mask(int first, int last) {
+  first = max(first, -(1 << 20));
+  last = min(last, 1 << 20);
+  ColMask m;
+  if (last < first) {
+    m.lo = 1 << 28;
+    m.span = 0u;
+  } else {
+    m.lo = first;
+    m.span = (unsigned int)(last - first);
+  }
+  return m;
+}
+__device__ __forceinline__ bool col_visible(const ColMask& m, int j) { return (unsigned int)(j - m.lo) <= m.span; }
 
 // Key range [lo, hi) any query position in [qpos_min, qpos_max] can see.
 __device__ __forceinline__ void visible_key_range(const ScoreCfg& c, int qpos_min, int qpos_max,
@@ -172,7 +236,7 @@ __device__ __forceinline__ void visible_key_range(const ScoreCfg& c, int qpos_mi
 }
 
 // Query-position range [lo, hi) that can see any key in [k_min, k_max].
-__device__ __forceinline__ void visible_query_range(const ScoreCfg& c, int k_min, int k_max,
+__host__ __device__ __forceinline__ void visible_query_range(const ScoreCfg& c, int k_min, int k_max,
                                                     int qpos_begin, int qpos_end, int& lo,
                                                     int& hi) {
   int right = c.wr;

@@ -34,10 +34,12 @@ template <> __device__ __forceinline__ __nv_bfloat16 hsub_rn(__nv_bfloat16 a, __
 
 // Rotary on element d of a head vector x (read through `get`), every product and sum
 // rounded to T like the reference's eager arithmetic (flash_attn_interface.py:57-66).
+// A position outside the table [0, rotary_seqlen) leaves the element unrotated (the host checks
+// the lengths when validation is on; this keeps the read in bounds when it is off).
 template <typename T, typename F>
 __device__ __forceinline__ T rotary_elem(F get, int d, const T* cos, const T* sin, int pos,
-                                         int rotary_dim, int interleaved) {
-  if (d >= rotary_dim) return get(d);
+                                         int rotary_dim, int interleaved, int rotary_seqlen) {
+  if (d >= rotary_dim || pos < 0 || pos >= rotary_seqlen) return get(d);
   const int half = rotary_dim >> 1;
   int i, partner;
   bool first;
@@ -94,7 +96,8 @@ __global__ void kv_append_kernel(const fa_decode_args p, int page_shift) {
   const T* sin = reinterpret_cast<const T*>(p.rotary_sin);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     T kv = kn[d];
-    if (cos) kv = rotary_elem<T>([&](int j) { return kn[j]; }, d, cos, sin, pos, p.rotary_dim, p.rotary_interleaved);
+    if (cos) kv = rotary_elem<T>([&](int j) { return kn[j]; }, d, cos, sin, pos, p.rotary_dim, p.rotary_interleaved,
+                                   p.rotary_seqlen);
     kc[d] = kv;
     vc[d] = vn[d];
   }
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
         if (cos) {
           const int pos = len - p.seqlen_q + sq + pad;
           val = rotary_elem<T>([&](int j) { return qrow[j]; }, d, cos, sin, pos, p.rotary_dim,
-                               p.rotary_interleaved);
+                               p.rotary_interleaved, p.rotary_seqlen);
         } else {
           val = qrow[d];
         }

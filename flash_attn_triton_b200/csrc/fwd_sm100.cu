@@ -37,6 +37,8 @@
 #include <type_traits>
 
 #include "common.cuh"
+#define PROF_TAG fwd
+#include "prof.cuh"
 #include "sm100.cuh"
 
 namespace fa {
@@ -44,32 +46,6 @@ namespace fa {
 using namespace sm100;
 
 __device__ int g_fwd_sm100_status = 0;
-
-#ifdef FA_TRACE
-// Timeline of one CTA (blockIdx 0,0,0) for kernel tuning: clock64 stamps per role and step.
-__device__ long long g_fwd_trace[3][32][8];
-#define FA_TRACE_EV(role, step, ev)                                                          \
-  do {                                                                                       \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (step) < 32 &&              \
-        (threadIdx.x & 31) == 0)                                                             \
-      g_fwd_trace[role][step][ev] = clock64();                                               \
-  } while (0)
-// per-launch sums over all CTAs: clock64 cycles of [0] setup, [1] until the first score tile,
-// [2] main loop, [3] epilogue, [4] exit barrier, [5] key tiles, [6] CTAs
-__device__ unsigned long long g_fwd_phase[8];
-extern "C" int fa_debug_fwd_phases(unsigned long long* out, int reset) {
-  int r = (int)cudaMemcpyFromSymbol(out, g_fwd_phase, sizeof(unsigned long long) * 8);
-  if (reset) {
-    unsigned long long z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_fwd_phase, z, sizeof(z));
-  }
-  return r;
-}
-#define FA_PHASE_STAMP(var) const long long var = clock64()
-#else
-#define FA_TRACE_EV(role, step, ev) do {} while (0)
-#define FA_PHASE_STAMP(var) do {} while (0)
-#endif
 
 namespace {
 
@@ -133,10 +109,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                  const fa_attn_args p, const ScoreCfg cfg, const float* __restrict__ sq,
-                 const float* __restrict__ sk) {
+                 const float* __restrict__ sk, int* const host_status) {
   static_assert(!kInt8 || D == 128, "the INT8 variant stages 128-byte code rows");
   using C = Cfg<D>;
-  FA_PHASE_STAMP(ph_t0);
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -204,14 +179,13 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  FA_PHASE_STAMP(ph_t1);
 
   if (warp >= 10) {
     // idle warps of the producer/MMA warpgroup; in the INT8 variant warp 10 stages the key
     // scales of the key tile of step j into shared memory (slot j & 1)
     reg_dealloc<72>();
     if (kInt8 && warp == 10) {
-      const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
+      const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.total_k;   // rows of the scale arrays per (batch, head)
       for (int j = 0; j < nsteps; ++j) {
         const int buf = j % kSkSlots;
         bool w = true;
@@ -326,7 +300,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         advance();
       }
       for (int j = 0; j < nsteps && ok; ++j) {
-        FA_TRACE_EV(2, j, 0);
         wwait(&sh->kv_full[stage], phase, 24);          // V_j
         if (!ok) break;
         const int vstage = stage;
@@ -336,7 +309,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int kstage = stage;
         const uint32_t kbase = sKV + stage * C::kTileBytes;
         bool k_waited = false;
-        FA_TRACE_EV(2, j, 1);
         auto do_stream = [&](int x, int sjb, int sje, int& pcnt) {
           if (j >= sjb && j < sje) {
             wwait(&sh->p_ready[x], pcnt & 1, 25 + x);
@@ -360,9 +332,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         };
         do_stream(0, jb0, je0, pcnt0);
-        FA_TRACE_EV(2, j, 2);
         if (ok) do_stream(1, jb1, je1, pcnt1);
-        FA_TRACE_EV(2, j, 4);
         if (!ok) break;
         mma_commit_lp(smem_u32(&sh->kv_empty[vstage]), leader);
         if (more) {
@@ -377,6 +347,11 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else {
     // ------------------------------- softmax groups -------------------------------------
     reg_alloc<216>();
+    PROF_VARS(12);
+#ifdef FA_PROF
+    const long long prof_start = clock64();
+    long long prof_t1 = 0;
+#endif
     const int x = warp >> 2;                         // stream = query tile of the CTA
     const int m0 = m00 + x * kBM;
     const int row_in_tile = (warp & 3) * 32 + lane;  // TMEM lane
@@ -390,12 +365,9 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
     const int tq_min = m0 + off, tq_max = tq_min + kBM - 1;
     // INT8: scale of this query row and the row of key scales of this (batch, head)
-    const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.seqlen_k;
+    const int64_t bh_rows = ((int64_t)b * p.heads_q + h) * p.total_k;
     const float sq_row = (kInt8 && row < si.q_len) ? sq[bh_rows + row] : 1.f;
     const int my_jb = x ? jb1 : jb0, my_je = x ? je1 : je0;
-#ifdef FA_TRACE
-    long long ph_t2 = 0;
-#endif
 
     for (int j = kInt8 ? 0 : my_jb; j < (kInt8 ? nsteps : my_je) && ok; ++j) {
       if (kInt8 && (j < my_jb || j >= my_je)) {
@@ -411,23 +383,30 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (cfg.wl >= 0) masked |= (k0 < tq_max - cfg.wl);
       if (cfg.wr >= 0) masked |= (k0 + kBN - 1 > tq_min + cfg.wr);
 
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 0);
+      PROF_T0();
       ok = wait_bar(&sh->s_full[x], t & 1, sh, 31 + x);
+#ifdef FA_PROF
+      if (t == 0) PROF_ADD(1); else PROF_ADD(0);
+      prof_t1 = clock64();
+      PROF_COUNT(masked ? 9 : 8, 1);
+#endif
       if (!ok) break;
       tc_fence_after();
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 1);
-#ifdef FA_TRACE
-      if (t == 0) ph_t2 = clock64();
-#endif
 
       // ---- the 128 scores of this row into registers -------------------------------------
       uint32_t r[4][32];
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) tmem_ld32(tSx + cc * 32, r[cc]);
       tmem_wait_ld();
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 2);
 
       const bool prescaled = kExtras || masked || kInt8;
+      // columns (keys) of this tile that this thread's query row sees (used by masked tiles only)
+      ColMask cm;
+      if (masked) {
+        int vk_lo, vk_hi;
+        visible_k_interval(cfg, qpos, si.k_len, vk_lo, vk_hi);
+        cm = make_col_mask(vk_lo - k0, vk_hi - k0);
+      }
       if (kInt8) {
         // score = float(acc) * s_q * (s_k * softmax_scale * log2 e): the same product as the
         // reference's (acc * (s_q * s_k)) * (scale * log2 e) up to the last rounding.
@@ -435,7 +414,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // (an integer add and a float subtract instead of a quarter-rate I2F); packed pairs.
         ok = wait_bar(&sh->sk_full[j % kSkSlots], (j / kSkSlots) & 1, sh, 37 + x);
         if (!ok) break;
-        if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 6);
         const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[j % kSkSlots][0]);
         const float2 sq2 = make_float2(sq_row, sq_row), nb2 = make_float2(-12582912.0f, -12582912.0f);
         // Two copies of the loop: without the per-element mask test there are no branches inside,
@@ -458,8 +436,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               float v[4] = {v01.x, v01.y, v23.x, v23.y};
               if (kMask) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (!visible(cfg, qpos, k0 + cc * 32 + i + e, si.k_len)) v[e] = -INFINITY;
+                for (int e = 0; e < 4; ++e) v[e] = col_visible(cm, cc * 32 + i + e) ? v[e] : -INFINITY;
               }
 #pragma unroll
               for (int e = 0; e < 4; ++e) r[cc][i + e] = __float_as_uint(v[e]);
@@ -469,25 +446,36 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (masked) scale_tile(std::true_type{});
         else scale_tile(std::false_type{});
         mbar_arrive(smem_u32(&sh->sk_empty[j % kSkSlots]));
-        if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 7);
       } else if (prescaled) {
-        // score pipeline and mask applied once, in place; values end up in the log2 domain
+        // score pipeline and mask applied once, in place; values end up in the log2 domain.
+        // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
         const float dist0 = (float)(qpos - k0);
+        auto score_tile = [&](auto mask_tag, auto cap_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
+          constexpr bool kCap = decltype(cap_tag)::value;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float v = __uint_as_float(r[cc][i]);
-            const int col = k0 + cc * 32 + i;
-            if (kExtras) {
-              float th;
-              v = score_log2_dist(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
-            } else {
-              v *= cfg.scale_log2;
+            for (int i = 0; i < 32; ++i) {
+              float v = __uint_as_float(r[cc][i]);
+              if (kExtras) {
+                float th;
+                v = score_log2_feat<kCap>(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
+              } else {
+                v *= cfg.scale_log2;
+              }
+              if (kMask) v = col_visible(cm, cc * 32 + i) ? v : -INFINITY;
+              r[cc][i] = __float_as_uint(v);
             }
-            if (masked && !visible(cfg, qpos, col, si.k_len)) v = -INFINITY;
-            r[cc][i] = __float_as_uint(v);
           }
+        };
+        const bool cap = kExtras && cfg.softcap > 0.f;
+        if (masked) {
+          if (cap) score_tile(std::true_type{}, std::true_type{});
+          else score_tile(std::true_type{}, std::false_type{});
+        } else {
+          if (cap) score_tile(std::false_type{}, std::true_type{});
+          else score_tile(std::false_type{}, std::false_type{});
         }
       }
 
@@ -512,6 +500,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
 
+#ifdef FA_PROF
+      prof_acc[masked ? 3 : 2] += (unsigned int)(clock64() - prof_t1);   // load + score + max phase
+      prof_t1 = clock64();
+#endif
       // ---- lazy rescale ----------------------------------------------------------------
       if (t == 0) {
         m_used = mx;
@@ -541,9 +533,12 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_wait_st();
         }
       }
+#ifdef FA_PROF
+      prof_acc[4] += (unsigned int)(clock64() - prof_t1);                 // rescale (incl. its wait)
+      prof_t1 = clock64();
+#endif
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       const float mul = prescaled ? 1.f : cfg.scale_log2;
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 3);
 
       // ---- P = exp2(s - m), row sum, P -> TMEM in place over S ----------------------------
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
@@ -585,22 +580,20 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ps[0] = acc2[0].x; ps[1] = acc2[0].y; ps[2] = acc2[1].x; ps[3] = acc2[1].y;
       }
       l += (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 4);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->p_ready[x]));
-      if (lane == 0 && (warp & 3) == 0) FA_TRACE_EV(x, t, 5);
+#ifdef FA_PROF
+      prof_acc[5] += (unsigned int)(clock64() - prof_t1);                 // exp + store phase
+#endif
     }
 
     // ---- epilogue: O / l -> global, base-2 LSE ------------------------------------------
-    FA_PHASE_STAMP(ph_t3);
-#ifdef FA_TRACE
-    if (tid == 0 && nsteps > 0) {
-      atomicAdd(&g_fwd_phase[1], (unsigned long long)(ph_t2 - ph_t1));
-      atomicAdd(&g_fwd_phase[2], (unsigned long long)(ph_t3 - ph_t2));
-    }
-#endif
     const int my_tiles = my_je - my_jb;
+#ifdef FA_PROF
+    prof_acc[6] = (unsigned int)(clock64() - prof_start);                 // start of role -> end of main loop
+    prof_t1 = clock64();
+#endif
     if (ok && my_tiles > 0) ok = wait_bar(&sh->o_ready[x], (my_tiles - 1) & 1, sh, 35 + x);
     // A stream without key tiles writes zeros over its Q tile straight away: the TMA load of
     // both Q tiles (issued whenever the CTA has steps) must have landed first, or it would
@@ -659,27 +652,17 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         p.lse2[si.q_boff * p.lse_stride[0] + (si.q_row0 + row) * p.lse_stride[1] +
                (int64_t)h * p.lse_stride[2]] = l > 0.f ? m_used + log2f(l) : -INFINITY;
     }
-#ifdef FA_TRACE
-    if (tid == 0) atomicAdd(&g_fwd_phase[3], (unsigned long long)(clock64() - ph_t3));
+#ifdef FA_PROF
+    prof_acc[7] = (unsigned int)(clock64() - prof_t1);                    // epilogue
+    prof_acc[10] = 1;
+    PROF_FLUSH((tid & 127) == 0, (warp >> 2) * 16, 12);
 #endif
   }
 
-#ifdef FA_TRACE
-  long long ph_t4 = clock64();
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 8) tmem_dealloc(tmem, 512);
-#ifdef FA_TRACE
-  if (tid == 0) {
-    const long long t5 = clock64();
-    atomicAdd(&g_fwd_phase[0], (unsigned long long)(ph_t1 - ph_t0));
-    atomicAdd(&g_fwd_phase[4], (unsigned long long)(t5 - ph_t4));
-    atomicAdd(&g_fwd_phase[5], (unsigned long long)((je0 - jb0) + (je1 - jb1)));
-    atomicAdd(&g_fwd_phase[6], 1ull);
-    atomicAdd(&g_fwd_phase[7], (unsigned long long)(t5 - ph_t0));
-  }
-#endif
+  if (tid == 0) report_abort(sh->abort_flag, host_status);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -724,7 +707,7 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
     return FA_ERR_LAUNCH;
   }
   dim3 grid((a.seqlen_q + 2 * kBM - 1) / (2 * kBM), a.heads_q, a.batch);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, a, cfg, nullptr, nullptr);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, a, cfg, nullptr, nullptr, host_wait_word(a.device));
   return check_launch("fwd_sm100");
 }
 
@@ -777,7 +760,10 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
   memset(&p, 0, sizeof(p));
   p.dtype = FA_F16;
   p.device = a.device;
-  p.batch = B; p.seqlen_q = S; p.seqlen_k = S; p.heads_q = H; p.heads_kv = H; p.head_dim = D;
+  p.batch = B; p.seqlen_q = S; p.heads_q = H; p.heads_kv = H; p.head_dim = D;
+  p.seqlen_k = a.seqlen_k_valid > 0 ? a.seqlen_k_valid : S;   // keys past it are padding (masked, tiles skipped)
+  p.total_q = p.total_k = S;                                  // rows of q8 / k8 and of the scale arrays
+  p.q_pos_offset = a.q_pos_offset;
   p.o = a.o;
   p.o_stride[0] = (int64_t)H * S * D; p.o_stride[1] = D; p.o_stride[2] = (int64_t)S * D;
   p.lse2 = a.lse2;
@@ -793,20 +779,41 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
     return FA_ERR_LAUNCH;
   }
   dim3 grid((S + 2 * kBM - 1) / (2 * kBM), H, B);
-  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, cfg, a.sq_scratch, a.s_k);
+  kern<<<grid, kThreads, C::kSmemBytes, st>>>(tq, tk, tv, to, p, cfg, a.sq_scratch, a.s_k, host_wait_word(a.device));
   return check_launch("fwd_int8_sm100");
 }
 
-#ifdef FA_TRACE
-extern "C" int fa_debug_fwd_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(long long) * 3 * 32 * 8);
-}
-#endif
 
 int fwd_sm100_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_fwd_sm100_status, sizeof(int));
   return v;
+}
+
+void fwd_sm100_clear_status() {
+  const int z = 0;
+  cudaMemcpyToSymbol(g_fwd_sm100_status, &z, sizeof(int));
+}
+
+// One warp waits, for at most `clocks` cycles, on a barrier nothing arrives at: the time-out path
+// of bounded_wait with nothing else in flight.
+__global__ void wait_probe_kernel(long long clocks, int* host_status) {
+  __shared__ uint64_t bar;
+  __shared__ volatile int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncwarp();
+  bounded_wait<0>(&bar, 0, &abort_flag, &g_fwd_sm100_status, 99, clocks);
+  __syncwarp();
+  if (threadIdx.x == 0) report_abort(abort_flag, host_status);
+}
+
+int wait_probe(int device, long long clocks, cudaStream_t st) {
+  wait_probe_kernel<<<1, 32, 0, st>>>(clocks, host_wait_word(device));
+  return check_launch("wait_probe");
 }
 
 }  // namespace fa

@@ -116,7 +116,10 @@ __global__ void __launch_bounds__(128) fwd_int8_mma_kernel(const fa_int8_args p)
   const T* vg = reinterpret_cast<const T*>(p.v) + (int64_t)bh * S * D;
   const int8_t* k8g = p.k8 + (int64_t)bh * S * D;
   const float* skg = p.s_k + (int64_t)bh * S;
-  const int n_hi = p.causal ? min((S + BN - 1) / BN, (min(m0 + BM, S) - 1) / BN + 1) : (S + BN - 1) / BN;
+  const int klen = p.seqlen_k_valid > 0 ? p.seqlen_k_valid : S;   // keys past it are padding
+  const int off = p.q_pos_offset;                                 // query row i sits at position i + off
+  const int n_all = (klen + BN - 1) / BN;
+  const int n_hi = p.causal ? max(0, min(n_all, (min(m0 + BM, S) - 1 + off) / BN + 1)) : n_all;
 
   auto load_kv = [&](int n, int st) {
     load_tile_async<BN, D, NT>(sV + st * BN * P, vg, D, n * BN, S, tid);
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(128) fwd_int8_mma_kernel(const fa_int8_args p)
         const int row = r0 + i * 8;
         // (float(acc) * (s_q * s_k)) * qk_scale, then the additive -1e6 mask of the reference
         float v = __fmul_rn(__fmul_rn((float)acc[nb][e], __fmul_rn(sq_row[i], cS[cl])), qk_scale);
-        const bool keep = col < S && (!p.causal || col <= row);
+        const bool keep = col < klen && (!p.causal || col <= row + off);
         if (!keep) v += -1.0e6f;
         s[nb][e] = v;
         tmax[i] = fmaxf(tmax[i], v);

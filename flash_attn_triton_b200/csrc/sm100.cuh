@@ -31,6 +31,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
+// n arrivals at once (a role that stands in for several arrivals of a phase)
+__device__ __forceinline__ void mbar_arrive_cnt(uint32_t bar, uint32_t n) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(n) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -59,15 +63,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
 
 // Bounded wait used by the warp-specialised kernels: the already-complete case costs one
 // try_wait; otherwise spin, and every 256 polls look at the CTA's abort flag, at the device-wide
-// status word and at the clock.  After FA_WAIT_CLOCKS (~1 s) the waiter raises the CTA's abort
-// flag (so every other role of the CTA unwinds at its next poll) and the status word (so every
-// other CTA of this and of later launches gives up at once instead of waiting out its own
-// limit), and returns false.  The status word stays set until the process ends.
+// status word and at the clock.  After `limit` clocks (FA_WAIT_CLOCKS, ~1 s, in the kernels) the
+// waiter raises the CTA's abort flag (so every other role of the CTA unwinds at its next poll)
+// and the status word (so every other CTA of this and of later launches gives up at once instead
+// of waiting out its own limit), and returns false.  A CTA that unwound this way reports the code
+// to the host through report_abort() just before it exits.  The words stay set until
+// fa_device_wait_clear().
+// (The loop is kept exactly this small: a variant that also stored to host memory on the
+// time-out path made every kernel that waits through it measurably slower.)
 #ifndef FA_WAIT_CLOCKS
 #define FA_WAIT_CLOCKS 2000000000LL
 #endif
+template <long long kLimit = FA_WAIT_CLOCKS>
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
-                                             int* status, int code) {
+                                             int* status, int code, long long runtime_limit = 0) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
   if (mbar_try_wait(a, parity)) return true;
   const long long t0 = clock64();
@@ -79,12 +88,20 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
         *cta_abort = code;
         return false;
       }
-      if (clock64() - t0 > FA_WAIT_CLOCKS) {
+      if (clock64() - t0 > (kLimit > 0 ? kLimit : runtime_limit)) {
         *cta_abort = code;
         atomicCAS(status, 0, code);
         return false;
       }
     }
+  }
+}
+// Called by one thread of a CTA after its last barrier: when the CTA gave up on a wait, the code
+// goes to the word in mapped host memory that the entry points read before every launch.
+__device__ __forceinline__ void report_abort(int abort_code, volatile int* host_status) {
+  if (abort_code != 0 && host_status != nullptr) {
+    *host_status = abort_code;
+    __threadfence_system();
   }
 }
 

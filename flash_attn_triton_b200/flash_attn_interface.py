@@ -5,8 +5,8 @@ What is different underneath (results are the same within fp16 tolerance):
 * tensors are handed to the kernels in place -- no pad-to-64, no head-major transposes,
   no repeat_interleave for GQA (reference: flash_attn_interface.py:168-212, :300-317);
 * `flash_attn_with_kvcache` really appends to the cache, in place, and runs as one launch
-  chain with no host synchronisation (reference loops over the batch in Python, :501-525,
-  and its append at :487-492 writes into a temporary);
+  chain (no host synchronisation once the value checks are off, see set_validation; the reference
+  loops over the batch in Python, :501-525, and its append at :487-492 writes into a temporary);
 * bf16 is accepted as well as fp16;
 * `use_native_gqa` and `deterministic` are accepted and change nothing: GQA is always native
   and the backward always has a single writer per element.
@@ -227,7 +227,12 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
     (num_pages, page_size, nheads_k, d) with block_table (batch, max_pages);
     cache_seqlens = tokens already in the cache before this call.  The query rows are the
     last seqlen_q positions of the sequence after the append; causal, window and ALiBi are
-    measured from there.  `num_splits` (0 = automatic) is an extra tuning knob."""
+    measured from there (also without `causal`: the reference only shifts the causal mask,
+    flash_attn_interface.py:523).  `num_splits` (0 = automatic) is an extra tuning knob.
+
+    With value checks on (the default) the call reads a few flags back from the device (page
+    indices in range, lengths fit the cache and the rotary tables); `set_validation(False)` or
+    FA_B200_VALIDATE=0 turns them off and the call then never synchronises."""
     paged = block_table is not None
     if (rotary_cos is None) != (rotary_sin is None):
         raise ValueError("rotary_cos and rotary_sin must be supplied together")
@@ -318,6 +323,11 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
             raise ValueError("rotary_cos and rotary_sin must be (seqlen_ro, rotary_dim / 2)")
         if rotary_cos.shape[-1] * 2 > q.shape[-1]:
             raise ValueError("rotary tables exceed the head dimension")
+        if _VALIDATE:
+            # every rotated position (new keys and query rows) must have a table row
+            last = lengths.long() + n_new + (pads.long() if pads is not None else 0)
+            if torch.any(last > rotary_cos.shape[0]):
+                raise ValueError("rotary tables are shorter than the longest sequence after the append")
         cos = rotary_cos.to(device=dev, dtype=q.dtype).contiguous()
         sin = rotary_sin.to(device=dev, dtype=q.dtype).contiguous()
     alibi = _normalise_alibi(alibi_slopes, B, q.shape[2], dev)
@@ -475,7 +485,8 @@ def flash_attn_varlen_qkvpacked_func(qkv, cu_seqlens, max_seqlen, dropout_p=0.0,
 def attention_int8(q, k, v, causal=False, sm_scale=None, seq_len_k=None, seq_len_q=None):
     """INT8-QK^T attention on contiguous fp16 [B, H, S, D] tensors; fp16 backward.
     Same contract as the reference's attention_int8 (attention_kernel_int8.py:270-299) minus
-    its Turing-only gate: this one runs on sm_100."""
+    its Turing-only gate: this one runs on sm_100.  S must be a multiple of 64; a caller with
+    another length pads q, k, v and passes the true lengths as seq_len_k / seq_len_q."""
     head_dim = q.shape[-1]
     if not q.is_cuda:
         raise ValueError("The INT8 kernel requires CUDA tensors")
@@ -493,7 +504,15 @@ def attention_int8(q, k, v, causal=False, sm_scale=None, seq_len_k=None, seq_len
         raise ValueError("The INT8 kernel requires q, k and v of the same shape")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
-    return _ops.Int8Attention.apply(q, k, v, causal, sm_scale, N.IMPL_AUTO)
+    S = q.shape[2]
+    seq_len_k = S if seq_len_k is None else int(seq_len_k)
+    seq_len_q = S if seq_len_q is None else int(seq_len_q)
+    if not 0 < seq_len_k <= S or not 0 < seq_len_q <= S:
+        raise ValueError("seq_len_k and seq_len_q must lie in (0, padded sequence length]")
+    # Padded calls (attention_kernel_int8.py:108-118, :245): keys at or past seq_len_k are masked and
+    # the causal diagonal is shifted by seq_len_k - seq_len_q, in the forward and in the backward.
+    return _ops.Int8Attention.apply(q, k, v, causal, sm_scale, N.IMPL_AUTO,
+                                    seq_len_k if seq_len_k < S else 0, seq_len_k - seq_len_q)
 
 
 class FlashSelfAttention(torch.nn.Module):

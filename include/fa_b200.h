@@ -41,7 +41,7 @@ typedef enum fa_status {
   FA_ERR_DEVICE_WAIT = -5  /* a bounded device-side wait ran out (kernel set its flag) */
 } fa_status;
 
-typedef enum fa_dtype { FA_F16 = 0, FA_BF16 = 1 } fa_dtype;
+typedef enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 /* rotary / row movers only */ } fa_dtype;
 
 /* Kernel family selector (fa_attn_args.impl). */
 typedef enum fa_impl {
@@ -228,23 +228,85 @@ typedef struct fa_int8_args {
    * mma.sync kernel (which quantises q in shared memory) is used. */
   int8_t* q8_scratch;
   float* sq_scratch;
+  /* Padded calls (attention_kernel_int8.py:108-118, :245): keys at or past seqlen_k_valid are
+   * masked (0 = all seqlen keys are valid), and query row i sits at position i + q_pos_offset for
+   * the causal mask (the reference passes SEQ_LEN_K - SEQ_LEN_Q). */
+  int32_t seqlen_k_valid;
+  int32_t q_pos_offset;
 } fa_int8_args;
 
 int fa_fwd_int8(const fa_int8_args* args, void* stream);
+
+/*
+ * Rotary position embedding on x (batch, seqlen, heads, head_dim) -- or packed (tokens, heads,
+ * head_dim) with cu_seqlens -- into out (same layout; out == x rotates in place):
+ *   non-interleaved: pairs (x[i], x[i + rotary_dim/2]);  interleaved: pairs (x[2i], x[2i+1])
+ *   o0 = x0 cos - x1 sin,  o1 = x0 sin + x1 cos   in fp32, rounded once;  conjugate negates sin
+ * Row r of sequence b uses table row r + seqlen_offsets[b] (or + seqlen_offset); rows past the
+ * table read cos = 1, sin = 0; columns >= rotary_dim are copied.  cos/sin have x's dtype.
+ * Replaces rotary_kernel / apply_rotary (flash_attn/ops/triton/rotary.py:11-130, :133-234).
+ */
+typedef struct fa_rotary_args {
+  int32_t dtype, device; /* fa_dtype incl. FA_F32 */
+  int32_t batch, seqlen, heads, head_dim; /* seqlen = the longest sequence when packed */
+  const void* x;
+  void* out;
+  int64_t x_stride[3], out_stride[3]; /* (batch, row, head) in elements; packed ignores [0] */
+  const void* cos; /* (rotary_seqlen, rotary_dim/2) contiguous */
+  const void* sin;
+  int32_t rotary_dim, rotary_seqlen;
+  int32_t interleaved, conjugate;
+  int32_t seqlen_offset;          /* used when seqlen_offsets is NULL */
+  const int32_t* seqlen_offsets;  /* (batch) or NULL */
+  const int32_t* cu_seqlens;      /* (batch+1) or NULL */
+} fa_rotary_args;
+
+int fa_rotary(const fa_rotary_args* args, void* stream);
+
+/*
+ * Row movers for un-padding / re-padding a batch.  Rows are row_bytes long (a multiple of 16),
+ * src/dst 16-byte aligned, idx int64 on the device.
+ *   fa_gather_rows:   dst[i] = src[idx[i]]            (an index outside [0, src_rows) yields zeros)
+ *   fa_scatter_rows:  dst[idx[i]] = src[i], or += in element type add_dtype (fa_dtype; -1 = plain
+ *                     store).  Indices of one call must be distinct; one outside [0, dst_rows) is
+ *                     dropped.  Rows of dst that no index names keep their contents.
+ * Replace IndexFirstAxis / IndexPutFirstAxis / IndexFirstAxisResidual
+ * (flash_attn/bert_padding.py:8-96).
+ */
+int fa_gather_rows(const void* src, void* dst, const int64_t* idx, int64_t n_idx, int64_t row_bytes,
+                   int64_t src_rows, int32_t device, void* stream);
+int fa_scatter_rows(const void* src, void* dst, const int64_t* idx, int64_t n_idx, int64_t row_bytes,
+                    int64_t dst_rows, int32_t add_dtype, int32_t device, void* stream);
 
 /* Host-only helpers. */
 const char* fa_version(void);
 const char* fa_last_error(void);
 /* 1 when fa_fwd with FA_IMPL_AUTO would pick the tcgen05 kernel for these arguments. */
 int fa_fwd_uses_tcgen05(const fa_attn_args* args);
-/* Status word of the tcgen05 kernels' bounded waits on `device`: 0, or the code of the wait
- * that ran out (the kernel then released its tensor memory and returned early, leaving its
- * outputs incomplete).  Once set the word stays set until the process ends, and every later
- * tcgen05 launch on that device returns at its first wait.  Synchronises the device. */
+/*
+ * Time-outs of bounded device-side waits.  Every wait inside the tcgen05 kernels gives up after
+ * about a second; the kernel that gave up raises a status word (device memory, and a mirror in
+ * mapped host memory), releases its tensor memory and returns early, leaving its outputs
+ * incomplete.  From then on
+ *   - every tcgen05 launch on that device returns at its first wait, and
+ *   - fa_fwd / fa_bwd_* / fa_varlen_* / fa_fwd_int8 return FA_ERR_DEVICE_WAIT instead of launching
+ *     a tcgen05 kernel, as soon as the host mirror shows the code (no synchronisation needed),
+ * until fa_device_wait_clear() is called.
+ *
+ * fa_device_wait_status: 0, or the code of the wait that ran out.  Synchronises the device.
+ * fa_device_wait_clear:  synchronises, then puts the words of `device` back to zero.
+ * fa_wait_probe:         launches ONE warp that waits, for at most `clocks` cycles, on a barrier
+ *                        nothing ever arrives at (no copy or MMA in flight): exercises the
+ *                        time-out path for bring-up and tests.  Leaves the status set (code 99).
+ * fa_debug_set_wait_status: writes the host mirror only (host-side tests of the refusal).
+ */
 int fa_device_wait_status(int device);
+int fa_device_wait_clear(int device);
+int fa_wait_probe(int32_t device, int64_t clocks, void* stream);
+int fa_debug_set_wait_status(int32_t device, int32_t code);
 /* sizeof of an argument block as this library was compiled: 0 = fa_attn_args,
  * 1 = fa_decode_args, 2 = fa_int8_args.  Lets a foreign-language binding check its
- * struct layout before the first call. */
+ * struct layout before the first call.  3 = fa_rotary_args. */
 size_t fa_sizeof_args(int which);
 
 #ifdef __cplusplus

@@ -14,9 +14,11 @@ from the reference's own eager restatement and kernels:
 * base-2 LSE saved for the backward .......... flash_attn_triton/triton_kernel/attention_kernel.py:522-533
 * per-token INT8 K quantiser ................. flash_attn_triton/triton_kernel/attention_kernel_int8.py:27-30,58-79
 * INT8 QK^T forward .......................... flash_attn_triton/triton_kernel/attention_kernel_int8.py:82-141,167-217
+* rotary-embedding kernel (helper package) ... flash_attn/ops/triton/rotary.py:11-130
+* un-padding / re-padding (helper package) ... flash_attn/bert_padding.py:98-213
 
 Parity pin: tests/golden/*.npz hold outputs of the unmodified reference kernels run
-under Triton's CPU interpreter (tests/golden/make_golden.py); tests/test_oracle_golden.py
+under Triton's CPU interpreter (tests/golden/make_golden.py, make_golden_compat.py); tests/test_oracle_golden.py
 checks every function below against them.
 """
 from __future__ import annotations
@@ -281,7 +283,16 @@ def quantize_q_rows_ref(q):
     return round_i8_np(x), s
 
 
-def attention_int8_ref(q, k, v, causal=False, sm_scale=None):
+def _int8_keep(S, causal, seq_len_k, seq_len_q):
+    """Mask of a padded INT8 call (attention_kernel_int8.py:108-118): keys at or past seq_len_k
+    are dropped, query row i sits at position i + seq_len_k - seq_len_q for the causal test."""
+    seq_len_k = S if seq_len_k is None else seq_len_k
+    seq_len_q = S if seq_len_q is None else seq_len_q
+    keep = keep_mask(S, S, causal, (-1, -1), q_pos_offset=seq_len_k - seq_len_q)
+    return keep & (torch.arange(S) < seq_len_k)[None, :]
+
+
+def attention_int8_ref(q, k, v, causal=False, sm_scale=None, seq_len_k=None, seq_len_q=None):
     """INT8-QK^T forward in the reference's arithmetic.  q,k,v: fp16 (B,H,S,D).
 
     scores(log2) = float(int32 q8.k8) * (s_q*s_k) * (sm_scale*1.44269504)
@@ -297,9 +308,8 @@ def attention_int8_ref(q, k, v, causal=False, sm_scale=None):
                        torch.from_numpy(k8.astype(np.float32)))  # exact: |sum| < 2^24
     qk = acc * (torch.from_numpy(s_q)[..., :, None] * torch.from_numpy(s_k)[..., None, :])
     qk = qk * np.float32(sm_scale * 1.44269504)
-    if causal:
-        keep = keep_mask(S, S, True, (-1, -1))
-        qk = qk + torch.where(keep, 0.0, -1.0e6)[None, None]
+    keep = _int8_keep(S, causal, seq_len_k, seq_len_q)
+    qk = qk + torch.where(keep, 0.0, -1.0e6)[None, None]
     m = qk.max(dim=-1, keepdim=True).values
     p = torch.exp2(qk - m)
     l = p.sum(dim=-1, keepdim=True)
@@ -308,7 +318,7 @@ def attention_int8_ref(q, k, v, causal=False, sm_scale=None):
     return out, lse2, k8, s_k
 
 
-def attention_int8_grads_ref(q, k, v, dout, causal=False, sm_scale=None):
+def attention_int8_grads_ref(q, k, v, dout, causal=False, sm_scale=None, seq_len_k=None, seq_len_q=None):
     """Gradients the INT8 path returns: the fp16 dense backward run on the ORIGINAL fp16
     q,k,v with the base-2 LSE and the output saved by the INT8 forward
     (attention_kernel_int8.py:256-267 -> attention_kernel.py:1104-1155).  So
@@ -317,13 +327,12 @@ def attention_int8_grads_ref(q, k, v, dout, causal=False, sm_scale=None):
     B, H, S, D = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    out, lse2, _, _ = attention_int8_ref(q, k, v, causal, sm_scale)
+    out, lse2, _, _ = attention_int8_ref(q, k, v, causal, sm_scale, seq_len_k, seq_len_q)
     o16 = out.half().float()
     qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
     s2 = torch.einsum("bhqd,bhkd->bhqk", qf, kf) * (sm_scale * LOG2E)
     p = torch.exp2(s2 - lse2[..., None])
-    if causal:
-        p = p * keep_mask(S, S, True, (-1, -1))[None, None]
+    p = p * _int8_keep(S, causal, seq_len_k, seq_len_q)[None, None]
     delta = (o16 * dof).sum(-1, keepdim=True)
     dp = torch.einsum("bhqd,bhkd->bhqk", dof, vf)
     ds = p * (dp - delta)
@@ -331,3 +340,65 @@ def attention_int8_grads_ref(q, k, v, dout, causal=False, sm_scale=None):
     dq = torch.einsum("bhqk,bhkd->bhqd", ds, kf) * sm_scale
     dk = torch.einsum("bhqk,bhqd->bhkd", ds, qf) * sm_scale
     return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------------------
+# helper package: rotary embedding kernel and un-padding (flash_attn/ in the reference)
+# ---------------------------------------------------------------------------------------
+def rotary_emb_ref(x, cos, sin, seqlen_offsets=0, cu_seqlens=None, max_seqlen=None, interleaved=False,
+                   conjugate=False):
+    """Rotary embedding as the reference's kernel computes it
+    (flash_attn/ops/triton/rotary.py:11-130): fp32 arithmetic on the first rotary_dim columns,
+    o0 = x0 cos - x1 sin, o1 = x0 sin + x1 cos with pairs (i, i + rotary_dim/2) or, interleaved,
+    (2i, 2i+1); sin negated for the conjugate (backward) form; table rows past the end read
+    cos = 1, sin = 0; one rounding to x's dtype.  x (B,S,H,D), or packed (T,H,D) with cu_seqlens."""
+    xf = x.float()
+    out = xf.clone()
+    half = cos.shape[1]
+    rot = 2 * half
+    cf, sf = cos.float(), sin.float()
+    if conjugate:
+        sf = -sf
+
+    def one(seq, offset):                              # seq (S,H,D) view of `out`, rotated in place
+        pos = torch.arange(seq.shape[0]) + int(offset)
+        ok = (pos >= 0) & (pos < cf.shape[0])
+        c = torch.where(ok[:, None], cf[pos.clamp(0, cf.shape[0] - 1)], torch.ones(1))[:, None, :]
+        s = torch.where(ok[:, None], sf[pos.clamp(0, cf.shape[0] - 1)], torch.zeros(1))[:, None, :]
+        if interleaved:
+            x0, x1 = seq[..., 0:rot:2].clone(), seq[..., 1:rot:2].clone()
+            seq[..., 0:rot:2] = x0 * c - x1 * s
+            seq[..., 1:rot:2] = x0 * s + x1 * c
+        else:
+            x0, x1 = seq[..., :half].clone(), seq[..., half:rot].clone()
+            seq[..., :half] = x0 * c - x1 * s
+            seq[..., half:rot] = x0 * s + x1 * c
+
+    if cu_seqlens is None:
+        for b in range(x.shape[0]):
+            off = seqlen_offsets[b] if isinstance(seqlen_offsets, torch.Tensor) else seqlen_offsets
+            one(out[b], off)
+    else:
+        cu = [int(c) for c in cu_seqlens]
+        for b in range(len(cu) - 1):
+            off = seqlen_offsets[b] if isinstance(seqlen_offsets, torch.Tensor) else seqlen_offsets
+            one(out[cu[b]:cu[b + 1]], off)
+    return out.to(x.dtype)
+
+
+def unpad_ref(hidden_states, attention_mask):
+    """(tokens, indices, cu_seqlens int32, max_seqlen) of the valid positions of a padded batch
+    (flash_attn/bert_padding.py:98-122), with plain indexing."""
+    lens = attention_mask.sum(dim=-1).to(torch.int32)
+    idx = torch.nonzero(attention_mask.flatten()).flatten()
+    cu = torch.cat([torch.zeros(1, dtype=torch.int32), torch.cumsum(lens, 0).to(torch.int32)])
+    flat = hidden_states.reshape((-1,) + tuple(hidden_states.shape[2:]))
+    return flat[idx], idx, cu, int(lens.max())
+
+
+def pad_ref(tokens, indices, batch, seqlen):
+    """Zero-padded (batch, seqlen, ...) tensor with `tokens` at `indices`
+    (flash_attn/bert_padding.py:197-213)."""
+    out = torch.zeros((batch * seqlen,) + tuple(tokens.shape[1:]), dtype=tokens.dtype)
+    out[indices] = tokens
+    return out.reshape((batch, seqlen) + tuple(tokens.shape[1:]))

@@ -25,7 +25,7 @@ import sys
 import types
 
 
-def load_reference(path: str = "/root/reference"):
+def load_reference(path: str):
     os.environ["TRITON_INTERPRET"] = "1"
     import torch
     import triton

@@ -86,3 +86,59 @@ def paged_case(seed, B, Hq, Hkv, D, page, n_pages, lens, max_pages):
         bt[b, need:] = perm[at]
         at += need
     return q, kc, vc, kn, vn, torch.from_numpy(bt), torch.tensor(lens, dtype=torch.int32)
+
+
+# ----------------------------------------------------------------------------------------
+# helper package (rotary embedding, un-padding)
+# ----------------------------------------------------------------------------------------
+ROTARY_CASES = {
+    # name: generator arguments
+    "half": dict(seed=50, B=2, S=9, H=3, D=32, rot=32, S_ro=16),
+    "half_partial": dict(seed=51, B=2, S=9, H=3, D=64, rot=32, S_ro=16),
+    "interleaved": dict(seed=52, B=2, S=10, H=2, D=32, rot=16, S_ro=24, interleaved=True),
+    "offset_int": dict(seed=53, B=1, S=7, H=2, D=32, rot=32, S_ro=16, offset=5),
+    "offset_tensor": dict(seed=54, B=3, S=6, H=2, D=32, rot=32, S_ro=20, offsets=[0, 7, 14]),
+    "conjugate": dict(seed=55, B=2, S=8, H=2, D=32, rot=32, S_ro=8, conjugate=True, interleaved=True),
+    "varlen": dict(seed=56, B=3, S=0, H=2, D=32, rot=32, S_ro=16, lens=[5, 1, 9]),
+}
+
+
+def rotary_case(seed, B, S, H, D, rot, S_ro, interleaved=False, conjugate=False, offset=0, offsets=None,
+                lens=None):
+    """x (B,S,H,D) -- or packed (sum(lens),H,D) -- fp16 N(0,1); cos/sin (S_ro, rot/2) fp16 from
+    base-10000 frequencies.  Returns (x, cos, sin, kwargs of apply_rotary)."""
+    rng = np.random.default_rng(seed)
+    inv = 1.0 / (10000.0 ** (np.arange(0, rot, 2, dtype=np.float32) / rot))
+    ang = np.arange(S_ro, dtype=np.float32)[:, None] * inv[None, :]
+    cos = torch.from_numpy(np.cos(ang).astype(np.float16))
+    sin = torch.from_numpy(np.sin(ang).astype(np.float16))
+    kw = dict(interleaved=interleaved, conjugate=conjugate)
+    if lens is not None:
+        x = randn16(rng, sum(lens), H, D)
+        kw.update(cu_seqlens=torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32),
+                  max_seqlen=max(lens))
+    else:
+        x = randn16(rng, B, S, H, D)
+    if offsets is not None:
+        kw["seqlen_offsets"] = torch.tensor(offsets, dtype=torch.int32)
+    elif offset:
+        kw["seqlen_offsets"] = offset
+    return x, cos, sin, kw
+
+
+def padding_case(seed, B, S, H, D):
+    """hidden states (B,S,H,D) fp16, a (B,S) 0/1 mask with ragged valid prefixes, and the
+    (B,S) lengths-in-row table of the concatenated-samples variant."""
+    rng = np.random.default_rng(seed)
+    hs = randn16(rng, B, S, H, D)
+    valid = rng.integers(1, S + 1, size=B)
+    mask = torch.from_numpy((np.arange(S)[None, :] < valid[:, None]).astype(np.int32))
+    lens_in_row = np.zeros((B, S), dtype=np.int32)
+    for b in range(B):
+        left, i = int(valid[b]), 0
+        while left > 0:
+            n = int(rng.integers(1, left + 1))
+            lens_in_row[b, i] = n
+            left -= n
+            i += 1
+    return hs, mask, torch.from_numpy(lens_in_row)

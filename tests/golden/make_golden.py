@@ -2,7 +2,7 @@
 
 Run from the repository root in a container that has the reference checked out:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference [case ...]     (or FA_REF_PATH=...)
 
 The reference's Triton kernels are executed by Triton's interpreter (see
 oracle/ref_loader.py for the three harness shims).  Inputs come from tests/golden/cases.py;
@@ -21,7 +21,10 @@ sys.path.insert(0, HERE)
 
 from oracle.ref_loader import load_reference  # noqa: E402
 
-REF = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+_REF_PATH = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FA_REF_PATH")
+if not _REF_PATH:
+    sys.exit("pass the reference checkout as argv[1] or in FA_REF_PATH")
+REF = load_reference(_REF_PATH)
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
@@ -152,6 +155,14 @@ def int8():
         out = AK8._attention_int8.apply(qg, kg, vg, causal, 0.125, 128, 128)
         dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
         save(f"int8_bwd_causal{int(causal)}", checksum=cases.checksum(q, k, v, do), out=out,
+             dq=dq, dk=dk, dv=dv)
+        # padded call: 150 valid tokens inside 192 rows, seq_len_k = seq_len_q = 150 (:108-118, :245)
+        q, k, v = cases.int8_case(33, 1, 2, 192, 64)
+        do = cases.randn16(np.random.default_rng(34), 1, 2, 192, 64)
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        out = AK8._attention_int8.apply(qg, kg, vg, causal, 0.125, 150, 150)
+        dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
+        save(f"int8_padded_causal{int(causal)}", checksum=cases.checksum(q, k, v, do), out=out,
              dq=dq, dk=dk, dv=dv)
 
 

@@ -96,6 +96,33 @@ def test_golden_int8_backward(golden, causal):
         assert util.excess(tr(t), r, rel=2e-2) <= INT8_GRAD_TOL  # atol and rtol of the reference's test
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+def test_golden_int8_padded(golden, causal):
+    """A padded call: 150 valid tokens in 192 rows, seq_len_k = seq_len_q = 150
+    (attention_kernel_int8.py:108-118, :245), against the reference's outputs and gradients."""
+    import flash_attn_triton_b200 as fa
+    g = golden(f"int8_padded_causal{causal}")
+    q, k, v = cases.int8_case(33, 1, 2, 192, 64)
+    do = cases.randn16(np.random.default_rng(34), 1, 2, 192, 64)
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    out = fa.attention_int8(qd, kd, vd, causal=bool(causal), sm_scale=0.125, seq_len_k=150, seq_len_q=150)
+    dq, dk, dv = torch.autograd.grad((out.float() * do.to(DEV).float()).sum(), (qd, kd, vd))
+    assert maxdiff(out, g["out"]) <= util.FWD_TOL
+    # the reference's dq of the padded query rows is not meaningful under a causal mask (it skips
+    # the key-length mask there); everything a caller keeps is compared
+    assert maxdiff(dq[:, :, :150], g["dq"][:, :, :150]) <= util.GRAD_TOL
+    assert maxdiff(dk, g["dk"]) <= util.GRAD_TOL and maxdiff(dv, g["dv"]) <= util.GRAD_TOL
+    assert not dk[:, :, 150:].any() and not dv[:, :, 150:].any()
+    # D = 128 takes the tcgen05 kernel: same call against the oracle, with a causal offset too
+    q, k, v = cases.int8_case(35, 1, 2, 320, 128)
+    for lk, lq in ((300, 300), (257, 200)):
+        o = fa.attention_int8(q.to(DEV), k.to(DEV), v.to(DEV), causal=bool(causal), seq_len_k=lk, seq_len_q=lq)
+        ro, _, _, _ = orc.attention_int8_ref(q, k, v, causal=bool(causal), seq_len_k=lk, seq_len_q=lq)
+        assert maxdiff(o, ro) <= util.FWD_TOL, (lk, lq)
+    with pytest.raises(ValueError):
+        fa.attention_int8(q.to(DEV), k.to(DEV), v.to(DEV), seq_len_k=321)
+
+
 def test_int8_value_errors():
     import flash_attn_triton_b200 as fa
     q = torch.zeros(1, 1, 64, 64, device=DEV, dtype=torch.float16)
