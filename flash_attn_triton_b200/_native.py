@@ -35,6 +35,9 @@ class AttnArgs(C.Structure):
         ("dout", C.c_void_p), ("do_stride", _I64x3), ("delta", C.c_void_p),
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("dq_stride", _I64x3), ("dk_stride", _I64x3), ("dv_stride", _I64x3),
+        ("seqused_q", C.c_void_p), ("seqused_k", C.c_void_p),
+        ("attn_bias", C.c_void_p), ("bias_stride", C.c_int64 * 4),
+        ("dropout_p", C.c_float), ("dropout_row_stride", C.c_int32), ("dropout_seed", C.c_uint64),
     ]
 
 
@@ -89,6 +92,8 @@ EXPORTS = {
     "fa_bwd_preprocess": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fa_bwd_dq": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fa_bwd_dkdv": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "fa_attn_probs": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p, C.POINTER(C.c_int64 * 4), C.c_void_p, C.c_int64,
+                                C.c_void_p]),
     "fa_varlen_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fa_varlen_bwd_dq": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "fa_varlen_bwd_dkdv": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
@@ -111,6 +116,7 @@ EXPORTS = {
     "fa_device_wait_clear": (C.c_int, [C.c_int]),
     "fa_wait_probe": (C.c_int, [C.c_int32, C.c_int64, C.c_void_p]),
     "fa_debug_set_wait_status": (C.c_int, [C.c_int32, C.c_int32]),
+    "fa_mma_peak_probe": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "fa_sizeof_args": (C.c_size_t, [C.c_int]),
 }
 

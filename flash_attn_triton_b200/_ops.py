@@ -24,8 +24,34 @@ def _alibi_ptr(alibi):
     return None if alibi is None else alibi.data_ptr()
 
 
+class Features:
+    """The options beyond the score pipeline that the argument block carries: an additive fp32
+    bias (batch, heads, rows, cols; broadcast dimensions have stride 0), dropout with the
+    reference's random stream, and the per-sequence length overrides of a packed batch."""
+
+    __slots__ = ("bias", "dropout_p", "seed", "row_stride", "seqused_q", "seqused_k")
+
+    def __init__(self, bias=None, dropout_p=0.0, seed=0, row_stride=0, seqused_q=None, seqused_k=None):
+        self.bias, self.dropout_p, self.seed, self.row_stride = bias, float(dropout_p), int(seed), int(row_stride)
+        self.seqused_q, self.seqused_k = seqused_q, seqused_k
+
+    def tensors(self):
+        return [t for t in (self.bias, self.seqused_q, self.seqused_k) if t is not None]
+
+    def fill(self, a):
+        if self.bias is not None:
+            a.attn_bias = self.bias.data_ptr()
+            a.bias_stride = (C.c_int64 * 4)(*self.bias.stride())
+        if self.dropout_p > 0.0:
+            a.dropout_p, a.dropout_seed, a.dropout_row_stride = self.dropout_p, self.seed, self.row_stride
+        a.seqused_q, a.seqused_k = N.ptr(self.seqused_q), N.ptr(self.seqused_k)
+
+
+_NO_FEATURES = Features()
+
+
 def _fill_common(a, q, k, v, o, dims_q, dims_k, *, batch, sq, sk, hq, hkv, d, scale, causal, wl,
-                 wr, softcap, alibi, q_pos_offset, impl, cu_q=None, cu_k=None):
+                 wr, softcap, alibi, q_pos_offset, impl, cu_q=None, cu_k=None, feat=None):
     a.dtype = N.dtype_code(q.dtype)
     a.device = q.device.index if q.device.index is not None else torch.cuda.current_device()
     a.impl = impl
@@ -46,6 +72,7 @@ def _fill_common(a, q, k, v, o, dims_q, dims_k, *, batch, sq, sk, hq, hkv, d, sc
     a.causal = int(bool(causal))
     a.window_left, a.window_right = int(wl), int(wr)
     a.q_pos_offset = int(q_pos_offset)
+    (feat or _NO_FEATURES).fill(a)
 
 
 # dimension indices of (batch, row, head) in each layout
@@ -55,7 +82,7 @@ _THD = (None, 0, 1)    # packed (tokens, heads, dim)
 
 
 def dense_forward(q, k, v, scale, causal, wl, wr, softcap, alibi, q_pos_offset, impl, layout,
-                  want_lse):
+                  want_lse, feat=None):
     dims = _BSHD if layout == "bshd" else _BHSD
     B = q.shape[0]
     Sq, Hq = q.shape[dims[1]], q.shape[dims[2]]
@@ -67,7 +94,7 @@ def dense_forward(q, k, v, scale, causal, wl, wr, softcap, alibi, q_pos_offset, 
     a = N.AttnArgs()
     _fill_common(a, q, k, v, o, dims, dims, batch=B, sq=Sq, sk=Sk, hq=Hq, hkv=Hkv, d=D,
                  scale=scale, causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi,
-                 q_pos_offset=q_pos_offset, impl=impl)
+                 q_pos_offset=q_pos_offset, impl=impl, feat=feat)
     if lse is not None:
         a.lse2 = lse.data_ptr()
         a.lse_stride = N._I64x3(Hq * Sq, 1, Sq)
@@ -76,8 +103,31 @@ def dense_forward(q, k, v, scale, causal, wl, wr, softcap, alibi, q_pos_offset, 
     return o, lse, (q, k, v)
 
 
+def dense_probs(q, k, v, lse, scale, causal, wl, wr, softcap, alibi, q_pos_offset, layout, feat=None):
+    """(probabilities fp32 (B, Hq, Sq, Sk), natural-log LSE (B, Hq, Sq)) of a dense call whose
+    forward produced the base-2 `lse`: the return_attn_probs surface
+    (flash_attn_interface.py:139-143 of the reference), from the fa_attn_probs kernel."""
+    dims = _BSHD if layout == "bshd" else _BHSD
+    B = q.shape[0]
+    Sq, Hq = q.shape[dims[1]], q.shape[dims[2]]
+    Sk, Hkv = k.shape[dims[1]], k.shape[dims[2]]
+    probs = torch.zeros((B, Hq, Sq, Sk), dtype=torch.float32, device=q.device)
+    lse_nat = torch.full((B, Hq, Sq), float("-inf"), dtype=torch.float32, device=q.device)
+    a = N.AttnArgs()
+    _fill_common(a, q, k, v, q, dims, dims, batch=B, sq=Sq, sk=Sk, hq=Hq, hkv=Hkv, d=q.shape[-1], scale=scale,
+                 causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi, q_pos_offset=q_pos_offset,
+                 impl=N.IMPL_AUTO, feat=feat)
+    a.lse2 = lse.data_ptr()
+    a.lse_stride = N._I64x3(Hq * Sq, 1, Sq)
+    ps = (C.c_int64 * 4)(*probs.stride())
+    with torch.cuda.device(q.device):
+        N.check(N.lib().fa_attn_probs(C.byref(a), probs.data_ptr(), C.byref(ps), lse_nat.data_ptr(), Sq,
+                                      N.stream_ptr(q.device)), "fa_attn_probs")
+    return probs, lse_nat
+
+
 def dense_backward(q, k, v, o, lse, dout, scale, causal, wl, wr, softcap, alibi, q_pos_offset,
-                   impl, layout):
+                   impl, layout, feat=None):
     dims = _BSHD if layout == "bshd" else _BHSD
     B = q.shape[0]
     Sq, Hq = q.shape[dims[1]], q.shape[dims[2]]
@@ -91,7 +141,7 @@ def dense_backward(q, k, v, o, lse, dout, scale, causal, wl, wr, softcap, alibi,
     a = N.AttnArgs()
     _fill_common(a, q, k, v, o, dims, dims, batch=B, sq=Sq, sk=Sk, hq=Hq, hkv=Hkv, d=D,
                  scale=scale, causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi,
-                 q_pos_offset=q_pos_offset, impl=impl)
+                 q_pos_offset=q_pos_offset, impl=impl, feat=feat)
     a.lse2 = lse.data_ptr()
     a.lse_stride = N._I64x3(Hq * Sq, 1, Sq)
     a.dout, a.do_stride = dout.data_ptr(), N.strides3(dout, dims)
@@ -112,26 +162,31 @@ class DenseAttention(torch.autograd.Function):
     """q (B,Sq,Hq,D), k/v (B,Sk,Hkv,D) ["bshd"] or head-major ["bhsd"]; returns o like q."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, wl, wr, softcap, alibi, q_pos_offset, impl, layout):
+    def forward(ctx, q, k, v, scale, causal, wl, wr, softcap, alibi, q_pos_offset, impl, layout, feat=None,
+                want_lse=False):
         need = any(t.requires_grad for t in (q, k, v))
         o, lse, (q, k, v) = dense_forward(q, k, v, scale, causal, wl, wr, softcap, alibi,
-                                          q_pos_offset, impl, layout, want_lse=need)
+                                          q_pos_offset, impl, layout, want_lse=need or want_lse, feat=feat)
         if need:
             ctx.save_for_backward(q, k, v, o, lse, alibi if alibi is not None else q.new_empty(0))
             ctx.cfg = (scale, causal, wl, wr, softcap, alibi is not None, q_pos_offset, impl, layout)
+            ctx.feat = feat
+        if want_lse:
+            ctx.mark_non_differentiable(lse)
+            return o, lse
         return o
 
     @staticmethod
-    def backward(ctx, dout):
+    def backward(ctx, dout, *unused):
         q, k, v, o, lse, alibi = ctx.saved_tensors
         scale, causal, wl, wr, softcap, has_alibi, off, impl, layout = ctx.cfg
         dq, dk, dv = dense_backward(q, k, v, o, lse, dout, scale, causal, wl, wr, softcap,
-                                    alibi if has_alibi else None, off, impl, layout)
-        return (dq, dk, dv) + (None,) * 9
+                                    alibi if has_alibi else None, off, impl, layout, feat=ctx.feat)
+        return (dq, dk, dv) + (None,) * 11
 
 
 def varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, softcap, alibi, impl,
-                   want_lse):
+                   want_lse, feat=None):
     Tq, Hq, D = q.shape
     Hkv = k.shape[1]
     batch = cu_q.numel() - 1
@@ -142,7 +197,7 @@ def varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, sof
     a = N.AttnArgs()
     _fill_common(a, q, k, v, o, _THD, _THD, batch=batch, sq=max_q, sk=max_k, hq=Hq, hkv=Hkv, d=D,
                  scale=scale, causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi,
-                 q_pos_offset=0, impl=impl, cu_q=cu_q, cu_k=cu_k)
+                 q_pos_offset=0, impl=impl, cu_q=cu_q, cu_k=cu_k, feat=feat)
     if lse is not None:
         a.lse2 = lse.data_ptr()
         a.lse_stride = N._I64x3(0, 1, Tq)
@@ -151,21 +206,44 @@ def varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, sof
     return o, lse, (q, k, v)
 
 
+def varlen_probs(q, k, v, lse, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, softcap, alibi, feat=None):
+    """(probabilities fp32 (batch, Hq, max_q, max_k) zero-padded, natural-log LSE (batch, Hq, max_q)
+    padded with -inf) of a packed call: flash_attn_interface.py:642-659 of the reference."""
+    Tq, Hq, D = q.shape
+    batch = cu_q.numel() - 1
+    probs = torch.zeros((batch, Hq, max_q, max_k), dtype=torch.float32, device=q.device)
+    lse_nat = torch.full((batch, Hq, max_q), float("-inf"), dtype=torch.float32, device=q.device)
+    a = N.AttnArgs()
+    _fill_common(a, q, k, v, q, _THD, _THD, batch=batch, sq=max_q, sk=max_k, hq=Hq, hkv=k.shape[1], d=D,
+                 scale=scale, causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi, q_pos_offset=0,
+                 impl=N.IMPL_AUTO, cu_q=cu_q, cu_k=cu_k, feat=feat)
+    a.lse2 = lse.data_ptr()
+    a.lse_stride = N._I64x3(0, 1, Tq)
+    ps = (C.c_int64 * 4)(*probs.stride())
+    with torch.cuda.device(q.device):
+        N.check(N.lib().fa_attn_probs(C.byref(a), probs.data_ptr(), C.byref(ps), lse_nat.data_ptr(), max_q,
+                                      N.stream_ptr(q.device)), "fa_attn_probs")
+    return probs, lse_nat
+
+
 def varlen_backward(q, k, v, o, lse, dout, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr,
-                    softcap, alibi, impl):
+                    softcap, alibi, impl, feat=None):
     Tq, Hq, D = q.shape
     Hkv = k.shape[1]
     batch = cu_q.numel() - 1
     dout = _prep(dout)
-    dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
-    # keys past cu_seqlens_k[-1] never get a writer; packed tensors are fully covered
-    dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-    dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+    # rows past cu_seqlens[-1] or past a sequence's used length never get a writer: start from zero
+    # when the packed tensors are not fully covered
+    partial = feat is not None and (feat.seqused_q is not None or feat.seqused_k is not None)
+    alloc = torch.zeros if partial else torch.empty
+    dq = alloc(q.shape, dtype=q.dtype, device=q.device)
+    dk = alloc(k.shape, dtype=k.dtype, device=k.device)
+    dv = alloc(v.shape, dtype=v.dtype, device=v.device)
     delta = torch.empty_like(lse)
     a = N.AttnArgs()
     _fill_common(a, q, k, v, o, _THD, _THD, batch=batch, sq=max_q, sk=max_k, hq=Hq, hkv=Hkv, d=D,
                  scale=scale, causal=causal, wl=wl, wr=wr, softcap=softcap, alibi=alibi,
-                 q_pos_offset=0, impl=impl, cu_q=cu_q, cu_k=cu_k)
+                 q_pos_offset=0, impl=impl, cu_q=cu_q, cu_k=cu_k, feat=feat)
     a.lse2 = lse.data_ptr()
     a.lse_stride = N._I64x3(0, 1, Tq)
     a.dout, a.do_stride = dout.data_ptr(), N.strides3(dout, _THD)
@@ -186,23 +264,28 @@ class VarlenAttention(torch.autograd.Function):
     """Packed q (Tq,Hq,D), k/v (Tk,Hkv,D) with int32 cu_seqlens on the device."""
 
     @staticmethod
-    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, softcap, alibi, impl):
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl, wr, softcap, alibi, impl, feat=None,
+                want_lse=False):
         need = any(t.requires_grad for t in (q, k, v))
         o, lse, (q, k, v) = varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, scale, causal, wl,
-                                           wr, softcap, alibi, impl, want_lse=need)
+                                           wr, softcap, alibi, impl, want_lse=need or want_lse, feat=feat)
         if need:
             ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k,
                                   alibi if alibi is not None else q.new_empty(0))
             ctx.cfg = (max_q, max_k, scale, causal, wl, wr, softcap, alibi is not None, impl)
+            ctx.feat = feat
+        if want_lse:
+            ctx.mark_non_differentiable(lse)
+            return o, lse
         return o
 
     @staticmethod
-    def backward(ctx, dout):
+    def backward(ctx, dout, *unused):
         q, k, v, o, lse, cu_q, cu_k, alibi = ctx.saved_tensors
         max_q, max_k, scale, causal, wl, wr, softcap, has_alibi, impl = ctx.cfg
         dq, dk, dv = varlen_backward(q, k, v, o, lse, dout, cu_q, cu_k, max_q, max_k, scale,
-                                     causal, wl, wr, softcap, alibi if has_alibi else None, impl)
-        return (dq, dk, dv) + (None,) * 11
+                                     causal, wl, wr, softcap, alibi if has_alibi else None, impl, feat=ctx.feat)
+        return (dq, dk, dv) + (None,) * 13
 
 
 # ----------------------------------------------------------------------------------------

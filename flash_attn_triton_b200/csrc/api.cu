@@ -99,6 +99,7 @@ unsigned int* work_queue(int device) {
 
 // kernel families (defined in the other translation units)
 int fwd_mma(const fa_attn_args&, const ScoreCfg&, cudaStream_t);
+int attn_probs(const fa_attn_args&, const ScoreCfg&, float*, const int64_t*, float*, int64_t, cudaStream_t);
 int bwd_preprocess(const fa_attn_args&, cudaStream_t);
 int bwd_dq_mma(const fa_attn_args&, const ScoreCfg&, cudaStream_t);
 int bwd_dkdv_mma(const fa_attn_args&, const ScoreCfg&, cudaStream_t);
@@ -123,6 +124,7 @@ int bwd_sm100_status();
 void fwd_sm100_clear_status();
 void bwd_sm100_clear_status();
 int wait_probe(int device, long long clocks, cudaStream_t st);
+int mma_peak_probe(int device, int kind, int iters, cudaStream_t st);
 
 static bool mult8(const int64_t* s, int n) {
   for (int i = 0; i < n; ++i)
@@ -141,6 +143,11 @@ static int validate_common(const fa_attn_args* a, bool need_cu) {
                  a->head_dim == 256,
              "head dimension must be one of 16, 32, 64, 128, or 256 (got %d)", a->head_dim);
   FA_REQUIRE(a->softcap >= 0.f, "softcap must be non-negative");
+  FA_REQUIRE(a->dropout_p >= 0.f && a->dropout_p < 1.f, "dropout_p must be in the range [0, 1)");
+  FA_REQUIRE(a->dropout_p == 0.f || a->dropout_row_stride > 0, "dropout needs dropout_row_stride > 0");
+  FA_REQUIRE(a->attn_bias == nullptr || a->cu_seqlens_q == nullptr, "attn_bias is for the dense layout only");
+  FA_REQUIRE((a->seqused_q == nullptr && a->seqused_k == nullptr) || a->cu_seqlens_q != nullptr,
+             "seqused_q/seqused_k need the packed layout");
   FA_REQUIRE((a->cu_seqlens_q == nullptr) == (a->cu_seqlens_k == nullptr),
              "cu_seqlens_q and cu_seqlens_k must be given together");
   if (need_cu) FA_REQUIRE(a->cu_seqlens_q != nullptr, "packed layout needs cu_seqlens_q/k");
@@ -169,9 +176,22 @@ static int validate_bwd(const fa_attn_args* a) {
 }
 
 static ScoreCfg cfg_of(const fa_attn_args* a) {
-  return make_score_cfg(a->softmax_scale, a->softcap, a->causal, a->window_left, a->window_right,
-                        a->alibi_slopes != nullptr);
+  ScoreCfg c = make_score_cfg(a->softmax_scale, a->softcap, a->causal, a->window_left, a->window_right,
+                              a->alibi_slopes != nullptr);
+  c.bias = a->attn_bias;
+  for (int i = 0; i < 4; ++i) c.bias_stride[i] = a->bias_stride[i];
+  if (a->dropout_p > 0.f) {
+    c.dropout_p = a->dropout_p;
+    c.dropout_scale = 1.f / (1.f - a->dropout_p);
+    c.seed_lo = (uint32_t)(a->dropout_seed & 0xffffffffull);
+    c.seed_hi = (uint32_t)(a->dropout_seed >> 32);
+    c.drop_stride = (uint32_t)a->dropout_row_stride;
+  }
+  return c;
 }
+
+// Bias and dropout are features of the mma.sync kernels.
+static bool needs_mma(const fa_attn_args* a) { return a->attn_bias != nullptr || a->dropout_p > 0.f; }
 
 // A bounded wait that ran out earlier on this device (host mirror of the status word): the tcgen05
 // kernels would return at their first wait, so the call is refused before anything is launched.
@@ -186,19 +206,19 @@ static int refuse_after_timeout(int device, const char* what) {
 
 static int fwd_impl(const fa_attn_args* a, void* stream, bool need_cu) {
   if (int r = validate_common(a, need_cu)) return r;
-  if (a->impl != FA_IMPL_MMA && fwd_sm100_supported(*a))
+  if (a->impl != FA_IMPL_MMA && fwd_sm100_supported(*a) && !needs_mma(a))
     if (int r = refuse_after_timeout(a->device, "fa_fwd")) return r;
   if (int r = ensure_device(a->device)) return r;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const ScoreCfg cfg = cfg_of(a);
   if (a->impl == FA_IMPL_TCGEN05) {
-    if (!fwd_sm100_supported(*a)) {
+    if (!fwd_sm100_supported(*a) || needs_mma(a)) {
       set_error("no tcgen05 forward kernel for this shape/feature set");
       return FA_ERR_UNSUPPORTED;
     }
     return fwd_sm100(*a, cfg, st);
   }
-  if (a->impl == FA_IMPL_AUTO && fwd_sm100_supported(*a)) return fwd_sm100(*a, cfg, st);
+  if (a->impl == FA_IMPL_AUTO && fwd_sm100_supported(*a) && !needs_mma(a)) return fwd_sm100(*a, cfg, st);
   return fwd_mma(*a, cfg, st);
 }
 
@@ -208,19 +228,19 @@ static int dq_impl(const fa_attn_args* a, void* stream, bool need_cu) {
   if (a->batch && a->seqlen_q) {
     FA_REQUIRE(a->dq && aligned16(a->dq) && mult8(a->dq_stride, 3), "dq pointer/alignment/stride");
   }
-  if (a->impl != FA_IMPL_MMA && bwd_sm100_supported(*a))
+  if (a->impl != FA_IMPL_MMA && bwd_sm100_supported(*a) && !needs_mma(a))
     if (int r = refuse_after_timeout(a->device, "fa_bwd_dq")) return r;
   if (int r = ensure_device(a->device)) return r;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const ScoreCfg cfg = cfg_of(a);
   if (a->impl == FA_IMPL_TCGEN05) {
-    if (!bwd_sm100_supported(*a)) {
+    if (!bwd_sm100_supported(*a) || needs_mma(a)) {
       set_error("no tcgen05 backward kernel for this shape/feature set");
       return FA_ERR_UNSUPPORTED;
     }
     return bwd_dq_sm100(*a, cfg, st);
   }
-  if (a->impl == FA_IMPL_AUTO && bwd_sm100_supported(*a)) return bwd_dq_sm100(*a, cfg, st);
+  if (a->impl == FA_IMPL_AUTO && bwd_sm100_supported(*a) && !needs_mma(a)) return bwd_dq_sm100(*a, cfg, st);
   return bwd_dq_mma(*a, cfg, st);
 }
 
@@ -232,19 +252,19 @@ static int dkdv_impl(const fa_attn_args* a, void* stream, bool need_cu) {
                    mult8(a->dv_stride, 3),
                "dk/dv pointer/alignment/stride");
   }
-  if (a->impl != FA_IMPL_MMA && bwd_sm100_supported(*a))
+  if (a->impl != FA_IMPL_MMA && bwd_sm100_supported(*a) && !needs_mma(a))
     if (int r = refuse_after_timeout(a->device, "fa_bwd_dkdv")) return r;
   if (int r = ensure_device(a->device)) return r;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const ScoreCfg cfg = cfg_of(a);
   if (a->impl == FA_IMPL_TCGEN05) {
-    if (!bwd_sm100_supported(*a)) {
+    if (!bwd_sm100_supported(*a) || needs_mma(a)) {
       set_error("no tcgen05 backward kernel for this shape/feature set");
       return FA_ERR_UNSUPPORTED;
     }
     return bwd_dkdv_sm100(*a, cfg, st);
   }
-  if (a->impl == FA_IMPL_AUTO && bwd_sm100_supported(*a)) return bwd_dkdv_sm100(*a, cfg, st);
+  if (a->impl == FA_IMPL_AUTO && bwd_sm100_supported(*a) && !needs_mma(a)) return bwd_dkdv_sm100(*a, cfg, st);
   return bwd_dkdv_mma(*a, cfg, st);
 }
 
@@ -256,6 +276,15 @@ extern "C" {
 
 int fa_fwd(const fa_attn_args* a, void* stream) { return fwd_impl(a, stream, false); }
 int fa_varlen_fwd(const fa_attn_args* a, void* stream) { return fwd_impl(a, stream, true); }
+
+int fa_attn_probs(const fa_attn_args* a, float* probs, const int64_t* probs_stride, float* lse_nat,
+                  int64_t lse_nat_stride, void* stream) {
+  if (int r = validate_common(a, false)) return r;
+  if (a->batch == 0 || a->seqlen_q == 0 || a->seqlen_k == 0) return FA_OK;
+  FA_REQUIRE(probs != nullptr && probs_stride != nullptr && a->lse2 != nullptr, "probs, probs_stride and lse2 are required");
+  if (int r = ensure_device(a->device)) return r;
+  return attn_probs(*a, cfg_of(a), probs, probs_stride, lse_nat, lse_nat_stride, reinterpret_cast<cudaStream_t>(stream));
+}
 
 int fa_bwd_preprocess(const fa_attn_args* a, void* stream) {
   if (int r = validate_common(a, false)) return r;
@@ -444,6 +473,13 @@ int fa_wait_probe(int32_t device, int64_t clocks, void* stream) {
   FA_REQUIRE(clocks > 0 && clocks <= 2000000000LL, "clocks must be in (0, 2e9]");
   if (int r = ensure_device(device)) return r;
   return wait_probe(device, clocks, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_mma_peak_probe(int32_t device, int32_t kind, int32_t iters, void* stream) {
+  FA_REQUIRE(kind == 0 || kind == 1, "kind: 0 = fp16 operands, 1 = int8 operands");
+  FA_REQUIRE(iters > 0 && iters <= (1 << 24), "iters must be in (0, 2^24]");
+  if (int r = ensure_device(device)) return r;
+  return mma_peak_probe(device, kind, iters, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int fa_debug_set_wait_status(int32_t device, int32_t code) {

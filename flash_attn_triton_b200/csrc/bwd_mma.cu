@@ -148,10 +148,16 @@ __global__ void __launch_bounds__(128) bwd_dq_mma_kernel(const fa_attn_args p, c
         const int i = e >> 1;
         const int row = r0 + i * 8;
         const int col = n * BN + nb * 8 + 2 * t + (e & 1);
+        const bool inside = row < si.q_len && col < si.k_len;
+        const float bias = (cfg.bias != nullptr && inside) ? bias_at(cfg, b, h, row, col) : 0.f;
         float th;
-        float sc = score_log2(cfg, slope, s[nb][e], row + off, col, th);
+        float sc = score_log2(cfg, slope, s[nb][e], row + off, col, th, bias);
         float pv = 0.f;
         if (visible(cfg, row + off, col, si.k_len) && lse[i] != -INFINITY) pv = exp2f(sc - lse[i]);
+        // dropout as the reference applies it in its backward (attention_kernel.py:750-762): the
+        // dropped-and-rescaled P multiplies (dP - delta)
+        if (cfg.dropout_p > 0.f)
+          pv = dropout_keep(cfg, (uint32_t)si.q_row0, row, col) ? pv * cfg.dropout_scale : 0.f;
         float ds = pv * (dp[nb][e] - dl[i]);
         if (cfg.softcap > 0.f) ds *= (1.f - th * th);
         s[nb][e] = ds;
@@ -318,11 +324,16 @@ __global__ void __launch_bounds__(128) bwd_dkdv_mma_kernel(const fa_attn_args p,
         const int qc = nb * 8 + 2 * t + (e & 1);  // query row inside the tile
         const int qrow = m * BM + qc;
         const float l2 = sLse[st * BM + qc];
+        const bool inside = qrow < si.q_len && key < si.k_len;
+        const float bias = (cfg.bias != nullptr && inside) ? bias_at(cfg, b, hq, qrow, key) : 0.f;
         float th;
-        float sc = score_log2(cfg, slope, s[nb][e], qrow + off, key, th);
+        float sc = score_log2(cfg, slope, s[nb][e], qrow + off, key, th, bias);
         float pv = 0.f;
         if (qrow < si.q_len && l2 != -INFINITY && visible(cfg, qrow + off, key, si.k_len))
           pv = exp2f(sc - l2);
+        // the same keep mask as in the forward (attention_kernel.py:641-652)
+        if (cfg.dropout_p > 0.f)
+          pv = dropout_keep(cfg, (uint32_t)si.q_row0, qrow, key) ? pv * cfg.dropout_scale : 0.f;
         float ds = pv * (dp[nb][e] - sDl[st * BM + qc]);
         if (cfg.softcap > 0.f) ds *= (1.f - th * th);
         s[nb][e] = pv;

@@ -52,6 +52,13 @@ struct ScoreCfg {
   int causal;
   int wl, wr;         // window; -1 = open
   int has_alibi;
+  // taken by the mma.sync kernels only
+  const float* bias;        // additive fp32 bias or null; element (b, h, row, col) through bias_stride
+  int64_t bias_stride[4];
+  float dropout_p;          // 0 = off
+  float dropout_scale;      // 1 / (1 - p)
+  uint32_t seed_lo, seed_hi;
+  uint32_t drop_stride;     // counter of element (row, col) = (row0 + row) * drop_stride + col
 };
 
 __host__ __device__ inline ScoreCfg make_score_cfg(float scale, float softcap, int causal, int wl,
@@ -65,7 +72,45 @@ __host__ __device__ inline ScoreCfg make_score_cfg(float scale, float softcap, i
   c.wl = wl;
   c.wr = wr;
   c.has_alibi = alibi ? 1 : 0;
+  c.bias = nullptr;
+  c.bias_stride[0] = c.bias_stride[1] = c.bias_stride[2] = c.bias_stride[3] = 0;
+  c.dropout_p = 0.f;
+  c.dropout_scale = 1.f;
+  c.seed_lo = c.seed_hi = c.drop_stride = 0u;
   return c;
+}
+
+// Philox4x32-10 (Salmon et al.) with key (k0, k1) and counter (c0, 0, 0, 0); first output word.
+// This is the generator behind the reference's tl.rand(seed, offset): key = the 64-bit seed,
+// c0 = the element's offset.
+__host__ __device__ inline uint32_t philox_first(uint32_t c0, uint32_t k0, uint32_t k1) {
+  uint32_t c1 = 0u, c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t pa = (uint64_t)0xD2511F53u * c0, pb = (uint64_t)0xCD9E8D57u * c2;
+    c0 = (uint32_t)(pb >> 32) ^ c1 ^ k0;
+    c2 = (uint32_t)(pa >> 32) ^ c3 ^ k1;
+    c1 = (uint32_t)pb;
+    c3 = (uint32_t)pa;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+// The 32 random bits as a float in [0, 1): the signed value folded to non-negative, times 2^-31.
+__host__ __device__ inline float uniform_from_bits(uint32_t bits) {
+  int32_t x = (int32_t)bits;
+  if (x < 0) x = -x - 1;
+  return (float)x * 4.6566127342e-10f;
+}
+// Dropout keep test of element (row, col) of a sequence whose first packed row is row0.
+__device__ __forceinline__ bool dropout_keep(const ScoreCfg& c, uint32_t row0, int row, int col) {
+  const uint32_t offset = (row0 + (uint32_t)row) * c.drop_stride + (uint32_t)col;
+  return uniform_from_bits(philox_first(offset, c.seed_lo, c.seed_hi)) > c.dropout_p;
+}
+__device__ __forceinline__ float bias_at(const ScoreCfg& c, int b, int h, int row, int col) {
+  return c.bias[(int64_t)b * c.bias_stride[0] + (int64_t)h * c.bias_stride[1] + (int64_t)row * c.bias_stride[2] +
+                (int64_t)col * c.bias_stride[3]];
 }
 
 // ex2.approx without the denormal handling exp2f() adds
@@ -147,11 +192,12 @@ __device__ __forceinline__ float fast_tanh(float x) {
 // conversion per tile instead of one per element).  `th` returns tanh(s/softcap) when softcap
 // is on (needed by the backward), else 0.
 __device__ __forceinline__ float score_log2_dist(const ScoreCfg& c, float slope, float dot, float dist,
-                                                 float& th) {
+                                                 float& th, float bias = 0.f) {
   th = 0.f;
-  if (!c.has_alibi && c.softcap == 0.f) return dot * c.scale_log2;
+  if (!c.has_alibi && c.softcap == 0.f && c.bias == nullptr) return dot * c.scale_log2;
   float s = dot * c.scale;
   if (c.has_alibi) s = fmaf(-slope, fabsf(dist), s);
+  s += bias;                                   // after ALiBi, before the soft cap
   if (c.softcap > 0.f) {
     th = fast_tanh(s * c.inv_softcap);
     s = c.softcap * th;
@@ -171,8 +217,8 @@ __device__ __forceinline__ float score_log2_feat(const ScoreCfg& c, float slope,
   return s * FA_LOG2E;
 }
 __device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
-                                            int kpos, float& th) {
-  return score_log2_dist(c, slope, dot, (float)(qpos - kpos), th);
+                                            int kpos, float& th, float bias = 0.f) {
+  return score_log2_dist(c, slope, dot, (float)(qpos - kpos), th, bias);
 }
 
 __device__ __forceinline__ bool visible(const ScoreCfg& c, int qpos, int kpos, int k_len) {
@@ -387,6 +433,8 @@ __device__ __forceinline__ SeqInfo seq_info(const fa_attn_args& p, int b) {
     s.q_boff = b;
     s.k_boff = b;
   }
+  if (p.seqused_q) s.q_len = max(0, min(s.q_len, p.seqused_q[b]));
+  if (p.seqused_k) s.k_len = max(0, min(s.k_len, p.seqused_k[b]));
   return s;
 }
 

@@ -811,6 +811,68 @@ __global__ void wait_probe_kernel(long long clocks, int* host_status) {
   if (threadIdx.x == 0) report_abort(abort_flag, host_status);
 }
 
+// Rate of the tensor pipe as this library drives it: every CTA (one per SM) issues `iters`
+// back-to-back tcgen05.mma of shape M128 N128 (K16 fp16 or K32 int8) on operand tiles that sit
+// in shared memory, into four accumulators in turn.  The host times the launch; the result is the
+// denominator for kernels that mix int8 and fp16 GEMMs (cuBLAS only gives the bf16 figure).
+template <bool kInt8>
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  __shared__ uint64_t done;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // operand tiles: 128 rows of 128 bytes each (A and B), filled with small pseudo-random values
+  for (int i = tid; i < 2 * 128 * 128 / 4; i += 128) {
+    uint32_t x = (uint32_t)i * 2654435761u + blockIdx.x;
+    reinterpret_cast<uint32_t*>(tiles)[i] = kInt8 ? (x & 0x0f0f0f0fu) : (0x2c002c00u | (x & 0x03ff03ffu));
+  }
+  if (tid == 0) {
+    mbar_init(smem_u32(&done), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  fence_proxy_async();
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base;
+  if (warp == 1) {
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    const uint32_t sA = smem_u32(tiles), sB = sA + 128 * 128;
+    const uint64_t da = make_smem_desc(sA, 16, 1024), db = make_smem_desc(sB, 16, 1024);
+    constexpr uint32_t idesc = kInt8 ? make_idesc(2, 1, 0, 0, 128, 128) : make_idesc(1, 0, 0, 0, 128, 128);
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t o = (uint32_t)((it & 3) * 32) >> 4;            // the four K steps of a 128-byte row
+      if (kInt8) {
+        if (leader) mma_i8_ss(tmem + ((it >> 2) & 3) * 128, da + o, db + o, idesc, 1u);
+        __syncwarp();
+      } else {
+        mma_f16_ss_lp(tmem + ((it >> 2) & 3) * 128, da + o, db + o, idesc, 1u, leader);
+      }
+    }
+    mma_commit_lp(smem_u32(&done), leader);
+    bounded_wait(&done, 0, &abort_flag, &g_fwd_sm100_status, 98);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+int mma_peak_probe(int device, int kind, int iters, cudaStream_t st) {
+  const int smem = 2 * 128 * 128 + 1024;
+  const int grid = sm_count(device);
+  if (kind == 1) mma_peak_kernel<true><<<grid, 128, smem, st>>>(iters);
+  else mma_peak_kernel<false><<<grid, 128, smem, st>>>(iters);
+  return check_launch("mma_peak_probe");
+}
+
 int wait_probe(int device, long long clocks, cudaStream_t st) {
   wait_probe_kernel<<<1, 32, 0, st>>>(clocks, host_wait_word(device));
   return check_launch("wait_probe");

@@ -10,14 +10,20 @@ What is different underneath (results are the same within fp16 tolerance):
 * bf16 is accepted as well as fp16;
 * `use_native_gqa` and `deterministic` are accepted and change nothing: GQA is always native
   and the backward always has a single writer per element.
-The eager "materialise the probabilities" paths (`return_attn_probs`, `attn_bias`) are kept
-as torch code like the reference's (:15-49, :139-148); fp32 inputs and `dropout_p > 0` use
-that path too.
+* `return_attn_probs`, `attn_bias`, `dropout_p`, `seqused_q/k` and paged packed K/V run on the
+  kernels too (the reference materialises them in torch, :15-49, :139-148, :533-581, :642-659):
+  the probabilities come from a kernel of their own, the bias and the dropout mask (the
+  reference's Philox stream, attention_kernel.py:345-358) are applied inside the mma.sync
+  kernels, the length overrides are read by every kernel, pages are gathered by a row mover;
+* fp32 tensors are computed with fp16 operands and fp32 accumulation (the precision of the
+  TF32 products the reference's fp32 path uses) and returned as fp32; values beyond the fp16
+  range are not supported there.
 """
 from __future__ import annotations
 
 import math
 import os
+import random
 
 import torch
 
@@ -38,40 +44,49 @@ _KERNEL_DTYPES = (torch.float16, torch.bfloat16)
 _ALL_DTYPES = (torch.float16, torch.bfloat16, torch.float32)
 
 
-def _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
-                          alibi_slopes, attn_bias=None, causal_offset=0):
-    """Eager path that materialises the probabilities (reference: flash_attn_interface.py:15-49).
-    Returns (out, natural-log lse, probs)."""
-    batch, q_len, q_heads, head_dim = q.shape
-    k_len, kv_heads = k.shape[1], k.shape[2]
-    if q_heads != kv_heads:
-        k = k.repeat_interleave(q_heads // kv_heads, dim=2)
-        v = v.repeat_interleave(q_heads // kv_heads, dim=2)
-    scale = 1.0 / math.sqrt(head_dim) if softmax_scale is None else softmax_scale
-    scores = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
-    q_pos = torch.arange(q_len, device=q.device) + causal_offset
-    k_pos = torch.arange(k_len, device=q.device)
-    keep = torch.ones((q_len, k_len), dtype=torch.bool, device=q.device)
-    if causal:
-        keep &= q_pos[:, None] >= k_pos[None, :]
-    if window_size[0] >= 0:
-        keep &= k_pos[None, :] >= q_pos[:, None] - window_size[0]
-    if window_size[1] >= 0:
-        keep &= k_pos[None, :] <= q_pos[:, None] + window_size[1]
-    if alibi_slopes is not None:
-        slopes = alibi_slopes if alibi_slopes.ndim == 2 else alibi_slopes[None, :]
-        scores = scores - slopes[:, :, None, None] * (q_pos[:, None] - k_pos[None, :]).abs()
+def _as_kernel_dtype(*tensors):
+    """fp32 tensors are computed at fp16 operand precision (see the module docstring)."""
+    if tensors[0].dtype == torch.float32:
+        return tuple(t.to(torch.float16) for t in tensors)
+    return tensors
+
+
+def _dense_features(q, k, dropout_p, attn_bias):
+    """Bias and dropout settings of a dense call, or None when neither is used."""
+    if attn_bias is None and not dropout_p:
+        return None
+    bias = None
     if attn_bias is not None:
-        scores = scores + attn_bias
-    if softcap > 0:
-        scores = softcap * torch.tanh(scores / softcap)
-    scores = scores.float().masked_fill(~keep[None, None], float("-inf"))
-    probs = torch.nan_to_num(torch.softmax(scores, dim=-1))
-    lse = torch.logsumexp(scores, dim=-1)
+        if attn_bias.requires_grad:
+            raise ValueError("attn_bias gradients are not produced; pass a tensor that does not require grad")
+        B, Sq, Hq = q.shape[0], q.shape[1], q.shape[2]
+        bias = attn_bias.detach().to(device=q.device, dtype=torch.float32)
+        try:
+            bias = bias.expand(B, Hq, Sq, k.shape[1])          # broadcast dimensions get stride 0
+        except RuntimeError:
+            raise ValueError("attn_bias must be broadcastable to (batch, nheads, seqlen_q, seqlen_k)")
+    seed = row_stride = 0
     if dropout_p:
-        probs = torch.nn.functional.dropout(probs, p=dropout_p, training=True)
-    out = torch.einsum("bhqk,bkhd->bqhd", probs.to(q.dtype), v)
-    return out, lse, probs
+        # one seed per call (attention_kernel.py:1238-1239); the counter of element (row, col) uses the
+        # sequence length the reference pads to: the next multiple of 64 of the longer side (:168-184, :300-307)
+        seed = random.randrange(2 ** 31 - 1)
+        row_stride = (max(q.shape[1], k.shape[1]) + 63) // 64 * 64
+    return _ops.Features(bias=bias, dropout_p=dropout_p, seed=seed, row_stride=row_stride)
+
+
+def _dense_call(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes, attn_bias,
+                return_attn_probs, q_pos_offset):
+    out_dtype = q.dtype
+    q, k, v = _as_kernel_dtype(q, k, v)
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    feat = _dense_features(q, k, dropout_p, attn_bias)
+    args = (softmax_scale, causal, window_size[0], window_size[1], softcap, alibi_slopes, int(q_pos_offset))
+    if not return_attn_probs:
+        return _ops.DenseAttention.apply(q, k, v, *args, N.IMPL_AUTO, "bshd", feat).to(out_dtype)
+    out, lse2 = _ops.DenseAttention.apply(q, k, v, *args, N.IMPL_AUTO, "bshd", feat, True)
+    probs, lse = _ops.dense_probs(q.detach(), k.detach(), v.detach(), lse2, *args, "bshd", feat)
+    return out.to(out_dtype), lse, probs
 
 
 def _normalise_alibi(alibi_slopes, batch, heads, device):
@@ -131,17 +146,9 @@ def flash_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
         )
     alibi_slopes = _normalise_alibi(alibi_slopes, batch_size, n_heads_q, q.device)
 
-    if return_attn_probs:
-        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
-                                     softcap, alibi_slopes, attn_bias)
-    if attn_bias is not None or dropout_p > 0.0 or q.dtype == torch.float32:
-        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
-                                     softcap, alibi_slopes, attn_bias)[0].to(q.dtype)
     _check_head_dim(head_dim)
-    if softmax_scale is None:
-        softmax_scale = 1.0 / math.sqrt(head_dim)
-    return _ops.DenseAttention.apply(q, k, v, softmax_scale, causal, window_size[0],
-                                     window_size[1], softcap, alibi_slopes, 0, N.IMPL_AUTO, "bshd")
+    return _dense_call(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes,
+                       attn_bias, return_attn_probs, 0)
 
 
 def flash_attn_func_cross(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
@@ -170,18 +177,8 @@ def flash_attn_func_cross(q, k, v, dropout_p=0.0, softmax_scale=None, causal=Fal
     if softcap < 0.0:
         raise ValueError("softcap must be non-negative")
     alibi_slopes = _normalise_alibi(alibi_slopes, q.shape[0], q.shape[2], q.device)
-    if return_attn_probs:
-        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
-                                     softcap, alibi_slopes, attn_bias, causal_offset=_causal_offset)
-    if attn_bias is not None or dropout_p > 0.0 or q.dtype == torch.float32:
-        return _attention_with_probs(q, k, v, dropout_p, softmax_scale, causal, window_size,
-                                     softcap, alibi_slopes, attn_bias,
-                                     causal_offset=_causal_offset)[0].to(q.dtype)
-    if softmax_scale is None:
-        softmax_scale = 1.0 / math.sqrt(q.shape[-1])
-    return _ops.DenseAttention.apply(q, k, v, softmax_scale, causal, window_size[0],
-                                     window_size[1], softcap, alibi_slopes, int(_causal_offset),
-                                     N.IMPL_AUTO, "bshd")
+    return _dense_call(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap, alibi_slopes,
+                       attn_bias, return_attn_probs, _causal_offset)
 
 
 def flash_attn_qkvpacked_func(qkv, dropout_p=0.0, softmax_scale=None, causal=False,
@@ -348,52 +345,26 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     """Attention over packed variable-length sequences (flash_attn_interface.py:527-690):
     q (total_q, nheads, d), k/v (total_k, nheads_k, d), int32 cu_seqlens on the device.
     Each sequence is masked with upper-left alignment."""
-    if block_table is not None:
-        if k.ndim != 4 or v.ndim != 4 or k.shape != v.shape:
-            raise ValueError("paged varlen k and v must have shape (pages, page_size, heads, dim)")
-        if block_table.ndim != 2 or block_table.shape[0] != cu_seqlens_k.numel() - 1:
-            raise ValueError("block_table must have shape (batch, max_num_pages)")
-        page_size = k.shape[1]
-        bounds = cu_seqlens_k.tolist()
-        page_parts, value_parts = [], []
-        for b in range(block_table.shape[0]):
-            length = bounds[b + 1] - bounds[b]
-            page_ids = block_table[b, :(length + page_size - 1) // page_size].to(torch.long)
-            if torch.any(page_ids < 0) or torch.any(page_ids >= k.shape[0]):
-                raise ValueError("block_table contains an invalid physical page index")
-            page_parts.append(k[page_ids].reshape(-1, k.shape[2], k.shape[3])[:length])
-            value_parts.append(v[page_ids].reshape(-1, v.shape[2], v.shape[3])[:length])
-        k = torch.cat(page_parts, dim=0) if page_parts else k.new_empty((0, k.shape[2], k.shape[3]))
-        v = torch.cat(value_parts, dim=0) if value_parts else v.new_empty((0, v.shape[2], v.shape[3]))
     batch_size = cu_seqlens_q.numel() - 1
+    paged = block_table is not None
+    if paged:
+        k, v = _gather_pages(k, v, block_table, cu_seqlens_k, max_seqlen_k)
+    used_q = used_k = None
     if seqused_q is not None:
-        used = torch.as_tensor(seqused_q).to(torch.int64).flatten().tolist()
-        if len(used) != batch_size:
+        used_q = torch.as_tensor(seqused_q, device=q.device).to(torch.int32).flatten().contiguous()
+        if used_q.numel() != batch_size:
             raise ValueError("seqused_q must contain one value per sequence")
-        bounds = cu_seqlens_q.tolist()
-        parts = []
-        for b in range(batch_size):
-            if used[b] < 0 or used[b] > bounds[b + 1] - bounds[b]:
-                raise ValueError("seqused_q exceeds the packed query sequence")
-            parts.append(q[bounds[b]:bounds[b] + used[b]])
-        q = torch.cat(parts, dim=0) if parts else q[:0]
-        cu_seqlens_q = torch.tensor([0] + torch.tensor(used).cumsum(0).tolist(), device=q.device,
-                                    dtype=torch.int32)
     if seqused_k is not None:
-        used = torch.as_tensor(seqused_k).to(torch.int64).flatten().tolist()
-        if len(used) != batch_size:
+        used_k = torch.as_tensor(seqused_k, device=q.device).to(torch.int32).flatten().contiguous()
+        if used_k.numel() != batch_size:
             raise ValueError("seqused_k must contain one value per sequence")
-        bounds = cu_seqlens_k.tolist()
-        kp, vp = [], []
-        for b in range(batch_size):
-            if used[b] < 0 or used[b] > bounds[b + 1] - bounds[b]:
-                raise ValueError("seqused_k exceeds the packed KV sequence")
-            kp.append(k[bounds[b]:bounds[b] + used[b]])
-            vp.append(v[bounds[b]:bounds[b] + used[b]])
-        k = torch.cat(kp, dim=0) if kp else k[:0]
-        v = torch.cat(vp, dim=0) if vp else v[:0]
-        cu_seqlens_k = torch.tensor([0] + torch.tensor(used).cumsum(0).tolist(), device=k.device,
-                                    dtype=torch.int32)
+    if _VALIDATE and (used_q is not None or used_k is not None):
+        lq = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).to(q.device)
+        lk = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).to(q.device)
+        if used_q is not None and bool(torch.any((used_q < 0) | (used_q > lq))):
+            raise ValueError("seqused_q exceeds the packed query sequence")
+        if used_k is not None and bool(torch.any((used_k < 0) | (used_k > lk))):
+            raise ValueError("seqused_k exceeds the packed KV sequence")
     if q.ndim != 3 or k.ndim != 3 or v.ndim != 3 or k.shape != v.shape:
         raise ValueError("packed q, k, and v must be rank-3 tensors with matching KV shapes")
     if cu_seqlens_q.ndim != 1 or cu_seqlens_k.ndim != 1:
@@ -430,7 +401,8 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
             raise ValueError("cu_seqlens arrays must start at zero and contain a batch boundary")
         if any(b < a for a, b in zip(cq, cq[1:])) or any(b < a for a, b in zip(ck, ck[1:])):
             raise ValueError("cu_seqlens arrays must be monotonically non-decreasing")
-        if cq[-1] != q.shape[0] or ck[-1] != k.shape[0]:
+        # gathered pages are sized by batch * max_seqlen_k, an upper bound of cu_seqlens_k[-1]
+        if cq[-1] != q.shape[0] or (ck[-1] > k.shape[0] if paged else ck[-1] != k.shape[0]):
             raise ValueError("cu_seqlens arrays must cover the packed q and KV tensors")
         if max_seqlen_q < max(b - a for a, b in zip(cq, cq[1:])) or \
                 max_seqlen_k < max(b - a for a, b in zip(ck, ck[1:])):
@@ -438,29 +410,80 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     if max_seqlen_q == 0 or max_seqlen_k == 0:
         return q.new_zeros((q.shape[0], q.shape[1], q.shape[2]))
     alibi = _normalise_alibi(alibi_slopes, batch_size, q.shape[1], q.device)
-    eager = return_attn_probs or dropout_p > 0.0 or q.dtype == torch.float32
-    if eager:
-        cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
-        outputs = []
-        lses = q.new_full((batch_size, q.shape[1], max_seqlen_q), float("-inf"), dtype=torch.float32)
-        probabilities = q.new_zeros((batch_size, q.shape[1], max_seqlen_q, max_seqlen_k),
-                                    dtype=torch.float32) if return_attn_probs else None
-        for b in range(batch_size):
-            out, lse, probs = _attention_with_probs(
-                q[cq[b]:cq[b + 1]].unsqueeze(0), k[ck[b]:ck[b + 1]].unsqueeze(0),
-                v[ck[b]:ck[b + 1]].unsqueeze(0), dropout_p, softmax_scale, causal, window_size,
-                softcap, None if alibi is None else alibi[b:b + 1])
-            outputs.append(out.squeeze(0))
-            if return_attn_probs:
-                lses[b, :, :cq[b + 1] - cq[b]] = lse[0]
-                probabilities[b, :, :cq[b + 1] - cq[b], :ck[b + 1] - ck[b]] = probs[0]
-        out = torch.cat(outputs, dim=0).to(q.dtype)
-        return (out, lses, probabilities) if return_attn_probs else out
+    out_dtype = q.dtype
+    q, k, v = _as_kernel_dtype(q, k, v)
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
-    return _ops.VarlenAttention.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q),
-                                      int(max_seqlen_k), softmax_scale, causal, window_size[0],
-                                      window_size[1], softcap, alibi, N.IMPL_AUTO)
+    if dropout_p and used_q is not None:
+        # The reference packs the used query rows before it launches (:552-566), so its dropout
+        # counters run over the packed rows.  Do the same here, for this combination only.
+        q = _compact_rows(q, cu_seqlens_q, used_q)
+        cu_seqlens_q = torch.cat([used_q.new_zeros(1), torch.cumsum(used_q, 0, dtype=torch.int32)])
+        used_q = None
+        compacted = True
+    else:
+        compacted = False
+    feat = None
+    if dropout_p or used_q is not None or used_k is not None:
+        # dropout counters follow the reference: (first packed row of the sequence + row) * max_seqlen_k + col
+        # (attention_kernel.py:91-93)
+        feat = _ops.Features(dropout_p=dropout_p, seed=random.randrange(2 ** 31 - 1) if dropout_p else 0,
+                             row_stride=int(max_seqlen_k), seqused_q=used_q, seqused_k=used_k)
+    args = (cu_seqlens_q, cu_seqlens_k, int(max_seqlen_q), int(max_seqlen_k), softmax_scale, causal,
+            window_size[0], window_size[1], softcap, alibi)
+    if return_attn_probs:
+        out, lse2 = _ops.VarlenAttention.apply(q, k, v, *args, N.IMPL_AUTO, feat, True)
+        probs, lse = _ops.varlen_probs(q.detach(), k.detach(), v.detach(), lse2, *args, feat)
+    else:
+        out = _ops.VarlenAttention.apply(q, k, v, *args, N.IMPL_AUTO, feat)
+    if used_q is not None and not compacted:
+        # the reference returns only the used rows, packed (flash_attn_interface.py:552-566); the one
+        # host read of the lengths sizes that result
+        out = _compact_rows(out, cu_seqlens_q, used_q)
+    out = out.to(out_dtype)
+    return (out, lse, probs) if return_attn_probs else out
+
+
+def _compact_rows(x, cu_seqlens, used):
+    """Rows [cu[b], cu[b] + used[b]) of every sequence b, concatenated (differentiable gather)."""
+    from .compat.bert_padding import index_first_axis
+    used64 = used.to(torch.int64)
+    total = int(used64.sum().item())
+    starts_out = torch.cumsum(used64, 0) - used64
+    seq = torch.repeat_interleave(torch.arange(used.numel(), device=x.device), used64, output_size=total)
+    idx = cu_seqlens[:-1].to(torch.int64)[seq] + (torch.arange(total, device=x.device) - starts_out[seq])
+    if total == 0:
+        return x[:0]
+    return index_first_axis(x, idx)
+
+
+def _gather_pages(k, v, block_table, cu_seqlens_k, max_seqlen_k):
+    """Paged K/V (pages, page_size, heads, dim) + block_table (batch, max_pages) -> packed
+    (rows, heads, dim) tensors laid out by cu_seqlens_k, with a row mover on the device and no
+    host read (flash_attn_interface.py:533-550 loops over the batch in Python).  The packed
+    tensors get batch * max_seqlen_k rows, an upper bound of cu_seqlens_k[-1]; rows past it are
+    zero and never read."""
+    from .compat.bert_padding import index_first_axis
+    if k.ndim != 4 or v.ndim != 4 or k.shape != v.shape:
+        raise ValueError("paged varlen k and v must have shape (pages, page_size, heads, dim)")
+    batch = cu_seqlens_k.numel() - 1
+    if block_table.ndim != 2 or block_table.shape[0] != batch:
+        raise ValueError("block_table must have shape (batch, max_num_pages)")
+    if max_seqlen_k < 0:
+        raise ValueError("max sequence lengths must be non-negative")
+    page_size = k.shape[1]
+    dev = k.device
+    if _VALIDATE and bool(torch.any(block_table < 0) | torch.any(block_table >= k.shape[0])):
+        raise ValueError("block_table contains an invalid physical page index")
+    cu = cu_seqlens_k.to(device=dev, dtype=torch.int64)
+    rows = batch * int(max_seqlen_k)
+    t = torch.arange(rows, device=dev)
+    seq = torch.searchsorted(cu[1:].contiguous(), t, right=True).clamp_(max=batch - 1)
+    pos = t - cu[seq]
+    page = block_table.to(device=dev, dtype=torch.int64)[seq, (pos // page_size).clamp_(0, block_table.shape[1] - 1)]
+    idx = torch.where(t < cu[-1], page * page_size + pos % page_size, torch.full_like(t, -1))
+    flat = lambda x: x.reshape(-1, x.shape[2], x.shape[3])
+    return index_first_axis(flat(k), idx), index_first_axis(flat(v), idx)
 
 
 def flash_attn_varlen_kvpacked_func(q, kv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,

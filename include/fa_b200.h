@@ -93,6 +93,29 @@ typedef struct fa_attn_args {
   void* dk;
   void* dv;
   int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+
+  /* Per-sequence length overrides of a packed batch (flash_attn_interface.py:552-581): sequence b
+   * uses only its first seqused_q[b] query rows / seqused_k[b] keys.  NULL = use all.  Rows past
+   * the used length are neither read nor written. */
+  const int32_t* seqused_q;
+  const int32_t* seqused_k;
+
+  /* Additive score bias, fp32, element (b, h, row, col) at attn_bias[b*s0 + h*s1 + row*s2 + col*s3]
+   * (a stride of 0 broadcasts); added after ALiBi, before the soft cap
+   * (flash_attn_interface.py:39-40).  Dense layout only; no gradient is produced for it.  NULL = none.
+   * Taken by the mma.sync kernels. */
+  const float* attn_bias;
+  int64_t bias_stride[4];
+
+  /* Dropout on the probabilities with the reference's random stream (attention_kernel.py:345-358,
+   * :91-93): element (row, col) is kept when philox4x32-10(key = dropout_seed, counter =
+   * (row0 + row) * dropout_row_stride + col) mapped to [0, 1) exceeds dropout_p; kept
+   * probabilities are scaled by 1 / (1 - p); row0 = cu_seqlens_q[b] in the packed layout, else 0.
+   * The same mask for every batch entry and head, as in the reference.  0 = off.
+   * Taken by the mma.sync kernels. */
+  float dropout_p;
+  int32_t dropout_row_stride;
+  uint64_t dropout_seed;
 } fa_attn_args;
 
 /* Forward: o and (optionally) lse2.
@@ -114,6 +137,17 @@ int fa_bwd_dq(const fa_attn_args* args, void* stream);
  * Replaces the dK/dV half of _attn_bwd (attention_kernel.py:567-673, :873-962) and
  * _varlen_bwd_dkdv (attention_kernel.py:188-272). */
 int fa_bwd_dkdv(const fa_attn_args* args, void* stream);
+
+/*
+ * Attention probabilities as a matrix (the `return_attn_probs` surface,
+ * flash_attn_interface.py:139-143, :642-659): probs[b, h, i, j] = exp2(score_log2(i, j) - lse2[i])
+ * with the score pipeline, mask and dropout of `args`, for i < q_len(b), j < k_len(b); other
+ * elements are left untouched (zero-fill the buffer first).  lse2 is the forward's.  When
+ * lse_nat is non-NULL the natural-log LSE of row i goes to lse_nat[(b*heads_q + h)*lse_nat_stride + i].
+ * probs_stride: element strides of (batch, head, row, col).
+ */
+int fa_attn_probs(const fa_attn_args* args, float* probs, const int64_t* probs_stride, float* lse_nat,
+                  int64_t lse_nat_stride, void* stream);
 
 /* Same three operations, but cu_seqlens_q/k are mandatory (the packed layout). */
 int fa_varlen_fwd(const fa_attn_args* args, void* stream);
@@ -304,6 +338,11 @@ int fa_device_wait_status(int device);
 int fa_device_wait_clear(int device);
 int fa_wait_probe(int32_t device, int64_t clocks, void* stream);
 int fa_debug_set_wait_status(int32_t device, int32_t code);
+/* Measurement aid: one CTA per SM issues `iters` back-to-back tcgen05.mma (M128 N128; K16 with fp16
+ * operands for kind 0, K32 with int8 operands for kind 1) from shared memory into tensor memory.
+ * Timed by the caller, it gives the tensor-pipe rate this library's own issue path reaches
+ * (2*128*128*K*iters*SMs FLOP per launch): the int8 denominator for the INT8 forward. */
+int fa_mma_peak_probe(int32_t device, int32_t kind, int32_t iters, void* stream);
 /* sizeof of an argument block as this library was compiled: 0 = fa_attn_args,
  * 1 = fa_decode_args, 2 = fa_int8_args.  Lets a foreign-language binding check its
  * struct layout before the first call.  3 = fa_rotary_args. */

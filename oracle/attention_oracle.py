@@ -100,6 +100,80 @@ def attention_ref(q, k, v, softmax_scale=None, causal=False, window=(-1, -1), so
     return out, lse
 
 
+# ----------------------------------------------------------------------------------------
+# dropout with the reference's random stream (attention_kernel.py:345-358, :91-93, :641-652, :749-762)
+# ----------------------------------------------------------------------------------------
+def philox_uniform(seed, offsets):
+    """tl.rand(seed, offset) restated: Philox4x32-10 with key = the 64-bit seed and counter
+    (offset, 0, 0, 0); the first output word, read as a signed int, folded to non-negative
+    (x < 0 -> -x - 1) and scaled by 2^-31.  offsets: integer array (wraps to 32 bits)."""
+    c0 = np.asarray(offsets).astype(np.uint64) & np.uint64(0xFFFFFFFF)
+    c1 = np.zeros_like(c0)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0 = np.uint64(int(seed) & 0xFFFFFFFF)
+    k1 = np.uint64((int(seed) >> 32) & 0xFFFFFFFF)
+    A, B_, M = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        pa, pb = A * c0, B_ * c2                      # 32 x 32 -> 64 bit products
+        c0, c2, c1, c3 = (pb >> np.uint64(32)) ^ c1 ^ k0, (pa >> np.uint64(32)) ^ c3 ^ k1, pb & M, pa & M
+        k0 = (k0 + np.uint64(0x9E3779B9)) & M
+        k1 = (k1 + np.uint64(0xBB67AE85)) & M
+    x = c0.astype(np.uint32).view(np.int32).astype(np.int64)
+    x = np.where(x < 0, -x - 1, x)
+    return (x.astype(np.float32) * np.float32(4.6566127342e-10)).astype(np.float32)
+
+
+def dropout_keep_ref(q_len, k_len, p, seed, row_stride, row0=0):
+    """Keep mask (q_len, k_len): element (i, j) is kept when the uniform drawn at counter
+    (row0 + i) * row_stride + j exceeds p.  Dense calls use row0 = 0 and row_stride = the longer
+    sequence length rounded up to 64 (the length the reference pads to); packed calls use
+    row0 = cu_seqlens_q[b] and row_stride = max_seqlen_k."""
+    off = (np.arange(q_len, dtype=np.int64)[:, None] + row0) * row_stride + np.arange(k_len, dtype=np.int64)[None, :]
+    return torch.from_numpy(philox_uniform(seed, off) > np.float32(p))
+
+
+def attention_dropout_ref(q, k, v, dout=None, dropout_p=0.0, seed=0, row_stride=None, row0=0, **kw):
+    """Dense attention with dropout, forward and (when dout is given) the gradients AS THE
+    REFERENCE'S KERNELS COMPUTE THEM: P is normalised before the mask is applied, kept entries are
+    scaled by 1/(1-p), and the backward multiplies (dP - delta) by the dropped-and-rescaled P
+    (attention_kernel.py:652-664, :760-762) -- not the exact derivative, whose delta term uses
+    the undropped P.  Returns (out, lse, probs_after_dropout[, dq, dk, dv]); layouts as attention_ref."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(D) if kw.get("softmax_scale") is None else kw["softmax_scale"]
+    softcap = kw.get("softcap", 0.0)
+    s = scores_ref(q, k, kw.get("softmax_scale"), kw.get("causal", False), kw.get("window", (-1, -1)), softcap,
+                   kw.get("alibi_slopes"), kw.get("attn_bias"), kw.get("q_pos_offset", 0))
+    probs = torch.nan_to_num(torch.softmax(s, dim=-1))
+    lse = torch.logsumexp(s, dim=-1)
+    if dropout_p > 0:
+        if row_stride is None:
+            row_stride = (max(Sq, Sk) + 63) // 64 * 64
+        keep = dropout_keep_ref(Sq, Sk, dropout_p, seed, row_stride, row0)
+        pd = torch.where(keep[None, None], probs / (1.0 - dropout_p), torch.zeros(()))
+    else:
+        pd = probs
+    g = Hq // Hkv
+    kf = k.float().repeat_interleave(g, dim=2)
+    vf = v.float().repeat_interleave(g, dim=2)
+    out = torch.einsum("bhqk,bkhd->bqhd", pd, vf)
+    if dout is None:
+        return out, lse, pd
+    dof = dout.float()
+    dv_full = torch.einsum("bhqk,bqhd->bkhd", pd, dof)
+    dp = torch.einsum("bqhd,bkhd->bhqk", dof, vf)
+    delta = (out * dof).sum(-1).transpose(1, 2)                      # (B, H, Sq)
+    ds = pd * (dp - delta[..., None])
+    if softcap > 0:
+        # d(softcap * tanh(u / softcap)) / du = 1 - tanh^2, with the capped score s = softcap * tanh(.)
+        ds = ds * (1.0 - (torch.nan_to_num(s, neginf=0.0) / softcap) ** 2)
+    dq = torch.einsum("bhqk,bkhd->bqhd", ds, kf) * scale
+    dk_full = torch.einsum("bhqk,bqhd->bkhd", ds, q.float()) * scale
+    fold = lambda t: t.reshape(B, Sk, Hkv, g, D).sum(3)
+    return out, lse, pd, dq, fold(dk_full), fold(dv_full)
+
+
 def attention_grads_ref(q, k, v, dout, **kw):
     """(out, lse, dq, dk, dv) in fp32 by autograd through attention_ref.  GQA gradients of
     a KV head are the sum over its query heads (attention_kernel.py:188-272)."""
@@ -157,6 +231,69 @@ def varlen_attention_grads_ref(q, k, v, dout, cu_q, cu_k, **kw):
                                      allow_unused=True)
     z = lambda g, t: torch.zeros_like(t) if g is None else g
     return out.detach(), lse.detach(), z(dq, q32), z(dk, k32), z(dv, v32)
+
+
+def varlen_attention_dropout_ref(q, k, v, cu_q, cu_k, max_seqlen_k, dout=None, dropout_p=0.0, seed=0,
+                                 alibi_slopes=None, **kw):
+    """Packed attention with dropout: every sequence through attention_dropout_ref with the
+    packed kernels' counters, (cu_q[b] + row) * max_seqlen_k + col (attention_kernel.py:91-93).
+    Returns (out (Tq,Hq,D), lse (Tq,Hq), probs list per sequence (Hq,q_len,k_len)[, dq, dk, dv])."""
+    cu_q = [int(x) for x in cu_q]
+    cu_k = [int(x) for x in cu_k]
+    batch = len(cu_q) - 1
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    lse = torch.full((q.shape[0], q.shape[1]), float("-inf"))
+    dq = torch.zeros(q.shape, dtype=torch.float32)
+    dk = torch.zeros(k.shape, dtype=torch.float32)
+    dv = torch.zeros(v.shape, dtype=torch.float32)
+    probs = []
+    slopes = None
+    if alibi_slopes is not None:
+        slopes = torch.as_tensor(alibi_slopes, dtype=torch.float32)
+        if slopes.ndim == 1:
+            slopes = slopes[None, :].expand(batch, -1)
+    for b in range(batch):
+        qs, qe, ks, ke = cu_q[b], cu_q[b + 1], cu_k[b], cu_k[b + 1]
+        if qe == qs or ke == ks:
+            probs.append(torch.zeros((q.shape[1], qe - qs, ke - ks)))
+            continue
+        r = attention_dropout_ref(q[qs:qe][None], k[ks:ke][None], v[ks:ke][None],
+                                  None if dout is None else dout[qs:qe][None], dropout_p=dropout_p, seed=seed,
+                                  row_stride=max_seqlen_k, row0=qs,
+                                  alibi_slopes=None if slopes is None else slopes[b:b + 1], **kw)
+        out[qs:qe] = r[0][0]
+        lse[qs:qe] = r[1][0].transpose(0, 1)
+        probs.append(r[2][0])
+        if dout is not None:
+            dq[qs:qe], dk[ks:ke], dv[ks:ke] = r[3][0], r[4][0], r[5][0]
+    return (out, lse, probs) if dout is None else (out, lse, probs, dq, dk, dv)
+
+
+def seqused_view(cu, used):
+    """Index list of the rows a packed call with seqused lengths reads: rows
+    [cu[b], cu[b] + used[b]) of every sequence, and the cu_seqlens of that packing
+    (flash_attn_interface.py:552-581)."""
+    cu = [int(x) for x in cu]
+    used = [int(x) for x in used]
+    idx = [cu[b] + i for b in range(len(used)) for i in range(used[b])]
+    new_cu = [0]
+    for u in used:
+        new_cu.append(new_cu[-1] + u)
+    return torch.tensor(idx, dtype=torch.long), new_cu
+
+
+def unpage_ref(pages, block_table, cu_k):
+    """Packed (Tk, H, D) rows of a paged tensor (pages, page_size, H, D): sequence b's tokens are
+    the first cu_k[b+1]-cu_k[b] slots of its pages, in block_table order
+    (flash_attn_interface.py:533-550)."""
+    page = pages.shape[1]
+    cu_k = [int(x) for x in cu_k]
+    parts = []
+    for b in range(len(cu_k) - 1):
+        n = cu_k[b + 1] - cu_k[b]
+        ids = block_table[b, :(n + page - 1) // page].long()
+        parts.append(pages[ids].reshape(-1, pages.shape[2], pages.shape[3])[:n])
+    return torch.cat(parts, dim=0)
 
 
 # ----------------------------------------------------------------------------------------

@@ -192,9 +192,50 @@ def kvcache():
          v_rows=torch.stack([vc2[p, o] for p, o in touched.tolist()]), lens=np.array(lens))
 
 
+def dropout():
+    """Dropout through the public wrappers with Python's `random` seeded, which fixes the seed the
+    reference draws (attention_kernel.py:1238-1239, :1371-1372): equal-length dense (padded to 64),
+    the cross path (both sides padded to the longer one) and the packed kernels."""
+    import random
+    IF, AK = REF.IF, REF.AK
+    blob = {}
+    specs = {
+        "eq100_causal": (2, 100, 100, 2, 2, 64, dict(causal=True, softmax_scale=0.125, dropout_p=0.25)),
+        "cross70x100_gqa": (1, 70, 100, 4, 2, 32, dict(causal=False, dropout_p=0.1)),
+        "cross100x70_cap": (1, 100, 70, 2, 2, 32, dict(causal=True, dropout_p=0.3, softcap=6.0)),
+    }
+    for i, (name, (B, Sq, Sk, Hq, Hkv, D, kw)) in enumerate(specs.items()):
+        q, k, v, do = cases.dense_case(300 + i, B, Sq, Sk, Hq, Hkv, D)
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        random.seed(4242 + i)
+        out = IF.flash_attn_func(qg, kg, vg, **kw)
+        dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
+        random.seed(4242 + i)
+        blob[name + ".seed"] = np.array(random.randrange(2 ** 31 - 1))
+        blob[name + ".checksum"] = np.array(cases.checksum(q, k, v, do))
+        for n, t in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+            blob[f"{name}.{n}"] = t.detach().numpy()
+        print(name, "done")
+    blob["_specs"] = np.array(repr(specs))
+    q_lens, k_lens = [37, 64, 130], [50, 64, 101]
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(9, q_lens, k_lens, 4, 2, 64)
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    random.seed(99)
+    out = IF.flash_attn_varlen_func(qg, kg, vg, cu_q, cu_k, 130, 101, dropout_p=0.2, causal=True)
+    dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
+    random.seed(99)
+    blob["varlen.seed"] = np.array(random.randrange(2 ** 31 - 1))
+    blob["varlen.checksum"] = np.array(cases.checksum(q, k, v, do))
+    blob["varlen.q_lens"], blob["varlen.k_lens"] = np.array(q_lens), np.array(k_lens)
+    for n, t in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+        blob[f"varlen.{n}"] = t.detach().numpy()
+    np.savez_compressed(os.path.join(HERE, "dropout.npz"), **blob)
+    print("wrote dropout")
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     only = sys.argv[2:]
-    for fn in (dense_lowlevel, dense_public, varlen, int8, kvcache):
+    for fn in (dense_lowlevel, dense_public, varlen, int8, kvcache, dropout):
         if not only or fn.__name__ in only:
             fn()

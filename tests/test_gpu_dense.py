@@ -169,9 +169,9 @@ def test_packed_and_strided_inputs():
     assert maxdiff(qkv.grad[:, :, 2], rdv) <= util.GRAD_TOL
 
 
-def test_eager_paths_bias_probs_dropout_fp32():
-    """attn_bias / return_attn_probs / dropout / fp32 go through the eager path like the
-    reference's (tests/test_compare_implementations.py:161-178)."""
+def test_bias_probs_dropout_fp32_smallest():
+    """attn_bias / return_attn_probs / dropout / fp32 at the sizes of the reference's own checks
+    (tests/test_compare_implementations.py:161-178); tests/test_gpu_features.py goes further."""
     q, k, v, do = cases.dense_case(14, 2, 7, 13, 2, 2, 16)
     bias = (torch.randn(2, 2, 7, 13, generator=torch.Generator().manual_seed(11)) * 0.1).half()
     out = fa().flash_attn_func_cross(q.to(DEV), k.to(DEV), v.to(DEV), attn_bias=bias.to(DEV))
@@ -186,7 +186,7 @@ def test_eager_paths_bias_probs_dropout_fp32():
     o = fa().flash_attn_func(z, z, torch.ones_like(z), dropout_p=0.5)
     assert torch.all(torch.isclose(o, torch.full_like(o, 2.0), atol=1e-3) | (o.abs() < 1e-3))
     o32 = fa().flash_attn_func(q.float().to(DEV), k.float().to(DEV), v.float().to(DEV))
-    assert o32.dtype == torch.float32 and maxdiff(o32, orc.attention_ref(q, k, v)[0]) <= 1e-4
+    assert o32.dtype == torch.float32 and maxdiff(o32, orc.attention_ref(q, k, v)[0]) <= util.FWD_TOL
 
 
 def test_modules():

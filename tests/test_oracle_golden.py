@@ -175,3 +175,42 @@ def test_int8_padded(golden, causal):
     assert maxdiff(dq[:, :, :150], g["dq"][:, :, :150]) <= GRAD_TOL
     for name, t in (("dk", dk), ("dv", dv)):
         assert maxdiff(t, g[name]) <= GRAD_TOL, name
+
+
+def test_philox_known_answers():
+    """The first Philox4x32-10 word for a few (seed, counter) pairs, as Triton's tl.rand produced
+    them under its interpreter."""
+    u = orc.philox_uniform(0, np.array([5, 982, 1959]))
+    assert u.tolist() == [0.9006523489952087, 0.7447494268417358, 0.2224503457546234]
+    u = orc.philox_uniform(1234, np.array([5, 982, 1959]))
+    assert u.tolist() == [0.4206197261810303, 0.9028539061546326, 0.7525394558906555]
+
+
+def test_dropout_dense(golden):
+    """The reference's dropout, forward and backward, restated: same Philox counters, same
+    dS = P_dropped * (dP - delta) backward."""
+    g = golden("dropout")
+    specs = ast.literal_eval(str(g["_specs"]))
+    for i, (name, (B, Sq, Sk, Hq, Hkv, D, kw)) in enumerate(specs.items()):
+        q, k, v, do = cases.dense_case(300 + i, B, Sq, Sk, Hq, Hkv, D)
+        assert cases.checksum(q, k, v, do) == str(g[name + ".checksum"]), name
+        out, lse, pd, dq, dk, dv = orc.attention_dropout_ref(
+            q, k, v, do, dropout_p=kw["dropout_p"], seed=int(g[name + ".seed"]),
+            softmax_scale=kw.get("softmax_scale"), causal=kw.get("causal", False), softcap=kw.get("softcap", 0.0))
+        # kept probabilities are scaled by 1/(1-p), and fp16 rounding errors with them
+        amp = 1.0 / (1.0 - kw["dropout_p"])
+        assert maxdiff(out, g[name + ".out"]) <= FWD_TOL * amp, name
+        for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+            assert maxdiff(t, g[f"{name}.{n}"]) <= GRAD_TOL * amp, (name, n)
+
+
+def test_dropout_varlen(golden):
+    g = golden("dropout")
+    ql, kl = g["varlen.q_lens"].tolist(), g["varlen.k_lens"].tolist()
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(9, ql, kl, 4, 2, 64)
+    assert cases.checksum(q, k, v, do) == str(g["varlen.checksum"])
+    out, lse, pd, dq, dk, dv = orc.varlen_attention_dropout_ref(
+        q, k, v, cu_q, cu_k, 101, do, dropout_p=0.2, seed=int(g["varlen.seed"]), causal=True)
+    assert maxdiff(out, g["varlen.out"]) <= FWD_TOL / 0.8
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t, g["varlen." + n]) <= GRAD_TOL / 0.8, n
