@@ -10,64 +10,103 @@ __device__ __forceinline__ int round_i8(float x) {
   return (int)(x >= 0.f ? floorf(__fadd_rn(x, 0.5f)) : ceilf(__fsub_rn(x, 0.5f)));
 }
 
+// The same function for |x| < 2^22 without the round-to-integer and float-to-int conversions,
+// which run on the quarter-rate conversion pipe and bound a streaming kernel: ceil(x - 0.5) is
+// -floor(|x| + 0.5) (fp32 rounding is symmetric), and floor(t) of a non-negative t < 2^23 is
+// what the mantissa holds after t + 2^23 rounded DOWN (the sum's unit in the last place is 1).
+__device__ __forceinline__ int round_i8_fast(float x) {
+  const float t = __fadd_rn(fabsf(x), 0.5f);
+  const int m = __float_as_int(__fadd_rd(t, 8388608.0f)) & 0x3ff;
+  return x < 0.f ? -m : m;
+}
+
 // ---------------------------------------------------------------------------------------
 // K quantiser: rows x D fp16 -> int8 codes + fp32 scale per row.  HBM-bound: 2 B read and
-// 1 B written per element.  One 16-byte load per thread, D/8 lanes per row.
+// 1 B written per element.  D/8 lanes share a row, 16 bytes each; every thread keeps kRows
+// independent rows in flight per step (all loads are issued before the first is used) and the grid
+// strides over the rows, a few resident blocks per SM, so that enough bytes are outstanding to
+// cover the memory latency.  Loads and stores bypass L1 and are marked streaming: nothing is reused.
 // ---------------------------------------------------------------------------------------
 // kDivide: codes = round(x / s) (the reference's query form) instead of round(x * (1/s))
+#ifndef FA_QUANT_ROWS
+#define FA_QUANT_ROWS 6
+#endif
+#ifndef FA_QUANT_BLOCKS
+#define FA_QUANT_BLOCKS 8
+#endif
+constexpr int kQuantRows = FA_QUANT_ROWS;
 template <int D, bool kDivide = false>
 __global__ void __launch_bounds__(256) quantize_k_kernel(const __half* __restrict__ k,
                                                          int8_t* __restrict__ k8,
                                                          float* __restrict__ s_k, int64_t rows) {
   constexpr int LPR = D / 8;
-  constexpr int RPB = 256 / LPR;
+  constexpr int RPB = 256 / LPR;                     // rows per block and sub-step
   const int tid = threadIdx.x;
-  const int64_t row = (int64_t)blockIdx.x * RPB + tid / LPR;
   const int c = tid % LPR;
-  const bool ok = row < rows;
-  uint4 raw = make_uint4(0, 0, 0, 0);
-  if (ok) raw = __ldg(reinterpret_cast<const uint4*>(k + row * D + c * 8));
-  const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
-  float x[8];
-  float amax = 0.f;
+  const int64_t step = (int64_t)gridDim.x * RPB * kQuantRows;
+  for (int64_t blk = (int64_t)blockIdx.x * RPB * kQuantRows; blk < rows; blk += step) {   // block-uniform bound
+    const int64_t base = blk + tid / LPR;
+    uint4 raw[kQuantRows];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(h2[i]);
-    x[2 * i] = f.x;
-    x[2 * i + 1] = f.y;
-    amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-  }
+    for (int j = 0; j < kQuantRows; ++j) {
+      const int64_t row = base + (int64_t)j * RPB;
+      raw[j] = make_uint4(0, 0, 0, 0);
+      if (row < rows) raw[j] = __ldcs(reinterpret_cast<const uint4*>(k + row * D + c * 8));
+    }
 #pragma unroll
-  for (int s = LPR / 2; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-  const float sc = __fdiv_rn(fmaxf(amax, 1.0f), 127.0f);
-  const float inv = __fdiv_rn(1.0f, sc);
-  uint32_t lo = 0, hi = 0;
+    for (int j = 0; j < kQuantRows; ++j) {
+      const int64_t row = base + (int64_t)j * RPB;
+      const __half2* h2 = reinterpret_cast<const __half2*>(&raw[j]);
+      float x[8];
+      float amax = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float a = kDivide ? __fdiv_rn(x[i], sc) : __fmul_rn(x[i], inv);
-    const float c2 = kDivide ? __fdiv_rn(x[4 + i], sc) : __fmul_rn(x[4 + i], inv);
-    lo |= (uint32_t)(uint8_t)(int8_t)round_i8(a) << (8 * i);
-    hi |= (uint32_t)(uint8_t)(int8_t)round_i8(c2) << (8 * i);
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h2[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+      // every lane of the warp takes part in the shuffles (the loop bound is warp-uniform)
+#pragma unroll
+      for (int s = LPR / 2; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+      const float sc = __fdiv_rn(fmaxf(amax, 1.0f), 127.0f);
+      const float inv = __fdiv_rn(1.0f, sc);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = kDivide ? __fdiv_rn(x[i], sc) : __fmul_rn(x[i], inv);
+        const float c2 = kDivide ? __fdiv_rn(x[4 + i], sc) : __fmul_rn(x[4 + i], inv);
+        lo |= (uint32_t)(uint8_t)(int8_t)round_i8_fast(a) << (8 * i);
+        hi |= (uint32_t)(uint8_t)(int8_t)round_i8_fast(c2) << (8 * i);
+      }
+      if (row < rows) {
+        __stcs(reinterpret_cast<uint2*>(k8 + row * D + c * 8), make_uint2(lo, hi));
+        if (c == 0) __stcs(s_k + row, sc);
+      }
+    }
   }
-  if (ok) {
-    *reinterpret_cast<uint2*>(k8 + row * D + c * 8) = make_uint2(lo, hi);
-    if (c == 0) s_k[row] = sc;
-  }
+}
+
+template <int D, bool kDivide>
+static int launch_quantiser(const void* x, int8_t* x8, float* s, int64_t rows, cudaStream_t st, const char* what) {
+  constexpr int RPB = 256 / (D / 8);
+  const int64_t need = (rows + RPB * kQuantRows - 1) / (RPB * kQuantRows);
+  int device = 0;
+  cudaGetDevice(&device);
+  const int64_t cap = (int64_t)sm_count(device) * FA_QUANT_BLOCKS;  // 8 blocks of 256 threads fill an SM
+  quantize_k_kernel<D, kDivide><<<(unsigned)(need < cap ? need : cap), 256, 0, st>>>(
+      reinterpret_cast<const __half*>(x), x8, s, rows);
+  return check_launch(what);
 }
 
 int quantize_k(const void* k, int8_t* k8, float* s_k, int64_t rows, int head_dim, cudaStream_t st) {
   if (rows == 0) return FA_OK;
-#define FA_Q(DD)                                                                              \
-  case DD: {                                                                                  \
-    constexpr int RPB = 256 / (DD / 8);                                                       \
-    quantize_k_kernel<DD><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(               \
-        reinterpret_cast<const __half*>(k), k8, s_k, rows);                                   \
-    return check_launch("quantize_k");                                                        \
-  }
   switch (head_dim) {
-    FA_Q(32) FA_Q(64) FA_Q(128) FA_Q(256)
+    case 32: return launch_quantiser<32, false>(k, k8, s_k, rows, st, "quantize_k");
+    case 64: return launch_quantiser<64, false>(k, k8, s_k, rows, st, "quantize_k");
+    case 128: return launch_quantiser<128, false>(k, k8, s_k, rows, st, "quantize_k");
+    case 256: return launch_quantiser<256, false>(k, k8, s_k, rows, st, "quantize_k");
   }
-#undef FA_Q
   set_error("INT8 path needs head_dim in {32,64,128,256}, got %d", head_dim);
   return FA_ERR_UNSUPPORTED;
 }
@@ -80,10 +119,7 @@ int quantize_q(const void* q, int8_t* q8, float* s_q, int64_t rows, int head_dim
     set_error("quantize_q: head_dim 128 only");
     return FA_ERR_UNSUPPORTED;
   }
-  constexpr int RPB = 256 / (128 / 8);
-  quantize_k_kernel<128, true><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(
-      reinterpret_cast<const __half*>(q), q8, s_q, rows);
-  return check_launch("quantize_q");
+  return launch_quantiser<128, true>(q, q8, s_q, rows, st, "quantize_q");
 }
 
 // ---------------------------------------------------------------------------------------
