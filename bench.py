@@ -577,7 +577,9 @@ def run_ours(args, rank, world, local_rank):
     # batch goes through in NCH chunks: the copy-in of chunk c+1 (copy stream) and the copy-out of
     # chunk c-1 (second copy stream) overlap the kernels of chunk c; (batch x head) units are
     # independent, so chunking changes no result.
-    NCH = 4
+    NCH = max(1, min(B, int(os.environ.get("FA_BENCH_E2E_CHUNKS", "16"))))
+    while B % NCH:
+        NCH -= 1
     hq, hk_, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
     ho, hdq, hdk, hdv = (torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (q, q, k, v))
     dq_, dk_, dv_, ddo = (torch.empty_like(q) for _ in range(4))
