@@ -321,18 +321,56 @@ def decode_bench(dev, peaks, iters=20, batch_lo=0, batch_hi=64):
 
 
 def profile_case(args):
-    """Forward + backward on B=2 H=16 S=4096 D=128 causal (inputs 128 MiB > L2), W+K steps."""
+    """Small cases for ncu captures (a few hundred MB on the device, more than the 126 MB L2), W+K
+    steps of one kernel family each:
+      dense     forward + backward, B2 H16 S4096 D128 causal (per-CTA dK/dV kernel)
+      dense_nc  the same without the mask (persistent dK/dV kernel)
+      varlen    8 packed sequences, H8 D128, causal + window 1024 + ALiBi + soft cap (feature variants)
+      decode    16 sequences of the paged-decode workload
+      int8      INT8-QK^T forward B1 H8 S8192 D128 and both quantisers"""
+    import flash_attn_triton_b200 as fa
     from flash_attn_triton_b200 import _native as N
     from flash_attn_triton_b200 import _ops
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
-    q, k, v, do = (torch.randn(2, S, H, D, device=dev, dtype=torch.float16, generator=g) for _ in range(4))
+    which = args.profile_case
     scale = 1.0 / math.sqrt(D)
-    for _ in range(args.warmup + args.steps):
-        o, lse, _ = _ops.dense_forward(q, k, v, scale, True, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd", True)
-        _ops.dense_backward(q, k, v, o, lse, do, scale, True, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd")
+    n = args.warmup + args.steps
+    if which in ("dense", "dense_nc"):
+        causal = which == "dense"
+        q, k, v, do = (torch.randn(2, S, H, D, device=dev, dtype=torch.float16, generator=g) for _ in range(4))
+        for _ in range(n):
+            o, lse, _ = _ops.dense_forward(q, k, v, scale, causal, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd", True)
+            _ops.dense_backward(q, k, v, o, lse, do, scale, causal, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bshd")
+        what = "B2 H16 S4096 D128 fwd+bwd, causal=%d" % causal
+    elif which == "varlen":
+        import numpy as np
+        lens = (64 * np.random.default_rng(3).integers(4, 65, size=8)).tolist()
+        Hh, T = 8, int(sum(lens))
+        q, k, v, do = (torch.randn(T, Hh, D, device=dev, dtype=torch.float16, generator=g) for _ in range(4))
+        cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=dev)
+        alibi = torch.tensor([[2.0 ** (-8 * (i + 1) / Hh) for i in range(Hh)]] * 8, device=dev).contiguous()
+        cfg = (max(lens), max(lens), scale, True, 1024, 0, 30.0, alibi)
+        for _ in range(n):
+            o, lse, _ = _ops.varlen_forward(q, k, v, cu, cu, *cfg, N.IMPL_AUTO, True)
+            _ops.varlen_backward(q, k, v, o, lse, do, cu, cu, *cfg, N.IMPL_AUTO)
+        what = "packed %d tokens in 8 sequences, H8 D128, causal window 1024 ALiBi softcap 30, fwd+bwd" % T
+    elif which == "decode":
+        (q, kc, vc, kn, vn, cos, sin, cl, bt), bytes_step, _ = decode_case(dev, 0, 16)
+        fa.set_validation(False)
+        for _ in range(n):
+            fa.flash_attn_with_kvcache(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl, block_table=bt,
+                                       rotary_interleaved=False)
+        what = "paged decode, sequences [0,16) of the workload, %.0f MB of K/V per step" % (bytes_step / 1e6)
+    elif which == "int8":
+        q, k, v = (torch.randn(1, 8, 8192, D, device=dev, dtype=torch.float16, generator=g) for _ in range(3))
+        for _ in range(n):
+            fa.attention_int8(q, k, v, causal=False)
+        what = "INT8 forward B1 H8 S8192 D128 non-causal incl. K and Q quantisers"
+    else:
+        raise SystemExit("unknown profile case " + str(which))
     torch.cuda.synchronize()
-    print(json.dumps({"profile_case": "B2 H16 S4096 D128 causal fwd+bwd", "steps": args.warmup + args.steps,
+    print(json.dumps({"profile_case": which, "what": what, "steps": n,
                       "device_wait_status": N.lib().fa_device_wait_status(0)}))
 
 
@@ -702,9 +740,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile-case", action="store_true",
-                    help="run only forward+backward steps on a reduced batch (B=2) and exit: the small "
-                         "case used for ncu captures")
+    ap.add_argument("--profile-case", nargs="?", const="dense", default=None,
+                    choices=["dense", "dense_nc", "varlen", "decode", "int8"],
+                    help="run only W+K steps of one small case and exit (for ncu captures); default: dense")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

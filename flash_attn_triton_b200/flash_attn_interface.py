@@ -89,6 +89,17 @@ def _dense_call(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
     return out.to(out_dtype), lse, probs
 
 
+def _raise_first(checks):
+    """checks: [(0-d bool tensor on the device, message)] in order of precedence.  One reduction and
+    ONE device->host read decide whether any of them is set; only then are they looked at one by one."""
+    if not checks:
+        return
+    if bool(torch.stack([c for c, _ in checks]).any()):
+        for c, msg in checks:
+            if bool(c):
+                raise ValueError(msg)
+
+
 def _normalise_alibi(alibi_slopes, batch, heads, device):
     """(nheads,) or (batch, nheads) -> contiguous fp32 (batch, nheads); None stays None."""
     if alibi_slopes is None:
@@ -227,10 +238,12 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
     measured from there (also without `causal`: the reference only shifts the causal mask,
     flash_attn_interface.py:523).  `num_splits` (0 = automatic) is an extra tuning knob.
 
-    With value checks on (the default) the call reads a few flags back from the device (page
-    indices in range, lengths fit the cache and the rotary tables); `set_validation(False)` or
-    FA_B200_VALIDATE=0 turns them off and the call then never synchronises."""
+    With value checks on (the default) the call reads ONE flag back from the device (page indices
+    in range, lengths fit the cache and the rotary tables, reduced on the device);
+    `set_validation(False)` or FA_B200_VALIDATE=0 turns them off and the call then never
+    synchronises."""
     paged = block_table is not None
+    checks = []          # value checks, evaluated together just before the launch (one host read)
     if (rotary_cos is None) != (rotary_sin is None):
         raise ValueError("rotary_cos and rotary_sin must be supplied together")
     if q.ndim != 4 or k_cache.ndim != 4 or v_cache.ndim != 4:
@@ -252,9 +265,10 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
             raise ValueError("cache_batch_idx cannot be combined with paged KV caches")
         page_size = k_cache.shape[1]
         cache_capacity = block_table.shape[1] * page_size
-        if _VALIDATE and (torch.any(block_table < 0) or torch.any(block_table >= k_cache.shape[0])):
-            raise ValueError("block_table contains an invalid physical page index")
         block_table = block_table.to(device=dev, dtype=torch.int32).contiguous()
+        if _VALIDATE:
+            checks.append((torch.any((block_table < 0) | (block_table >= k_cache.shape[0])),
+                           "block_table contains an invalid physical page index"))
     else:
         cache_capacity = k_cache.shape[1]
     if q.shape[-1] != k_cache.shape[-1]:
@@ -274,15 +288,20 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
     rows = None
     if cache_batch_idx is not None:
         rows = _as_i32(cache_batch_idx, dev)
-        if rows.numel() != B or (_VALIDATE and (torch.any(rows < 0) or torch.any(rows >= k_cache.shape[0]))):
+        if rows.numel() != B:
             raise ValueError("cache_batch_idx must contain valid cache-row indices")
+        if _VALIDATE:
+            checks.append((torch.any((rows < 0) | (rows >= k_cache.shape[0])),
+                           "cache_batch_idx must contain valid cache-row indices"))
     elif not paged and k_cache.shape[0] < B:
         raise ValueError("cache_batch_idx must contain valid cache-row indices")
     pads = None
     if cache_leftpad is not None:
         pads = _as_i32(cache_leftpad, dev)
-        if pads.numel() != B or (_VALIDATE and torch.any(pads < 0)):
+        if pads.numel() != B:
             raise ValueError("cache_leftpad must contain one non-negative value per query batch")
+        if _VALIDATE:
+            checks.append((torch.any(pads < 0), "cache_leftpad must contain one non-negative value per query batch"))
     n_new = 0
     if k is not None or v is not None:
         if k is None or v is None or k.shape != v.shape:
@@ -299,8 +318,7 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
             raise ValueError("new KV tensors do not fit in the cache")
         if _VALIDATE:
             total = lengths.long() + n_new + (pads.long() if pads is not None else 0)
-            if torch.any(lengths < 0) or torch.any(total > cache_capacity):
-                raise ValueError("new KV tensors do not fit in the cache")
+            checks.append((torch.any((lengths < 0) | (total > cache_capacity)), "new KV tensors do not fit in the cache"))
         if n_new == 0:
             k = v = None
     else:
@@ -312,8 +330,8 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
             raise ValueError("cache_seqlens must contain valid lengths for every batch item")
         if _VALIDATE:
             total = lengths.long() + (pads.long() if pads is not None else 0)
-            if torch.any(lengths < 0) or torch.any(total > cache_capacity):
-                raise ValueError("cache_seqlens must contain valid lengths for every batch item")
+            checks.append((torch.any((lengths < 0) | (total > cache_capacity)),
+                           "cache_seqlens must contain valid lengths for every batch item"))
     cos = sin = None
     if rotary_cos is not None:
         if rotary_cos.shape != rotary_sin.shape or rotary_cos.ndim != 2:
@@ -323,11 +341,12 @@ def flash_attn_with_kvcache(q, k_cache, v_cache, k=None, v=None, rotary_cos=None
         if _VALIDATE:
             # every rotated position (new keys and query rows) must have a table row
             last = lengths.long() + n_new + (pads.long() if pads is not None else 0)
-            if torch.any(last > rotary_cos.shape[0]):
-                raise ValueError("rotary tables are shorter than the longest sequence after the append")
+            checks.append((torch.any(last > rotary_cos.shape[0]),
+                           "rotary tables are shorter than the longest sequence after the append"))
         cos = rotary_cos.to(device=dev, dtype=q.dtype).contiguous()
         sin = rotary_sin.to(device=dev, dtype=q.dtype).contiguous()
     alibi = _normalise_alibi(alibi_slopes, B, q.shape[2], dev)
+    _raise_first(checks)
     if B == 0 or q.shape[1] == 0:
         return q.new_empty(q.shape)
     if softmax_scale is None:
@@ -359,12 +378,14 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
         if used_k.numel() != batch_size:
             raise ValueError("seqused_k must contain one value per sequence")
     if _VALIDATE and (used_q is not None or used_k is not None):
-        lq = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).to(q.device)
-        lk = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).to(q.device)
-        if used_q is not None and bool(torch.any((used_q < 0) | (used_q > lq))):
-            raise ValueError("seqused_q exceeds the packed query sequence")
-        if used_k is not None and bool(torch.any((used_k < 0) | (used_k > lk))):
-            raise ValueError("seqused_k exceeds the packed KV sequence")
+        checks = []
+        if used_q is not None:
+            lq = (cu_seqlens_q[1:] - cu_seqlens_q[:-1]).to(q.device)
+            checks.append((torch.any((used_q < 0) | (used_q > lq)), "seqused_q exceeds the packed query sequence"))
+        if used_k is not None:
+            lk = (cu_seqlens_k[1:] - cu_seqlens_k[:-1]).to(q.device)
+            checks.append((torch.any((used_k < 0) | (used_k > lk)), "seqused_k exceeds the packed KV sequence"))
+        _raise_first(checks)
     if q.ndim != 3 or k.ndim != 3 or v.ndim != 3 or k.shape != v.shape:
         raise ValueError("packed q, k, and v must be rank-3 tensors with matching KV shapes")
     if cu_seqlens_q.ndim != 1 or cu_seqlens_k.ndim != 1:
@@ -396,7 +417,8 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     cu_seqlens_k = cu_seqlens_k.to(dtype=torch.int32).contiguous()
     if _VALIDATE:
         # one device->host transfer for every value check the reference makes (:588-626)
-        cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+        both = torch.cat((cu_seqlens_q, cu_seqlens_k)).tolist()
+        cq, ck = both[:batch_size + 1], both[batch_size + 1:]
         if cq[0] != 0 or ck[0] != 0:
             raise ValueError("cu_seqlens arrays must start at zero and contain a batch boundary")
         if any(b < a for a, b in zip(cq, cq[1:])) or any(b < a for a, b in zip(ck, ck[1:])):
