@@ -772,11 +772,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // tiles to the TMA unit and releases the two ring entries once the unit has read them.
       {
         const int stgA = posA + w.total, stgB = posB + w.total - 1;
-#ifdef FA_X_DIRECT
-        const bool via_tma = false;
-#else
         const bool via_tma = (p.cu_seqlens_k == nullptr) || (w.n0 + kT <= w.g.k_len);
-#endif
         wq(&sh->stg_ready[0], wi & 1, 62);
         if (ok && via_tma && leader) {
 #pragma unroll
@@ -1062,11 +1058,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_after();
       PROF_T0();
       const uint32_t stg = (x == 0) ? slotB(stgB) : slotA(stgA);
-#ifdef FA_X_DIRECT
-      const bool via_tma = false;
-#else
       const bool via_tma = (p.cu_seqlens_k == nullptr) || (w.n0 + kT <= w.g.k_len);
-#endif
       drain_acc<T, D>((x == 0 ? tdV : tdK) + lane_addr, (x == 0) ? 1.f : cfg.scale, via_tma, stg, lrow, 0, grow);
       tc_fence_before();
       if (via_tma) fence_proxy_async();
