@@ -204,17 +204,30 @@ __device__ __forceinline__ float score_log2_dist(const ScoreCfg& c, float slope,
   }
   return s * FA_LOG2E;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // The same for the kernels that are compiled per feature set: ALiBi always applied (a zero slope
-// leaves the score unchanged, exactly), the soft cap selected at compile time.
+// leaves the score unchanged, exactly), the soft cap selected at compile time.  Written so that
+// everything that does not depend on the element is a loop-invariant product the compiler hoists:
+//   no cap:  dot * scale_log2 - (slope log2e) |dist|                               2 instructions
+//   cap:     u = 2 log2e / cap * (dot * scale - slope |dist|),  r = 1 / (2^u + 1),
+//            tanh = 1 - 2 r,  score = cap log2e (1 - 2 r)                          2 + 2 MUFU + 2
+// (2^u = inf gives r = 0, tanh = 1; 2^u = 0 gives r = 1, tanh = -1: no special cases).
 template <bool kCap>
 __device__ __forceinline__ float score_log2_feat(const ScoreCfg& c, float slope, float dot, float dist, float& th) {
-  float s = fmaf(-slope, fabsf(dist), dot * c.scale);
-  th = 0.f;
-  if (kCap) {
-    th = fast_tanh(s * c.inv_softcap);
-    s = c.softcap * th;
+  if (!kCap) {
+    th = 0.f;
+    return fmaf(-(slope * FA_LOG2E), fabsf(dist), dot * c.scale_log2);
   }
-  return s * FA_LOG2E;
+  const float k = c.inv_softcap * (2.f * FA_LOG2E);
+  const float u = fmaf(-(slope * k), fabsf(dist), dot * (c.scale * k));
+  const float r = rcp_approx(ex2(u) + 1.f);
+  th = fmaf(-2.f, r, 1.f);
+  const float cl = c.softcap * FA_LOG2E;
+  return fmaf(-2.f * cl, r, cl);
 }
 __device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
                                             int kpos, float& th, float bias = 0.f) {
