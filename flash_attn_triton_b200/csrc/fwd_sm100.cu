@@ -479,6 +479,28 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
 
+      // ---- packed batches: keep the next sequence's values out of P V ---------------------
+      // The last key tile of a packed sequence also holds rows of the NEXT sequence.  Their
+      // probabilities are exactly 0, but 0 * inf or 0 * NaN is NaN: zero those rows of the V tile
+      // (ring entry 2 j + 1 in order of use K0 V0 K1 V1 ...) before P is handed to the issuer.
+      // One thread per row; a row is D contiguous 16-bit values per 64-wide box, so the swizzle
+      // does not matter.  Both streams may do it for the same tile (zeros over zeros).
+      if (!kInt8 && p.cu_seqlens_k != nullptr && k0 + kBN > si.k_len) {
+        const int vpos = 2 * j + 1;
+        ok = wait_bar(&sh->kv_full[vpos % C::kStages], (vpos / C::kStages) & 1, sh, 39);
+        if (!ok) break;
+        if (k0 + row_in_tile >= si.k_len) {
+          unsigned char* vrow = tiles + C::kTileBytes * (2 + vpos % C::kStages) + row_in_tile * 128;
+#pragma unroll
+          for (int bx = 0; bx < C::kBoxes; ++bx) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              reinterpret_cast<uint4*>(vrow + bx * (kBN * 128))[c] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        fence_proxy_async();
+      }
+
       // ---- row maximum: eight chains of three-input maxima --------------------------------
       float mx;
       {

@@ -216,3 +216,22 @@ def test_bounded_wait_times_out_and_is_reported():
     (the word is per process)."""
     r = subprocess.run([sys.executable, "-c", _PROBE % ROOT], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "probe ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_forward_ignores_non_finite_rows_of_the_next_sequence(causal):
+    """The last key tile of a packed sequence also stages rows of the next sequence; their
+    probabilities are 0, and 0 * inf must not reach the output (tcgen05 and mma.sync forward)."""
+    from flash_attn_triton_b200 import _native as N, _ops
+    lens = [100, 60, 300]
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(77, lens, lens, 4, 2, 128)
+    k2, v2 = k.clone(), v.clone()
+    k2[100:160] = float("nan")                 # the whole second sequence is poisoned
+    v2[100:160] = float("inf")
+    ref, _ = orc.varlen_attention_ref(q, k, v, cu_q, cu_k, causal=causal)
+    for impl in (N.IMPL_TCGEN05, N.IMPL_MMA):
+        o, _, _ = _ops.varlen_forward(q.to(DEV), k2.to(DEV), v2.to(DEV), cu_q.to(DEV), cu_k.to(DEV), 300, 300,
+                                      128 ** -0.5, causal, -1, -1, 0.0, None, impl, False)
+        o = o.float().cpu()
+        assert torch.isfinite(o[:100]).all() and torch.isfinite(o[160:]).all(), impl
+        assert (o[:100] - ref[:100]).abs().max().item() <= 2e-3 and (o[160:] - ref[160:]).abs().max().item() <= 2e-3
