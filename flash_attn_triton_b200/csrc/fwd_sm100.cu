@@ -766,7 +766,20 @@ static int launch(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st, i
   return check_launch("fwd_sm100");
 }
 
+// Two kernels.  The persistent one (fwd_persist_sm100.cu) takes the calls with long work items:
+// measured with launches interleaved on one GPU it is 3-4 % faster at 4096-8192 keys (dense, GQA
+// and the packed workload) and 9 % slower at 1024 keys, where an item is four or five steps and
+// the hand-over between items costs more than a fresh CTA.  This file keeps the one-CTA-per-item
+// kernel for those, and for the INT8 variant.
+#ifndef FA_FWD_PERSISTENT_FROM
+#define FA_FWD_PERSISTENT_FROM 2048   // keys (dense: seqlen_k, packed: max_seqlen_k); 0 = never
+#endif
+int fwd_persist_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st);
+int fwd_persist_sm100_status();
+int fwd_persist_sm100_clear_status();
+
 int fwd_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
+  if (FA_FWD_PERSISTENT_FROM > 0 && a.seqlen_k >= FA_FWD_PERSISTENT_FROM) return fwd_persist_sm100(a, cfg, st);
   // Row extents of the tensor maps.  Dense: the sequence length.  Packed: the caller does
   // not pass the total token count, so the map covers rows up to the int32 limit of the
   // cu_seqlens; tiles never start past cu_seqlens[batch], and rows past a sequence's end
@@ -842,12 +855,13 @@ int fwd_int8_sm100(const fa_int8_args& a, cudaStream_t st) {
 int fwd_sm100_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_fwd_sm100_status, sizeof(int));
-  return v;
+  return v != 0 ? v : fwd_persist_sm100_status();
 }
 
 void fwd_sm100_clear_status() {
   const int z = 0;
   cudaMemcpyToSymbol(g_fwd_sm100_status, &z, sizeof(int));
+  fwd_persist_sm100_clear_status();
 }
 
 // One warp waits, for at most `clocks` cycles, on a barrier nothing arrives at: the time-out path
