@@ -434,7 +434,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = wait_bar(&sh->sk_full[j % kSkSlots], (j / kSkSlots) & 1, sh, 37 + x);
         if (!ok) break;
         const float4* S4 = reinterpret_cast<const float4*>(&sh->skt[j % kSkSlots][0]);
-        const float2 sq2 = make_float2(sq_row, sq_row), nb2 = make_float2(-12582912.0f, -12582912.0f);
+        const float2 nb2 = make_float2(-12582912.0f, -12582912.0f);
         // Two copies of the loop: without the per-element mask test there are no branches inside,
         // so the compiler can issue the shared-memory loads of the scales in batches (each one
         // takes hundreds of cycles while the tensor pipe streams its operands).
@@ -450,8 +450,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                                                    __uint_as_float(0x4B400000u + r[cc][i + 1])), nb2);
               const float2 a23 = f2add(make_float2(__uint_as_float(0x4B400000u + r[cc][i + 2]),
                                                    __uint_as_float(0x4B400000u + r[cc][i + 3])), nb2);
-              const float2 v01 = f2mul(f2mul(a01, sq2), make_float2(s4.x, s4.y));
-              const float2 v23 = f2mul(f2mul(a23, sq2), make_float2(s4.z, s4.w));
+              // the per-query scale (positive, one value per thread) is applied after the maximum,
+              // inside the FMA that forms the exp2 argument
+              const float2 v01 = f2mul(a01, make_float2(s4.x, s4.y));
+              const float2 v23 = f2mul(a23, make_float2(s4.z, s4.w));
               float v[4] = {v01.x, v01.y, v23.x, v23.y};
               if (kMask) {
 #pragma unroll
@@ -540,6 +542,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mx = fmaxf(fmax3(mt[0], mt[1], mt[2]), fmaxf(fmax3(mt[3], mt[4], mt[5]), fmaxf(mt[6], mt[7])));
       }
       if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
+      if (kInt8) mx *= sq_row;               // s_q > 0
 
 #ifdef FA_PROF
       prof_acc[masked ? 3 : 2] += (unsigned int)(clock64() - prof_t1);   // load + score + max phase
@@ -587,14 +590,14 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // Outlier keys make the rows peaky; with a stale reference maximum the dominant
         // probability is 2^x instead of exactly 1, so its rounding to T would not cancel
         // in O / l unless l sums the ROUNDED values that enter P@V.
-        const float2 nm2 = make_float2(-m_safe, -m_safe);
+        const float2 nm2 = make_float2(-m_safe, -m_safe), sq2 = make_float2(sq_row, sq_row);
         float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float2 a = f2add(make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), nm2);
+            const float2 a = f2fma(make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), sq2, nm2);
             pk[i >> 1] = Elem<T>::pack(ex2(a.x), ex2(a.y));
             acc2[(i >> 1) & 1] = f2add(acc2[(i >> 1) & 1], Elem<T>::unpack(pk[i >> 1]));
           }
