@@ -1,13 +1,16 @@
-// KV-cache decode: in-place append with fused rotary, then split-KV attention over a
-// paged (or contiguous) cache, then a small combine.  HBM-bound: the job of the main
+// KV-cache decode: split-KV attention over a paged (or contiguous) cache with the in-place append
+// and the rotary embedding fused in, then a small combine.  HBM-bound: the job of the main
 // kernel is to stream every cached K/V byte exactly once at full bandwidth.
 //
-//   kv_append_kernel : rotate k_new (optional) and write k_new/v_new into the cache slots
 //   decode_kernel    : CTA = (split, kv head x row group, sequence).  The query rows of one
 //                      GQA group (seqlen_q x group <= 16 per row group) form the M=16 side
 //                      of mma.sync m16n8k16, so one K/V byte serves the whole group.  K/V
 //                      tiles of 64 keys arrive through a 3-stage cp.async ring of 16-byte
 //                      page-row gathers; 4 warps take 16 keys each and merge at the end.
+//                      The new tokens (k_new rotated, v_new) never come from the cache: the CTAs
+//                      whose split holds their positions put them into the staged tile
+//                      themselves, and the CTA of row group 0 also writes them to their cache
+//                      slots -- one writer per (sequence, kv head, token), no separate launch.
 //   combine_kernel   : merges the per-split partial outputs with their base-2 LSEs.
 #include <mutex>
 
@@ -79,31 +82,6 @@ __device__ __forceinline__ int64_t cache_row_offset(const fa_decode_args& p, int
 }
 
 // ---------------------------------------------------------------------------------------
-// append
-// ---------------------------------------------------------------------------------------
-template <typename T>
-__global__ void kv_append_kernel(const fa_decode_args p, int page_shift) {
-  const int D = p.head_dim;
-  const int b = blockIdx.z, i = blockIdx.y, hk = blockIdx.x;
-  const int len = p.cache_seqlens[b];
-  const int pad = p.cache_leftpad ? p.cache_leftpad[b] : 0;
-  const int pos = len + pad + i;
-  const T* kn = reinterpret_cast<const T*>(p.k_new) + b * p.kn_stride[0] + i * p.kn_stride[1] + hk * p.kn_stride[2];
-  const T* vn = reinterpret_cast<const T*>(p.v_new) + b * p.vn_stride[0] + i * p.vn_stride[1] + hk * p.vn_stride[2];
-  T* kc = reinterpret_cast<T*>(p.k_cache) + cache_row_offset(p, b, pos, page_shift, p.kc_stride) + hk * p.kc_stride[2];
-  T* vc = reinterpret_cast<T*>(p.v_cache) + cache_row_offset(p, b, pos, page_shift, p.vc_stride) + hk * p.vc_stride[2];
-  const T* cos = reinterpret_cast<const T*>(p.rotary_cos);
-  const T* sin = reinterpret_cast<const T*>(p.rotary_sin);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    T kv = kn[d];
-    if (cos) kv = rotary_elem<T>([&](int j) { return kn[j]; }, d, cos, sin, pos, p.rotary_dim, p.rotary_interleaved,
-                                   p.rotary_seqlen);
-    kc[d] = kv;
-    vc[d] = vn[d];
-  }
-}
-
-// ---------------------------------------------------------------------------------------
 // split-KV attention
 // ---------------------------------------------------------------------------------------
 template <typename T, int D>
@@ -121,7 +99,9 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
   const int hk = blockIdx.y / geo.row_groups, rg = blockIdx.y % geo.row_groups;
   const int G = p.heads_q / p.heads_kv;
   const int R = p.seqlen_q * G;  // query rows of this kv head: r = sq * G + gi
-  const int len = p.cache_seqlens[b] + (p.k_new ? p.seqlen_new : 0);
+  const int len_old = p.cache_seqlens[b];
+  const int n_new = p.k_new ? p.seqlen_new : 0;
+  const int len = len_old + n_new;
   const int pad = p.cache_leftpad ? p.cache_leftpad[b] : 0;
   const int k_begin = split * geo.chunk;
   if (k_begin >= len && split > 0) return;
@@ -143,7 +123,7 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
 #pragma unroll
       for (int i = tid; i < BN * CPR; i += NT) {
         const int r = i / CPR, c = i % CPR;
-        const bool ok = key0 + r < k_end;
+        const bool ok = key0 + r < min(k_end, len_old);     // new tokens are staged from k_new / v_new below
         const int rr = ok ? r : 0;
         cp_async16(smem_u32(dK + r * P + c * 8), kbase + kt + rr * p.kc_stride[1] + c * 8, ok ? 16 : 0);
         cp_async16(smem_u32(dV + r * P + c * 8), vbase + vt + rr * p.vc_stride[1] + c * 8, ok ? 16 : 0);
@@ -153,7 +133,7 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
     for (int i = tid; i < BN * CPR; i += NT) {
       const int r = i / CPR, c = i % CPR;
       const int key = key0 + r;
-      const bool ok = key < k_end;
+      const bool ok = key < min(k_end, len_old);
       const int pos = (ok ? key : k_begin) + pad;
       const int64_t ko = cache_row_offset(p, b, pos, geo.page_shift, p.kc_stride);
       const int64_t vo = cache_row_offset(p, b, pos, geo.page_shift, p.vc_stride);
@@ -221,6 +201,38 @@ __global__ void __launch_bounds__(128) decode_kernel(const fa_decode_args p, con
       const int nx = ti + NS - 1;
       if (nx < ntiles) load_tile(nx, nx % NS);
       cp_async_commit();
+    }
+    // ---- append: the new tokens of this tile, rotated, into the staged tile and the cache ----
+    {
+      const int key0 = k_begin + ti * BN;
+      const int first = max(key0, len_old), last = min(key0 + BN, k_end);   // new keys [first, last)
+      if (n_new > 0 && last > first) {
+        const T* cos = reinterpret_cast<const T*>(p.rotary_cos);
+        const T* sin = reinterpret_cast<const T*>(p.rotary_sin);
+        T* dK = sK + (ti % NS) * BN * P;
+        T* dV = sV + (ti % NS) * BN * P;
+        for (int i = tid; i < (last - first) * D; i += NT) {
+          const int key = first + i / D, d = i % D;
+          const int tok = key - len_old, pos = key + pad;
+          const T* kn = reinterpret_cast<const T*>(p.k_new) + b * p.kn_stride[0] + tok * p.kn_stride[1] +
+                        hk * p.kn_stride[2];
+          const T* vn = reinterpret_cast<const T*>(p.v_new) + b * p.vn_stride[0] + tok * p.vn_stride[1] +
+                        hk * p.vn_stride[2];
+          T kv = kn[d];
+          if (cos) kv = rotary_elem<T>([&](int j) { return kn[j]; }, d, cos, sin, pos, p.rotary_dim,
+                                         p.rotary_interleaved, p.rotary_seqlen);
+          const T vv = vn[d];
+          dK[(key - key0) * P + d] = kv;
+          dV[(key - key0) * P + d] = vv;
+          if (rg == 0) {
+            reinterpret_cast<T*>(p.k_cache)[cache_row_offset(p, b, pos, geo.page_shift, p.kc_stride) +
+                                            (int64_t)hk * p.kc_stride[2] + d] = kv;
+            reinterpret_cast<T*>(p.v_cache)[cache_row_offset(p, b, pos, geo.page_shift, p.vc_stride) +
+                                            (int64_t)hk * p.vc_stride[2] + d] = vv;
+          }
+        }
+        __syncthreads();
+      }
     }
     const T* cK = sK + (ti % NS) * BN * P + warp * 16 * P;
     const T* cV = sV + (ti % NS) * BN * P + warp * 16 * P;
@@ -459,11 +471,6 @@ static int launch_decode(const fa_decode_args& a, const ScoreCfg& cfg, const Dec
 
 template <typename T>
 static int decode_t(const fa_decode_args& a, const ScoreCfg& cfg, const DecodeGeom& g, cudaStream_t st) {
-  if (a.k_new) {
-    dim3 grid(a.heads_kv, a.seqlen_new, a.batch);
-    kv_append_kernel<T><<<grid, a.head_dim >= 128 ? 128 : 64, 0, st>>>(a, g.page_shift);
-    if (int r = check_launch("kv_append")) return r;
-  }
   switch (a.head_dim) {
     case 16: return launch_decode<T, 16>(a, cfg, g, st);
     case 32: return launch_decode<T, 32>(a, cfg, g, st);
