@@ -33,6 +33,7 @@
 //
 // Every mbarrier wait is bounded; on timeout the CTA raises a device-side status word,
 // releases its TMEM and returns.
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -782,7 +783,11 @@ int fwd_persist_sm100_status();
 int fwd_persist_sm100_clear_status();
 
 int fwd_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
-  if (FA_FWD_PERSISTENT_FROM > 0 && a.seqlen_k >= FA_FWD_PERSISTENT_FROM) return fwd_persist_sm100(a, cfg, st);
+  // FA_B200_FWD_PERSISTENT_FROM in the environment overrides the threshold (tests run the
+  // persistent kernel on small shapes with it; 0 = never)
+  int from = FA_FWD_PERSISTENT_FROM;
+  if (const char* e = getenv("FA_B200_FWD_PERSISTENT_FROM")) from = atoi(e);
+  if (from > 0 && a.seqlen_k >= from) return fwd_persist_sm100(a, cfg, st);
   // Row extents of the tensor maps.  Dense: the sequence length.  Packed: the caller does
   // not pass the total token count, so the map covers rows up to the int32 limit of the
   // cu_seqlens; tiles never start past cu_seqlens[batch], and rows past a sequence's end

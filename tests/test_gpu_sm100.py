@@ -111,3 +111,47 @@ def test_tcgen05_forward_query_tile_without_keys():
         empty_rows = slice(Sk + 50, Sq)  # query positions whose window [q-50, q+70] lies past the last key
         assert torch.count_nonzero(o[:, empty_rows]).item() == 0
         assert torch.isinf(lse[:, :, empty_rows]).all() and (lse[:, :, empty_rows] < 0).all()
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("feat", [0, 1, 3, 6])
+def test_persistent_forward_on_small_shapes(shape, feat, monkeypatch):
+    """The persistent forward kernel normally takes calls from 2048 keys up; here it is forced on
+    for the small shapes (ragged tiles, streams without tiles, items of one step) and must agree
+    with the oracle and, bit for bit, with the one-CTA-per-item kernel."""
+    from flash_attn_triton_b200 import _native as N, _ops
+    B, Sq, Sk, Hq, Hkv, D = shape
+    kw = FEATS[feat]
+    q, k, v, do = cases.dense_case(2100 + feat, B, Sq, Sk, Hq, Hkv, D)
+    sl = torch.tensor([[2.0 ** (-(i + 1)) for i in range(Hq)]] * B) if kw.get("alibi") else None
+    scale = 0.1 if feat >= 2 else 1.0 / np.sqrt(D)
+    args = (scale, kw.get("causal", False), kw.get("wl", -1), kw.get("wr", -1), kw.get("softcap", 0.0),
+            None if sl is None else sl.to(DEV), 0)
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "0")
+    o0, l0, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+    monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "1")
+    o1, l1, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+    o2, l2, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+    assert N.lib().fa_device_wait_status(0) == 0
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    assert torch.equal(o0, o1) and torch.equal(l0, l1)
+    ro, rl = orc.attention_ref(q, k, v, softmax_scale=scale, causal=kw.get("causal", False),
+                               window=(kw.get("wl", -1), kw.get("wr", -1)), softcap=kw.get("softcap", 0.0),
+                               alibi_slopes=sl)
+    assert maxdiff(o1, ro) <= util.FWD_TOL and maxdiff(l1 * LN2, rl) <= util.FWD_TOL
+
+
+def test_persistent_forward_packed(monkeypatch):
+    from flash_attn_triton_b200 import _native as N, _ops
+    lens = [100, 60, 300, 513, 1]
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(2200, lens, lens, 4, 2, 128)
+    args = (cu_q.to(DEV), cu_k.to(DEV), 513, 513, 128 ** -0.5, True, 200, 0, 0.0, None)
+    monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "0")
+    o0, l0, _ = _ops.varlen_forward(q.to(DEV), k.to(DEV), v.to(DEV), *args, N.IMPL_TCGEN05, True)
+    monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "1")
+    o1, l1, _ = _ops.varlen_forward(q.to(DEV), k.to(DEV), v.to(DEV), *args, N.IMPL_TCGEN05, True)
+    assert N.lib().fa_device_wait_status(0) == 0
+    assert torch.equal(o0, o1) and torch.equal(l0, l1)
+    ro, _ = orc.varlen_attention_ref(q, k, v, cu_q, cu_k, causal=True, window=(200, 0))
+    assert maxdiff(o1, ro) <= util.FWD_TOL
