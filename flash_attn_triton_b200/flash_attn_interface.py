@@ -436,11 +436,36 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
     q, k, v = _as_kernel_dtype(q, k, v)
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(q.shape[-1])
+    if dropout_p and deterministic and not return_attn_probs:
+        # The reference's deterministic path runs every sequence through its dense kernel
+        # (:660-681): one seed draw and dense dropout counters per sequence.  The kernels here
+        # are deterministic either way, so only this combination needs the same walk to
+        # reproduce the reference's masks.
+        if used_q is not None or used_k is not None:
+            q, cu_seqlens_q = (_compact_rows(q, cu_seqlens_q, used_q), _cu_of(used_q)) if used_q is not None \
+                else (q, cu_seqlens_q)
+            if used_k is not None:
+                k, v = _compact_rows(k, cu_seqlens_k, used_k), _compact_rows(v, cu_seqlens_k, used_k)
+                cu_seqlens_k = _cu_of(used_k)
+        both = torch.cat((cu_seqlens_q, cu_seqlens_k)).tolist()
+        cq, ck = both[:batch_size + 1], both[batch_size + 1:]
+        outs = []
+        for i in range(batch_size):
+            qp, kp, vp = q[cq[i]:cq[i + 1]], k[ck[i]:ck[i + 1]], v[ck[i]:ck[i + 1]]
+            if qp.shape[0] == 0:
+                outs.append(qp.new_empty((0, q.shape[1], q.shape[2])))
+            elif kp.shape[0] == 0:
+                outs.append(qp.new_zeros((qp.shape[0], q.shape[1], q.shape[2])))
+            else:
+                outs.append(_dense_call(qp.unsqueeze(0), kp.unsqueeze(0), vp.unsqueeze(0), dropout_p, softmax_scale,
+                                        causal, window_size, softcap,
+                                        None if alibi is None else alibi[i:i + 1], None, False, 0).squeeze(0))
+        return torch.cat(outs, dim=0).to(out_dtype)
     if dropout_p and used_q is not None:
         # The reference packs the used query rows before it launches (:552-566), so its dropout
         # counters run over the packed rows.  Do the same here, for this combination only.
         q = _compact_rows(q, cu_seqlens_q, used_q)
-        cu_seqlens_q = torch.cat([used_q.new_zeros(1), torch.cumsum(used_q, 0, dtype=torch.int32)])
+        cu_seqlens_q = _cu_of(used_q)
         used_q = None
         compacted = True
     else:
@@ -464,6 +489,10 @@ def flash_attn_varlen_func(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, ma
         out = _compact_rows(out, cu_seqlens_q, used_q)
     out = out.to(out_dtype)
     return (out, lse, probs) if return_attn_probs else out
+
+
+def _cu_of(lengths):
+    return torch.cat([lengths.new_zeros(1), torch.cumsum(lengths, 0, dtype=torch.int32)])
 
 
 def _compact_rows(x, cu_seqlens, used):

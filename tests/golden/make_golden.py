@@ -229,6 +229,15 @@ def dropout():
     blob["varlen.q_lens"], blob["varlen.k_lens"] = np.array(q_lens), np.array(k_lens)
     for n, t in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
         blob[f"varlen.{n}"] = t.detach().numpy()
+    # the deterministic packed path: one dense call, and one seed draw, per sequence (:660-681)
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    random.seed(77)
+    out = IF.flash_attn_varlen_func(qg, kg, vg, cu_q, cu_k, 130, 101, dropout_p=0.2, causal=True, deterministic=True)
+    dq, dk, dv = torch.autograd.grad((out.float() * do.float()).sum(), (qg, kg, vg))
+    random.seed(77)
+    blob["varlen_det.seeds"] = np.array([random.randrange(2 ** 31 - 1) for _ in q_lens])
+    for n, t in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+        blob[f"varlen_det.{n}"] = t.detach().numpy()
     np.savez_compressed(os.path.join(HERE, "dropout.npz"), **blob)
     print("wrote dropout")
 

@@ -61,6 +61,22 @@ def test_dropout_golden_varlen(golden):
         assert maxdiff(t, g["varlen." + n]) <= util.GRAD_TOL / 0.8, n
 
 
+def test_dropout_golden_varlen_deterministic(golden):
+    """deterministic=True walks the sequences like the reference does (one seed draw and dense
+    dropout counters per sequence), so its masks are reproduced too."""
+    g = golden("dropout")
+    ql, kl = g["varlen.q_lens"].tolist(), g["varlen.k_lens"].tolist()
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(9, ql, kl, 4, 2, 64)
+    qd, kd, vd = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    random.seed(77)
+    out = fa().flash_attn_varlen_func(qd, kd, vd, cu_q.to(DEV), cu_k.to(DEV), 130, 101, dropout_p=0.2, causal=True,
+                                      deterministic=True)
+    dq, dk, dv = grads(out, do, (qd, kd, vd))
+    assert maxdiff(out, g["varlen_det.out"]) <= util.FWD_TOL / 0.8
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t, g["varlen_det." + n]) <= util.GRAD_TOL / 0.8, n
+
+
 @pytest.mark.parametrize("shape", [(2, 200, 200, 4, 2, 128), (1, 333, 150, 2, 2, 64), (1, 64, 64, 2, 1, 16),
                                    (1, 150, 150, 2, 2, 256)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])

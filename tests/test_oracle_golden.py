@@ -214,3 +214,19 @@ def test_dropout_varlen(golden):
     assert maxdiff(out, g["varlen.out"]) <= FWD_TOL / 0.8
     for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
         assert maxdiff(t, g["varlen." + n]) <= GRAD_TOL / 0.8, n
+
+
+def test_dropout_varlen_deterministic(golden):
+    """deterministic=True: every sequence through the dense path with a seed of its own."""
+    g = golden("dropout")
+    ql, kl = g["varlen.q_lens"].tolist(), g["varlen.k_lens"].tolist()
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(9, ql, kl, 4, 2, 64)
+    seeds = g["varlen_det.seeds"].tolist()
+    for b in range(len(ql)):
+        qs, qe, ks, ke = int(cu_q[b]), int(cu_q[b + 1]), int(cu_k[b]), int(cu_k[b + 1])
+        out, _, _, dq, dk, dv = orc.attention_dropout_ref(q[qs:qe][None], k[ks:ke][None], v[ks:ke][None],
+                                                         do[qs:qe][None], dropout_p=0.2, seed=seeds[b], causal=True)
+        assert maxdiff(out[0], g["varlen_det.out"][qs:qe]) <= FWD_TOL / 0.8, b
+        assert maxdiff(dq[0], g["varlen_det.dq"][qs:qe]) <= GRAD_TOL / 0.8, b
+        assert maxdiff(dk[0], g["varlen_det.dk"][ks:ke]) <= GRAD_TOL / 0.8, b
+        assert maxdiff(dv[0], g["varlen_det.dv"][ks:ke]) <= GRAD_TOL / 0.8, b
