@@ -320,7 +320,7 @@ def apply_rotary_ref(x, cos, sin, positions, interleaved):
 def kvcache_ref(q, k_cache, v_cache, k_new=None, v_new=None, cos=None, sin=None,
                 cache_seqlens=None, cache_batch_idx=None, cache_leftpad=None,
                 block_table=None, softmax_scale=None, causal=False, window=(-1, -1),
-                rotary_interleaved=True, alibi_slopes=None):
+                rotary_interleaved=True, alibi_slopes=None, reference_alignment=False):
     """Append-then-attend against a contiguous or paged cache.
 
     This is the behaviour the reference's code is written to have
@@ -330,7 +330,10 @@ def kvcache_ref(q, k_cache, v_cache, k_new=None, v_new=None, cos=None, sin=None,
     reference the two `cache[idx, idx].copy_` lines at :487-492 write into a temporary,
     so its cache stays stale; tests pin the reference by doing the append themselves.)
     Query rows are bottom-right aligned for the causal mask (offset len_after-Sq, :523);
-    for window/ALiBi this oracle uses the same offset.
+    for window/ALiBi this oracle uses the same offset.  `reference_alignment=True` restates the
+    reference instead: without `causal` it measures window and ALiBi from query position 0
+    (flash_attn_interface.py:523 passes `_causal_offset=0`), which the library deliberately does
+    not do.
     Returns (out fp32 (B,Sq,Hq,D), k_cache_after, v_cache_after)."""
     kc = k_cache.clone()
     vc = v_cache.clone()
@@ -379,7 +382,7 @@ def kvcache_ref(q, k_cache, v_cache, k_new=None, v_new=None, cos=None, sin=None,
             sl = torch.as_tensor(alibi_slopes, dtype=torch.float32)
             sl = sl[b:b + 1] if sl.ndim == 2 else sl[None]
         o, _ = attention_ref(qb[None], kb[None], vb[None], softmax_scale, causal, window, 0.0,
-                             sl, q_pos_offset=L - Sq)
+                             sl, q_pos_offset=0 if (reference_alignment and not causal) else L - Sq)
         outs.append(o)
     return torch.cat(outs, dim=0), kc, vc
 

@@ -186,6 +186,14 @@ def kvcache():
     out = IF.flash_attn_with_kvcache(q, kc2, vc2, rotary_cos=cos, rotary_sin=sin,
                                      cache_seqlens=cl + 1, block_table=bt, causal=False,
                                      rotary_interleaved=False)
+    # The same call without `causal` but with a right window and ALiBi: the reference measures both
+    # from query position 0 here (:523), the library from the end of the sequence.  Stored so that
+    # the difference is pinned, not to be matched.
+    sl = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.03, 0.02, 0.01, 0.005])
+    out_nc = IF.flash_attn_with_kvcache(q, kc2, vc2, rotary_cos=cos, rotary_sin=sin, cache_seqlens=cl + 1,
+                                        block_table=bt, causal=False, rotary_interleaved=False,
+                                        window_size=(-1, 40), alibi_slopes=sl)
+    save("kvcache_noncausal_window", out=out_nc, slopes=sl)
     touched = torch.tensor([[int(bt[b, L // 64]), L % 64] for b, L in enumerate(lens)])
     save("kvcache_paged", checksum=cases.checksum(q, kc, vc, kn, vn, bt), out=out,
          touched=touched, k_rows=torch.stack([kc2[p, o] for p, o in touched.tolist()]),

@@ -50,6 +50,25 @@ def _contig_case(seed, B, Bc, cap, Hq, Hkv, D, Sq, Sn, dtype=torch.float16):
         (mk(B, Sn, Hkv, D) if Sn else None)
 
 
+def test_noncausal_window_alibi_is_bottom_right(golden):
+    """Without `causal`, window and ALiBi of a decode call are still measured from the end of the
+    sequence here.  The reference measures them from query position 0 in that case
+    (flash_attn_interface.py:523); its output is pinned in the golden so that the difference is a
+    known one (the CPU suite checks the oracle's restatement of the reference against it)."""
+    g = golden("kvcache_noncausal_window")
+    lens = golden("kvcache_paged")["lens"].tolist()
+    q, kc, vc, kn, vn, bt, cl = cases.paged_case(40, 3, 8, 2, 64, 64, 12, lens, 4)
+    cos, sin = cases.rotary_tables(256, 64)
+    sl = torch.from_numpy(g["slopes"])
+    out = fa().flash_attn_with_kvcache(dev(q), dev(kc), dev(vc), dev(kn), dev(vn), dev(cos), dev(sin),
+                                       cache_seqlens=dev(cl), block_table=dev(bt), rotary_interleaved=False,
+                                       causal=False, window_size=(-1, 40), alibi_slopes=dev(sl))
+    ro, _, _ = orc.kvcache_ref(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl, block_table=bt, causal=False,
+                               window=(-1, 40), alibi_slopes=sl, rotary_interleaved=False)
+    assert maxdiff(out, ro) <= util.FWD_TOL
+    assert maxdiff(out, g["out"]) > 0.05
+
+
 CONTIG = [
     # B, Bc, cap, Hq, Hkv, D, Sq, Sn, lens, kwargs
     (2, 2, 128, 4, 4, 64, 1, 1, [0, 100], dict()),

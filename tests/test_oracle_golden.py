@@ -230,3 +230,20 @@ def test_dropout_varlen_deterministic(golden):
         assert maxdiff(dq[0], g["varlen_det.dq"][qs:qe]) <= GRAD_TOL / 0.8, b
         assert maxdiff(dk[0], g["varlen_det.dk"][ks:ke]) <= GRAD_TOL / 0.8, b
         assert maxdiff(dv[0], g["varlen_det.dv"][ks:ke]) <= GRAD_TOL / 0.8, b
+
+
+def test_kvcache_noncausal_window_reference_alignment(golden):
+    """Without `causal` the reference measures window and ALiBi of a decode call from query
+    position 0 (flash_attn_interface.py:523); the oracle restates that behind a flag.  The library
+    measures them from the end of the sequence (tests/test_gpu_kvcache.py), a documented difference."""
+    g = golden("kvcache_noncausal_window")
+    lens = golden("kvcache_paged")["lens"].tolist()
+    q, kc, vc, kn, vn, bt, cl = cases.paged_case(40, 3, 8, 2, 64, 64, 12, lens, 4)
+    cos, sin = cases.rotary_tables(256, 64)
+    sl = torch.from_numpy(g["slopes"])
+    out, _, _ = orc.kvcache_ref(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl, block_table=bt, causal=False,
+                                window=(-1, 40), alibi_slopes=sl, rotary_interleaved=False, reference_alignment=True)
+    assert maxdiff(out, g["out"]) <= FWD_TOL
+    ours, _, _ = orc.kvcache_ref(q, kc, vc, kn, vn, cos, sin, cache_seqlens=cl, block_table=bt, causal=False,
+                                 window=(-1, 40), alibi_slopes=sl, rotary_interleaved=False)
+    assert maxdiff(ours, g["out"]) > 0.05          # the two conventions really differ on this case
