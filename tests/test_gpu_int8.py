@@ -137,8 +137,8 @@ def test_int8_value_errors():
 
 
 def test_config5_shape():
-    """B8 H32 S8192 D128 with 1 % x8 K outliers: codes/scales bit-exact on a slice (numpy
-    oracle), forward finite and checked on one (batch, head) against the int8-math oracle."""
+    """B8 H32 S8192 D128 with 1 % x8 K outliers: codes/scales bit-exact on four (batch, head)
+    slices (numpy oracle), forward finite and checked on the same four against the int8-math oracle."""
     from flash_attn_triton_b200 import _ops
     import flash_attn_triton_b200 as fa
     B, H, S, D = 8, 32, 8192, 128
@@ -148,13 +148,17 @@ def test_config5_shape():
     k = torch.randn(B, H, S, D, device=DEV, dtype=torch.float16, generator=g)
     k = torch.where(torch.rand(B, H, S, D, device=DEV, generator=g) < 0.01, k * 8, k)
     k8, s_k = _ops.quantize_k_int8(k)
-    r8, rs = orc.quantize_k_rows_ref(k[1, 2].cpu())
-    assert np.array_equal(k8[1, 2].cpu().numpy(), r8) and np.array_equal(s_k[1, 2].cpu().numpy(), rs)
+    slices = [(0, 0), (1, 2), (4, 17), (7, 31)]            # first, last and two in between
+    for b, h in slices:
+        r8, rs = orc.quantize_k_rows_ref(k[b, h].cpu())
+        assert np.array_equal(k8[b, h].cpu().numpy(), r8) and np.array_equal(s_k[b, h].cpu().numpy(), rs), (b, h)
     # dequantised codes reproduce k to half a step everywhere (size-independent property)
     err = (k8.float() * s_k[..., None] - k.float()).abs()
     assert (err <= 0.5001 * s_k[..., None]).all()
     for causal in (False, True):
         out = fa.attention_int8(q, k, v, causal=causal)
         assert torch.isfinite(out).all()
-        ro, _, _, _ = orc.attention_int8_ref(q[1:2, 2:3].cpu(), k[1:2, 2:3].cpu(), v[1:2, 2:3].cpu(), causal=causal)
-        assert maxdiff(out[1:2, 2:3], ro) <= util.FWD_TOL
+        for b, h in slices:
+            sl = (slice(b, b + 1), slice(h, h + 1))
+            ro, _, _, _ = orc.attention_int8_ref(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), causal=causal)
+            assert maxdiff(out[sl], ro) <= util.FWD_TOL, (b, h, causal)

@@ -150,15 +150,22 @@ def test_config3_shape_reduced_and_full():
     cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32, device=DEV)
     sl = torch.tensor([2.0 ** (-8 * (i + 1) / H) for i in range(H)], device=DEV)
     kw = dict(causal=True, window_size=(1024, 0), alibi_slopes=sl, softcap=30.0)
-    out = m.flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), **kw)
-    assert torch.isfinite(out).all()
+    do = torch.randn(T, H, D, device=DEV, dtype=torch.float16, generator=g)
+    qg, kg, vg = (t.detach().requires_grad_() for t in (q, k, v))
+    out = m.flash_attn_varlen_func(qg, kg, vg, cu, cu, max(lens), max(lens), **kw)
+    dq, dk, dv = torch.autograd.grad(out, (qg, kg, vg), do)
+    out = out.detach()
+    assert torch.isfinite(out).all() and all(torch.isfinite(t).all() for t in (dq, dk, dv))
     ones = m.flash_attn_varlen_func(q, k, torch.ones_like(v), cu, cu, max(lens), max(lens), **kw)
     assert (ones.float() - 1).abs().max().item() <= 2e-3
-    # shortest and longest sequence against the oracle, 2 heads
-    for b in (int(np.argmin(lens)), int(np.argmax(lens))):
+    # shortest, longest, first and last sequence against the oracle, 2 heads: output and gradients
+    # (every head has its own K/V here, so a head's slice of the gradients is self-contained)
+    for b in sorted({int(np.argmin(lens)), int(np.argmax(lens)), 0, len(lens) - 1}):
         s, e = int(cu[b]), int(cu[b + 1])
         hs = [0, H - 1]
-        ro, _ = orc.attention_ref(q[s:e, hs].cpu()[None], k[s:e, hs].cpu()[None], v[s:e, hs].cpu()[None],
-                                  causal=True, window=(1024, 0), softcap=30.0,
-                                  alibi_slopes=sl[hs].cpu())
-        assert maxdiff(out[s:e, hs], ro[0]) <= util.FWD_TOL
+        ro, _, rdq, rdk, rdv = orc.attention_grads_ref(
+            q[s:e, hs].cpu()[None], k[s:e, hs].cpu()[None], v[s:e, hs].cpu()[None], do[s:e, hs].cpu()[None],
+            causal=True, window=(1024, 0), softcap=30.0, alibi_slopes=sl[hs].cpu())
+        assert maxdiff(out[s:e, hs], ro[0]) <= util.FWD_TOL, b
+        for n, a, r in (("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+            assert maxdiff(a[s:e, hs], r[0]) <= util.GRAD_TOL, (b, n)
