@@ -253,3 +253,38 @@ def test_full_size_properties():
     assert maxdiff(vg.grad[b:b + 1, :, h:h + 1], rdv) <= util.GRAD_TOL
     # the other slices received a zero upstream gradient
     assert qg.grad[0].abs().max().item() == 0.0
+
+
+def test_lowlevel_attention_entry_points(golden):
+    """`attention` / `attention_varlen`, the operator layer under the public wrappers
+    (attention_kernel.py:1201-1259, :1364-1380 of the reference): head-major tensors, explicit
+    dropout seed, key-length mask and causal offset through seq_len_k / seq_len_q."""
+    from flash_attn_triton.triton_kernel.attention_kernel import attention, attention_varlen
+    g = golden("dense_c1_causal1")
+    q, k, v, do = cases.dense_case(0, 2, 128, 128, 4, 4, 64)
+    qh, kh, vh = (t.transpose(1, 2).contiguous().to(DEV).requires_grad_() for t in (q, k, v))
+    out = attention(qh, kh, vh, True, 0.125)
+    dq, dk, dv = torch.autograd.grad((out.float() * do.transpose(1, 2).to(DEV).float()).sum(), (qh, kh, vh))
+    assert maxdiff(out.transpose(1, 2), g["out"]) <= util.FWD_TOL
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert maxdiff(t.transpose(1, 2), g[n]) <= util.GRAD_TOL, n
+    # explicit seed: the mask is the oracle's Philox stream with counters row * S + col
+    q, k, v, do = cases.dense_case(16, 1, 192, 192, 2, 2, 64)
+    qh, kh, vh = (t.transpose(1, 2).contiguous().to(DEV) for t in (q, k, v))
+    out = attention(qh, kh, vh, False, None, 0.3, 4711)
+    ro = orc.attention_dropout_ref(q, k, v, dropout_p=0.3, seed=4711, row_stride=192)[0]
+    assert maxdiff(out.transpose(1, 2), ro) <= util.FWD_TOL / 0.7
+    # a padded call: 150 valid keys, queries shifted so that row i sits at position i + 30
+    out = attention(qh, kh, vh, True, None, 0.0, None, 150, 120)
+    ro, _ = orc.attention_ref(q, k[:, :150], v[:, :150], causal=True, q_pos_offset=30)
+    assert maxdiff(out.transpose(1, 2), ro) <= util.FWD_TOL
+    with pytest.raises(ValueError, match="equal sequence lengths"):
+        attention(qh, kh[:, :, :128], vh[:, :, :128])
+    with pytest.raises(ValueError, match="divisible by 64"):
+        attention(qh[:, :, :100], kh[:, :, :100], vh[:, :, :100])
+    # packed
+    ql = [37, 64, 130]
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(17, ql, ql, 4, 2, 64)
+    out = attention_varlen(q.to(DEV), k.to(DEV), v.to(DEV), cu_q.to(DEV), cu_k.to(DEV), 130, 130, True, None, 0.25, 99)
+    ro = orc.varlen_attention_dropout_ref(q, k, v, cu_q, cu_k, 130, dropout_p=0.25, seed=99, causal=True)[0]
+    assert maxdiff(out, ro) <= util.FWD_TOL / 0.75
