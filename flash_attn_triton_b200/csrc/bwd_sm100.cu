@@ -670,11 +670,16 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     };
     PROF_VARS(8);
     int posA = 0, posB = 0, wi = 0, tg = 0;          // tg: tiles issued so far by this CTA
+    // The last query tile of a packed sequence also stages rows of the NEXT sequence.  Their P is
+    // 0 (the statistics say so), but 0 * inf is NaN and dS^T Q, P^T dO contract over those rows:
+    // this warp, the first reader of every staged Q and dO tile, zeroes them once the tile has
+    // landed (scores and dP of those rows then are 0 too).
     // S^T = K Q^T (K from TMEM) - lse2 / scale_log2 for the tile at ring position qpos
-    auto issue_s = [&](int qpos, int tile_no) {
+    auto issue_s = [&](int qpos, int tile_no, int tail) {
       PROF_T0();
       wq(&sh->full_a[qpos % SQ], (qpos / SQ) & 1, 44);
       PROF_ADD(1);
+      if (ok && tail < kT) zero_tile_tail<C::kBoxes, kT>(slotA(qpos), tail, lane);
       PROF_T0();
       if (tile_no > 0) wq(&sh->r_free, 1, 49);                                  // the previous dP read out
       PROF_ADD(2);
@@ -698,12 +703,18 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (leader) mbar_arrive_cnt(smem_u32(&sh->empty_a[posA % SQ]), 2);
       __syncwarp();
       const int q0pos = posA + 1;
-      issue_s(q0pos, tg);
-      for (int i = 0; i < w.total && ok; ++i, ++tg) {
+      // the query tile that crosses the end of its sequence (-1: none) and its first row to zero;
+      // m_cur / m_nxt: query tile of stream position i / i + 1 (the tiles repeat per query head)
+      const int tail_m = (p.cu_seqlens_q != nullptr && (w.g.q_len % kT) != 0) ? w.g.q_len / kT : -1;
+      const int tail_first = w.g.q_len % kT, m_end = w.m_lo + w.ntiles;
+      int m_cur = w.m_lo, m_nxt = (w.m_lo + 1 == m_end) ? w.m_lo : w.m_lo + 1;
+      issue_s(q0pos, tg, m_cur == tail_m ? tail_first : kT);
+      for (int i = 0; i < w.total && ok; ++i, ++tg, m_cur = m_nxt, m_nxt = (m_nxt + 1 == m_end) ? w.m_lo : m_nxt + 1) {
         const int qpos = q0pos + i, opos = posB + i;
         PROF_T0();
         wq(&sh->full_b[opos % SO], (opos / SO) & 1, 44);
         PROF_ADD(3);
+        if (ok && m_cur == tail_m) zero_tile_tail<C::kBoxes, kT>(slotB(opos), tail_first, lane);
         PROF_T0();
         if (i == 0) wq(&sh->res_full, wi & 1, 43);                              // V of this item
         PROF_ADD(4);
@@ -717,7 +728,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (i + 1 < w.total) {
           mma_commit_lp(smem_u32(&sh->empty_b[opos % SO]), leader);   // this warp's last reads of dO(i) and of
           mma_commit_lp(smem_u32(&sh->empty_a[qpos % SQ]), leader);   // Q(i) and its statistics
-          issue_s(qpos + 1, tg + 1);
+          issue_s(qpos + 1, tg + 1, m_nxt == tail_m ? tail_first : kT);
         } else {
           mma_commit_lp(smem_u32(&sh->res_free), leader);             // ... and of V (the epilogue releases
         }                                                             // the last tile's ring entries)
@@ -1238,14 +1249,20 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!ok || w.total < 0) break;
       if (w.total == 0) continue;
       const int last = w.total - 1;
+      // The last key tile of a packed sequence (the first one visited) also stages rows of the NEXT
+      // sequence.  Their P is 0, but 0 * inf is NaN and dS K contracts over those rows: this warp,
+      // the first reader of every staged K and V tile, zeroes them once the tile has landed.
+      const int tail = p.cu_seqlens_k == nullptr ? kT : max(0, min(kT, w.g.k_len - (w.n_hi - 1) * kT));
       wq(&sh->res_full, wi & 1, 53);
       wq(&sh->full_a[posA % SK], (posA / SK) & 1, 54);
+      if (ok && tail < kT) zero_tile_tail<C::kBoxes, kT>(slotK(posA), tail, lane);
       if (ok) {
         mma_kmajor<D>(tS + (tg & 1) * kT, sQ, slotK(posA), idesc_s, leader);      // S(0) = Q K(0)^T
         mma_commit_lp(smem_u32(&sh->s_full[tg & 1]), leader);
         if (last == 0) mma_commit_lp(smem_u32(&sh->res_free), leader);
       }
       wq(&sh->full_b[posB % SV], (posB / SV) & 1, 54);
+      if (ok && tail < kT) zero_tile_tail<C::kBoxes, kT>(slotV(posB), tail, lane);
       if (ok) {
         mma_kmajor<D>(tdP, sdO, slotV(posB), idesc_s, leader);                    // dP(0) = dO V(0)^T
         mma_commit_lp(smem_u32(&sh->dp_full), leader);

@@ -166,6 +166,19 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
+// One warp zeroes rows [first, kRows) of a staged operand tile (128 bytes per row and 64-column
+// box, the rows of a box contiguous; zeros look the same under any swizzle) and orders the writes
+// before the reads of the async proxy that the warp's leader issues next.
+template <int kBoxes, int kRows>
+__device__ __forceinline__ void zero_tile_tail(uint32_t tile, int first, int lane) {
+#pragma unroll
+  for (int bx = 0; bx < kBoxes; ++bx) {
+    for (int o = first * 128 + lane * 16; o < kRows * 128; o += 512)
+      st_shared_v4(tile + bx * (kRows * 128) + o, make_uint4(0u, 0u, 0u, 0u));
+  }
+  fence_proxy_async();
+  __syncwarp();
+}
 
 // ---------------------------------------------------------------------------------------
 // TMEM

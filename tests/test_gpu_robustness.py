@@ -235,3 +235,31 @@ def test_packed_forward_ignores_non_finite_rows_of_the_next_sequence(causal):
         o = o.float().cpu()
         assert torch.isfinite(o[:100]).all() and torch.isfinite(o[160:]).all(), impl
         assert (o[:100] - ref[:100]).abs().max().item() <= 2e-3 and (o[160:] - ref[160:]).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("lens", [[100, 60, 300], [200, 60, 300], [3300, 60, 200]])
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_backward_ignores_non_finite_rows_of_the_next_sequence(lens, causal):
+    """Tail tiles of a packed sequence stage Q, K, V and dO rows of the next sequence.  dS = P (dP -
+    delta) is 0 * inf there, and dS K, dS^T Q and P^T dO contract over those rows: nothing of a
+    poisoned neighbour may reach the gradients of the other sequences (tcgen05 and mma.sync)."""
+    from flash_attn_triton_b200 import _native as N, _ops
+    q, k, v, do, cu_q, cu_k = cases.varlen_case(78, lens, lens, 2, 1, 128)
+    a, b = lens[0], lens[0] + lens[1]
+    bad = [t.clone() for t in (q, k, v, do)]
+    bad[0][a:b] = float("nan")
+    bad[1][a:b] = float("inf")
+    bad[2][a:b] = float("nan")
+    bad[3][a:b] = float("-inf")
+    _, _, rdq, rdk, rdv = orc.varlen_attention_grads_ref(q, k, v, do, cu_q, cu_k, causal=causal)
+    for impl in (N.IMPL_TCGEN05, N.IMPL_MMA):
+        qd, kd, vd, dod = (t.to(DEV) for t in bad)
+        args = (cu_q.to(DEV), cu_k.to(DEV), max(lens), max(lens), 128 ** -0.5, causal, -1, -1, 0.0, None, impl)
+        o, lse, _ = _ops.varlen_forward(qd, kd, vd, *args, True)
+        dq, dk, dv = _ops.varlen_backward(qd, kd, vd, o, lse, dod, *args)
+        assert N.lib().fa_device_wait_status(0) == 0
+        for g, r in zip((dq, dk, dv), (rdq, rdk, rdv)):
+            g = g.float().cpu()
+            assert torch.isfinite(g[:a]).all() and torch.isfinite(g[b:]).all(), impl
+            assert (g[:a] - r[:a]).abs().max().item() <= util.GRAD_TOL, impl
+            assert (g[b:] - r[b:]).abs().max().item() <= util.GRAD_TOL, impl
