@@ -956,7 +956,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             for (int i = 0; i < kHalfT; ++i) {
               const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
               float th;
-              float pe = ex2(score_log2_feat<kCap>(cfg, slope, sv, dist0 + (float)i, th) + st[i]);
+              float pe = ex2(score_log2_feat_add<kCap>(cfg, slope, sv, dist0 + (float)i, st[i], th));
               if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
               pf[i] = pe;
               // the tanh factor of the soft cap is folded into the copy kept for dS
@@ -1386,7 +1386,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int i = 0; i < kHalfT; ++i) {
               const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
               float th;
-              float pe = ex2(score_log2_feat<kCap>(cfg, slope, sv, dist0 - (float)i, th) - l2);
+              float pe = ex2(score_log2_feat_add<kCap>(cfg, slope, sv, dist0 - (float)i, -l2, th));
               if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
               if (kCap) pe *= (1.f - th * th);
               pf[i] = pe;

@@ -209,25 +209,44 @@ __device__ __forceinline__ float rcp_approx(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 // The same for the kernels that are compiled per feature set: ALiBi always applied (a zero slope
 // leaves the score unchanged, exactly), the soft cap selected at compile time.  Written so that
 // everything that does not depend on the element is a loop-invariant product the compiler hoists:
 //   no cap:  dot * scale_log2 - (slope log2e) |dist|                               2 instructions
-//   cap:     u = 2 log2e / cap * (dot * scale - slope |dist|),  r = 1 / (2^u + 1),
-//            tanh = 1 - 2 r,  score = cap log2e (1 - 2 r)                          2 + 2 MUFU + 2
-// (2^u = inf gives r = 0, tanh = 1; 2^u = 0 gives r = 1, tanh = -1: no special cases).
+//   cap:     tanh = tanh.approx((dot * scale - slope |dist|) / cap)                1 + 1 MUFU,
+//            score = cap log2e * tanh, which the caller folds into the FMA that forms the exp2
+//            argument (soft_cap_factor()).
+// tanh.approx.f32 has a relative error of 2^-11, the rounding of the 16-bit probabilities the
+// score ends up in; against the fp32 oracle the outputs and gradients of the packed feature tests
+// moved by less than their last digit when it replaced 1 - 2 / (2^u + 1) (two MUFU results and
+// three more instructions per score: the element-wise warps of these variants are MUFU-bound).
 template <bool kCap>
-__device__ __forceinline__ float score_log2_feat(const ScoreCfg& c, float slope, float dot, float dist, float& th) {
+__device__ __forceinline__ float score_unit_feat(const ScoreCfg& c, float slope, float dot, float dist, float& th) {
   if (!kCap) {
     th = 0.f;
     return fmaf(-(slope * FA_LOG2E), fabsf(dist), dot * c.scale_log2);
   }
-  const float k = c.inv_softcap * (2.f * FA_LOG2E);
-  const float u = fmaf(-(slope * k), fabsf(dist), dot * (c.scale * k));
-  const float r = rcp_approx(ex2(u) + 1.f);
-  th = fmaf(-2.f, r, 1.f);
-  const float cl = c.softcap * FA_LOG2E;
-  return fmaf(-2.f * cl, r, cl);
+  th = tanh_approx(fmaf(-(slope * c.inv_softcap), fabsf(dist), dot * (c.scale * c.inv_softcap)));
+  return th;
+}
+// score in the log2 domain = score_unit_feat() * soft_cap_factor()
+template <bool kCap> __device__ __forceinline__ float soft_cap_factor(const ScoreCfg& c) {
+  return kCap ? c.softcap * FA_LOG2E : 1.f;
+}
+// score in the log2 domain + addend (the negated row maximum or LSE), one FMA after the unit score
+template <bool kCap>
+__device__ __forceinline__ float score_log2_feat_add(const ScoreCfg& c, float slope, float dot, float dist,
+                                                     float addend, float& th) {
+  if (!kCap) {
+    th = 0.f;
+    return fmaf(-(slope * FA_LOG2E), fabsf(dist), fmaf(dot, c.scale_log2, addend));
+  }
+  return fmaf(score_unit_feat<true>(c, slope, dot, dist, th), c.softcap * FA_LOG2E, addend);
 }
 __device__ __forceinline__ float score_log2(const ScoreCfg& c, float slope, float dot, int qpos,
                                             int kpos, float& th, float bias = 0.f) {

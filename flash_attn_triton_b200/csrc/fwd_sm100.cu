@@ -482,7 +482,7 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               float v = __uint_as_float(r[cc][i]);
               if (kExtras) {
                 float th;
-                v = score_log2_feat<kCap>(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
+                v = score_unit_feat<kCap>(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
               } else {
                 v *= cfg.scale_log2;
               }
@@ -542,7 +542,10 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         mx = fmaxf(fmax3(mt[0], mt[1], mt[2]), fmaxf(fmax3(mt[3], mt[4], mt[5]), fmaxf(mt[6], mt[7])));
       }
-      if (!prescaled) mx *= cfg.scale_log2;  // scale >= 0 on this path
+      // what the stored values are multiplied by to give log2-domain scores: softmax_scale log2e
+      // on the plain path, cap log2e for capped scores (stored as tanh), else 1; all >= 0
+      const float mul = !prescaled ? cfg.scale_log2 : ((kExtras && cfg.softcap > 0.f) ? cfg.softcap * FA_LOG2E : 1.f);
+      mx *= mul;
       if (kInt8) mx *= sq_row;               // s_q > 0
 
 #ifdef FA_PROF
@@ -583,7 +586,6 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       prof_t1 = clock64();
 #endif
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      const float mul = prescaled ? 1.f : cfg.scale_log2;
 
       // ---- P = exp2(s - m), row sum, P -> TMEM in place over S ----------------------------
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
