@@ -473,9 +473,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // key side, scores:     [w_hi, w_lo, w_hi, w_lo, 0, 0, 0, 0]        with w = 1 / scale_log2
     // key side, dP:         [0, 0, 0, 0, 1, 1, 0, 0]
     // so the score GEMM yields S - lse2 / scale_log2 and the dP GEMM dP - delta.
-    // the plain variant multiplies K by scale_log2 on its way into tensor memory (below), so the
-    // score GEMM already works in the log2 domain and the LSE enters with weight 1
-    const float w = kExtras ? 1.f / cfg.scale_log2 : 1.f;
+    const float w = 1.f / cfg.scale_log2;
     const T w_hi = Elem<T>::from_f(w), w_lo = Elem<T>::from_f(w - Elem<T>::to_f(w_hi));
     const uint32_t wp = (uint32_t)(*reinterpret_cast<const uint16_t*>(&w_hi)) |
                         ((uint32_t)(*reinterpret_cast<const uint16_t*>(&w_lo)) << 16);
@@ -845,17 +843,6 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         kr[c / 4][(c % 4) * 4] = v.x; kr[c / 4][(c % 4) * 4 + 1] = v.y;
         kr[c / 4][(c % 4) * 4 + 2] = v.z; kr[c / 4][(c % 4) * 4 + 3] = v.w;
       }
-      if (!kExtras) {
-        // K * (softmax_scale * log2 e), rounded to T once per item (the reference rounds the
-        // scaled Q the same way, attention_kernel.py:492-495): the exp2 argument then comes out
-        // of the GEMM as it is and the element-wise warps save a multiply per score
-        const typename Elem<T>::T2 c2h = splat_pair<T>(cfg.scale_log2);
-#pragma unroll
-        for (int c = 0; c < kChunks / 4; ++c) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) kr[c][i] = mul_pair<T>(kr[c][i], c2h);
-        }
-      }
 #pragma unroll
       for (int c = 0; c < kChunks / 4; ++c) tmem_st16(tK + lane_addr + x * (D / 4) + c * 16, kr[c]);
       tmem_wait_st();
@@ -963,11 +950,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
               if (kCap) st[i] = 1.f - th * th;
             }
           } else {
+            const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2);
 #pragma unroll
             for (int i = 0; i < kHalfT; i += 2) {
               const uint32_t* rr = i < 32 ? r0 : r1;
-              // K came in scaled: the GEMM delivers the exp2 argument
-              const float2 a = make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1]));
+              const float2 a = f2mul(make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1])), c2);
               float2 pe = ex2_pair<kPolyEvery>(a, i >> 1);
               if (kMask) {
                 pe.x = col_visible(cm, i) ? pe.x : 0.f;

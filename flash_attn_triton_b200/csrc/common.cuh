@@ -355,16 +355,6 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
 };
 
-// a pair of T values (one 32-bit word) times a scalar pair, rounded to T
-template <typename T> __device__ __forceinline__ uint32_t mul_pair(uint32_t u, typename Elem<T>::T2 c) {
-  typename Elem<T>::T2 v = *reinterpret_cast<typename Elem<T>::T2*>(&u);
-  v = __hmul2(v, c);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <typename T> __device__ __forceinline__ typename Elem<T>::T2 splat_pair(float x);
-template <> __device__ __forceinline__ __half2 splat_pair<__half>(float x) { return __float2half2_rn(x); }
-template <> __device__ __forceinline__ __nv_bfloat162 splat_pair<__nv_bfloat16>(float x) { return __float2bfloat162_rn(x); }
-
 // ---------------------------------------------------------------------------------------
 // warp-level MMA toolkit (mma.sync m16n8k16, ldmatrix, cp.async)
 // ---------------------------------------------------------------------------------------
