@@ -155,3 +155,26 @@ def test_persistent_forward_packed(monkeypatch):
     assert torch.equal(o0, o1) and torch.equal(l0, l1)
     ro, _ = orc.varlen_attention_ref(q, k, v, cu_q, cu_k, causal=True, window=(200, 0))
     assert maxdiff(o1, ro) <= util.FWD_TOL
+
+
+@pytest.mark.parametrize("shape,kw", [
+    ((1, 16384, 16384, 2, 1, 128), dict(causal=True)),              # 128 key tiles per work item
+    ((1, 16384, 16384, 1, 1, 64), dict(causal=True, wl=3000)),      # a window that ends inside tiles
+    ((1, 700, 20000, 2, 2, 128), dict()),                           # short queries over a long context
+], ids=["causal16k", "window16k", "cross20k"])
+def test_long_sequences_vs_oracle(shape, kw):
+    """Sequences far beyond the benchmark's 4096: the ring positions, barrier parities and the work
+    queue of the persistent kernels wrap many times inside one item; every output and gradient
+    against the fp32 oracle."""
+    from flash_attn_triton_b200 import _native as N
+    B, Sq, Sk, Hq, Hkv, D = shape
+    q, k, v, do = cases.dense_case(4242, B, Sq, Sk, Hq, Hkv, D)
+    scale = 1.0 / np.sqrt(D)
+    out = _run(N.IMPL_TCGEN05, *(t.to(DEV) for t in (q, k, v, do)), scale, kw, None)
+    assert N.lib().fa_device_wait_status(0) == 0
+    ro, rl, rdq, rdk, rdv = orc.attention_grads_ref(q, k, v, do, softmax_scale=scale, causal=kw.get("causal", False),
+                                                    window=(kw.get("wl", -1), kw.get("wr", -1)))
+    assert maxdiff(out[0], ro) <= util.FWD_TOL
+    assert maxdiff(out[1] * LN2, rl) <= util.FWD_TOL
+    for t, r in zip(out[2:], (rdq, rdk, rdv)):
+        assert maxdiff(t, r) <= util.GRAD_TOL
