@@ -222,7 +222,7 @@ __device__ __forceinline__ float tanh_approx(float x) {
 //            score = cap log2e * tanh, which the caller folds into the FMA that forms the exp2
 //            argument (soft_cap_factor()).
 // tanh.approx.f32 has a relative error of 2^-11, the rounding of the 16-bit probabilities the
-// score ends up in; against the fp32 oracle the outputs and gradients of the packed feature tests
+// score ends up in; against an fp32 computation the outputs and gradients of the packed feature tests
 // moved by less than their last digit when it replaced 1 - 2 / (2^u + 1) (two MUFU results and
 // three more instructions per score: the element-wise warps of these variants are MUFU-bound).
 template <bool kCap>
