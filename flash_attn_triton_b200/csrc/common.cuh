@@ -158,8 +158,10 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // f in [-0.5, 0.5], a degree-3 minimax polynomial for 2^f (relative error 1.0e-4, below the
 // rounding of the 16-bit probabilities it feeds), n added into the exponent field; packed fp32,
 // about 5.5 issue slots per result.  Arguments below -125 return 2^-125 rather than 0, so masked
-// (-inf) scores must not come here.  Measured: no gain in any kernel (the element-wise warps are
-// short of issue slots too), so the kernels keep kEvery = 0.
+// (-inf) scores must not come here.  Measured: a loss wherever the caller keeps a whole row of
+// scores in registers (the polynomial wants ~10 more per pair in flight); a gain of 3-8 % in the
+// persistent forward on long items once the exp2 pass re-reads its scores from tensor memory in
+// chunks (fwd_persist_sm100.cu, kPoly).  The backward kernels keep kEvery = 0.
 __device__ __forceinline__ float2 ex2_fma2(float2 x) {
   x.x = fmaxf(x.x, -125.f);
   x.y = fmaxf(x.y, -125.f);

@@ -24,6 +24,7 @@
 // Every mbarrier wait is bounded; on timeout the CTA records a status, frees its TMEM and returns.
 #include <type_traits>
 
+#include <cstdlib>
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -138,7 +139,11 @@ __device__ __forceinline__ int sched_get(PShared* sh, int idx, bool& ok) {
 
 }  // namespace
 
-template <typename T, int D, bool kExtras>
+// kPoly > 0: on unmasked tiles of the plain variant every kPoly-th pair of exponentials runs on
+// the FMA pipe (ex2_fma2) and the scores are read from tensor memory a second time for the exp2
+// pass, 32 columns at a time and one chunk ahead, instead of staying in 128 registers (the
+// polynomial needs the registers; without them it was a loss).  The host picks it for long items.
+template <typename T, int D, bool kExtras, int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -533,7 +538,34 @@ fwd_persist_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 
         // ---- P = exp2(s - m), row sum, P -> TMEM in place over S ----------------------------
         // packed pairs: one FMA, two exponentials, one conversion and one add per two scores
-        {
+        if (kPoly > 0 && !prescaled) {
+          const float2 mul2 = make_float2(mul, mul), nm2 = make_float2(-m_safe, -m_safe);
+          float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+          uint32_t ra[32], rb[32];
+          tmem_ld32(tSx, ra);
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t (&cur)[32] = (cc & 1) ? rb : ra;
+            uint32_t (&nxt)[32] = (cc & 1) ? ra : rb;
+            tmem_wait_ld();
+            if (cc < 3) tmem_ld32(tSx + (cc + 1) * 32, nxt);
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float2 a = f2fma(make_float2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1])), mul2, nm2);
+              const float2 pe = ex2_pair<kPoly>(a, i >> 1);
+              pk[i >> 1] = Elem<T>::pack(pe.x, pe.y);
+              acc2[(i >> 1) & 1] = f2add(acc2[(i >> 1) & 1], pe);
+            }
+            tmem_st16(tSx + cc * 16, pk);
+            if (kPvSplit && cc == 1) {
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(smem_u32(&sh->p_half[x]));
+            }
+          }
+          l += (acc2[0].x + acc2[0].y) + (acc2[1].x + acc2[1].y);
+        } else {
           const float2 mul2 = make_float2(mul, mul), nm2 = make_float2(-m_safe, -m_safe);
           float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
@@ -692,7 +724,15 @@ static int launch_p(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st,
     return FA_ERR_LAUNCH;
   }
   const bool extras = cfg.has_alibi || cfg.softcap > 0.f;
-  auto kern = extras ? fwd_persist_sm100_kernel<T, D, true> : fwd_persist_sm100_kernel<T, D, false>;
+  // A quarter of the exponentials on the FMA pipe pays when both streams of a CTA spend most of
+  // their time in unmasked tiles: measured with launches interleaved, D = 128, -3 % at 16 key
+  // tiles per item without a mask, -6 % at 24, -8 % at 32; with the causal mask +3 % at 32 key
+  // tiles (16.5 per item on average), +-1 % at 48, -4 % at 64, -7.5 % at 128.
+  const int nk = (a.seqlen_k + kBN - 1) / kBN;
+  bool poly = !extras && !packed && cfg.wl < 0 && cfg.wr < 0 && nk >= (cfg.causal ? 64 : 16);
+  if (const char* e = getenv("FA_B200_FWD_POLY")) poly = !extras && atoi(e) != 0;   // tests: 0 = never, 1 = always
+  auto kern = extras ? fwd_persist_sm100_kernel<T, D, true, 0>
+                     : (poly ? fwd_persist_sm100_kernel<T, D, false, 4> : fwd_persist_sm100_kernel<T, D, false, 0>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) {
     set_error("fwd_persist_sm100: cudaFuncSetAttribute(%d): %s", C::kSmemBytes, cudaGetErrorString(e));

@@ -128,6 +128,7 @@ def test_persistent_forward_on_small_shapes(shape, feat, monkeypatch):
     args = (scale, kw.get("causal", False), kw.get("wl", -1), kw.get("wr", -1), kw.get("softcap", 0.0),
             None if sl is None else sl.to(DEV), 0)
     qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    monkeypatch.setenv("FA_B200_FWD_POLY", "0")       # both kernels with every exponential on the MUFU
     monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "0")
     o0, l0, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
     monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "1")
@@ -140,6 +141,34 @@ def test_persistent_forward_on_small_shapes(shape, feat, monkeypatch):
                                window=(kw.get("wl", -1), kw.get("wr", -1)), softcap=kw.get("softcap", 0.0),
                                alibi_slopes=sl)
     assert maxdiff(o1, ro) <= util.FWD_TOL and maxdiff(l1 * LN2, rl) <= util.FWD_TOL
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("feat", [0, 1, 3])
+def test_persistent_forward_with_fma_pipe_exponentials(shape, feat, monkeypatch):
+    """The variant of the persistent forward that the host picks for long items (a quarter of the
+    exponentials of unmasked tiles as a polynomial on the FMA pipe, scores re-read from tensor
+    memory), forced on for the small shapes: the oracle's bars hold and two runs agree bit for bit."""
+    from flash_attn_triton_b200 import _native as N, _ops
+    B, Sq, Sk, Hq, Hkv, D = shape
+    kw = FEATS[feat]
+    q, k, v, do = cases.dense_case(2300 + feat, B, Sq, Sk, Hq, Hkv, D)
+    scale = 0.1 if feat >= 2 else 1.0 / np.sqrt(D)
+    args = (scale, kw.get("causal", False), kw.get("wl", -1), kw.get("wr", -1), 0.0, None, 0)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    monkeypatch.setenv("FA_B200_FWD_PERSISTENT_FROM", "1")
+    monkeypatch.setenv("FA_B200_FWD_POLY", "1")
+    o1, l1, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+    o2, l2, _ = _ops.dense_forward(qd, kd, vd, *args, N.IMPL_TCGEN05, "bshd", True)
+    dq, dk, dv = _ops.dense_backward(qd, kd, vd, o1, l1, dod, *args, N.IMPL_TCGEN05, "bshd")
+    assert N.lib().fa_device_wait_status(0) == 0
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    ro, rl, rdq, rdk, rdv = orc.attention_grads_ref(q, k, v, do, softmax_scale=scale, causal=kw.get("causal", False),
+                                                    window=(kw.get("wl", -1), kw.get("wr", -1)))
+    assert maxdiff(o1, ro) <= util.FWD_TOL and maxdiff(l1 * LN2, rl) <= util.FWD_TOL
+    # the backward takes this forward's LSE
+    for t, r in zip((dq, dk, dv), (rdq, rdk, rdv)):
+        assert maxdiff(t, r) <= util.GRAD_TOL
 
 
 def test_persistent_forward_packed(monkeypatch):
