@@ -492,6 +492,14 @@ def int8_bench(dev, peaks):
                          "frac": tf / peaks["bf16"], "peak_source": peaks["source"] + " cuBLAS bf16 burst",
                          "int8_peak_tops": i8_peak, "mixed_peak": mixed_peak,
                          "frac_of_mixed": tf / mixed_peak if mixed_peak else None, "traffic": None}}
+        # the fp16 forward on the same tensors: what the INT8 path has to beat
+        from flash_attn_triton_b200 import _native as N
+        args = (1.0 / math.sqrt(Dq), causal, -1, -1, 0.0, None, 0, N.IMPL_AUTO, "bhsd", False)
+        for _ in range(2):
+            _ops.dense_forward(q, k, v, *args)
+        ms16 = event_time(lambda: _ops.dense_forward(q, k, v, *args), 3)
+        out["fp16_fwd_same_shape_causal" if causal else "fp16_fwd_same_shape"] = {
+            "ms": ms16, "tflops": fl / ms16 / 1e9, "frac_of_measured_peak": fl / ms16 / 1e9 / peaks["bf16"]}
     return out
 
 
