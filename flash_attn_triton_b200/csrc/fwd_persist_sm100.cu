@@ -727,9 +727,10 @@ static int launch_p(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st,
   // A quarter of the exponentials on the FMA pipe pays when both streams of a CTA spend most of
   // their time in unmasked tiles: measured with launches interleaved, D = 128, -3 % at 16 key
   // tiles per item without a mask, -6 % at 24, -8 % at 32; with the causal mask +3 % at 32 key
-  // tiles (16.5 per item on average), +-1 % at 48, -4 % at 64, -7.5 % at 128.
+  // tiles (16.5 per item on average), +-1 % at 48, -4 % at 64, -7.5 % at 128.  D = 64: -6 to -9 %
+  // without a mask from 16 key tiles up; causal +9 % at 16, +5 % at 32, 0 at 64, -4 % at 128.
   const int nk = (a.seqlen_k + kBN - 1) / kBN;
-  bool poly = !extras && !packed && cfg.wl < 0 && cfg.wr < 0 && nk >= (cfg.causal ? 64 : 16);
+  bool poly = !extras && !packed && cfg.wl < 0 && cfg.wr < 0 && nk >= (cfg.causal ? (D == 64 ? 128 : 64) : 16);
   if (const char* e = getenv("FA_B200_FWD_POLY")) poly = !extras && atoi(e) != 0;   // tests: 0 = never, 1 = always
   auto kern = extras ? fwd_persist_sm100_kernel<T, D, true, 0>
                      : (poly ? fwd_persist_sm100_kernel<T, D, false, 4> : fwd_persist_sm100_kernel<T, D, false, 0>);
