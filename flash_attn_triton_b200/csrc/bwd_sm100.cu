@@ -935,19 +935,48 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // columns (query rows) of this tile that see this thread's key
         const ColMask cm = make_col_mask(vq_lo - (q0 + off), vq_hi - (q0 + off));
         // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
-        auto exp_body = [&](auto mask_tag, auto cap_tag) {
+        auto exp_body = [&](auto mask_tag, auto cap_tag, auto abs_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
           constexpr bool kCap = decltype(cap_tag)::value;
+          constexpr bool kAbs = decltype(abs_tag)::value;
           if (kExtras) {
+            // Packed pairs throughout (the loop body is what the instruction cache has to hold:
+            // as 64 scalar chains this variant stalled more on instruction fetch than on anything
+            // else).  The distance of a pair's columns advances by (2, 2); under the causal mask
+            // every visible element has distance >= 0 and |.| is not needed.
+            const float ka = kCap ? -(slope * cfg.inv_softcap) : -(slope * FA_LOG2E);
+            const float kb = kCap ? cfg.scale * cfg.inv_softcap : cfg.scale_log2;
+            const float cl = cfg.softcap * FA_LOG2E;
+            const float2 ka2 = make_float2(ka, ka), kb2 = make_float2(kb, kb), cl2 = make_float2(cl, cl);
+            const float2 one2 = make_float2(1.f, 1.f), none2 = make_float2(-1.f, -1.f), two2 = make_float2(2.f, 2.f);
+            float2 d2 = make_float2(dist0, dist0 + 1.f);
 #pragma unroll
-            for (int i = 0; i < kHalfT; ++i) {
-              const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
-              float th;
-              float pe = ex2(score_log2_feat_add<kCap>(cfg, slope, sv, dist0 + (float)i, st[i], th));
-              if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
-              pf[i] = pe;
-              // the tanh factor of the soft cap is folded into the copy kept for dS
-              if (kCap) st[i] = 1.f - th * th;
+            for (int i = 0; i < kHalfT; i += 2) {
+              const uint32_t* rr = i < 32 ? r0 : r1;
+              const float2 sv2 = make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1]));
+              const float2 da = kAbs ? make_float2(fabsf(d2.x), fabsf(d2.y)) : d2;
+              const float2 st2 = make_float2(st[i], st[i + 1]);
+              float2 pe;
+              if (kCap) {
+                const float2 y2 = f2fma(ka2, da, f2mul(sv2, kb2));
+                const float2 th2 = make_float2(tanh_approx(y2.x), tanh_approx(y2.y));
+                const float2 a2 = f2fma(th2, cl2, st2);
+                pe = make_float2(ex2(a2.x), ex2(a2.y));
+                // the tanh factor of the soft cap is folded into the copy kept for dS
+                const float2 g2 = f2fma(f2mul(th2, th2), none2, one2);
+                st[i] = g2.x;
+                st[i + 1] = g2.y;
+              } else {
+                const float2 a2 = f2fma(ka2, da, f2fma(sv2, kb2, st2));
+                pe = make_float2(ex2(a2.x), ex2(a2.y));
+              }
+              if (kMask) {
+                pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+              }
+              pf[i] = pe.x;
+              pf[i + 1] = pe.y;
+              d2 = f2add(d2, two2);
             }
           } else {
             const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2);
@@ -966,13 +995,19 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
         };
         const bool cap = kExtras && cfg.softcap > 0.f;
-        if (masked) {
-          if (cap) exp_body(std::true_type{}, std::true_type{});
-          else exp_body(std::true_type{}, std::false_type{});
-        } else {
-          if (cap) exp_body(std::false_type{}, std::true_type{});
-          else exp_body(std::false_type{}, std::false_type{});
-        }
+        // |distance| only where a visible element can lie on the other side of the diagonal
+        const bool need_abs = kExtras && !cfg.causal;
+        auto run_exp = [&](auto mask_tag) {
+          if (cap) {
+            if (need_abs) exp_body(mask_tag, std::true_type{}, std::true_type{});
+            else exp_body(mask_tag, std::true_type{}, std::false_type{});
+          } else {
+            if (need_abs) exp_body(mask_tag, std::false_type{}, std::true_type{});
+            else exp_body(mask_tag, std::false_type{}, std::false_type{});
+          }
+        };
+        if (masked) run_exp(std::true_type{});
+        else run_exp(std::false_type{});
 #ifdef FA_PROF
         prof_acc[masked ? 13 : 12] += (unsigned int)(clock64() - prof_t1);
         if (masked) prof_acc[14] += 1;
@@ -996,7 +1031,11 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         if (kExtras && cfg.softcap > 0.f) {
 #pragma unroll
-          for (int i = 0; i < kHalfT; ++i) pf[i] *= st[i];
+          for (int i = 0; i < kHalfT; i += 2) {
+            const float2 g = f2mul(make_float2(pf[i], pf[i + 1]), make_float2(st[i], st[i + 1]));
+            pf[i] = g.x;
+            pf[i + 1] = g.y;
+          }
         }
         tmem_wait_st();
         tc_fence_before();
@@ -1365,18 +1404,32 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // columns (keys) of this tile that this thread's query row sees
         const ColMask cm = make_col_mask(vk_lo - k0, vk_hi - k0);
         // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
-        auto exp_body = [&](auto mask_tag, auto cap_tag) {
+        auto exp_body = [&](auto mask_tag, auto cap_tag, auto abs_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
           constexpr bool kCap = decltype(cap_tag)::value;
+          constexpr bool kAbs = decltype(abs_tag)::value;
           if (kExtras) {
+            // packed pairs; the distance of a pair's columns goes down by (2, 2)
+            const FeatK fk = feat_k<kCap>(cfg, slope);
+            const float cl = cfg.softcap * FA_LOG2E;
+            const float2 cl2 = make_float2(cl, cl), nl2 = make_float2(-l2, -l2);
+            const float2 one2 = make_float2(1.f, 1.f), none2 = make_float2(-1.f, -1.f), step2 = make_float2(-2.f, -2.f);
+            float2 d2 = make_float2(dist0, dist0 - 1.f);
 #pragma unroll
-            for (int i = 0; i < kHalfT; ++i) {
-              const float sv = __uint_as_float(i < 32 ? r0[i & 31] : r1[i & 31]);
-              float th;
-              float pe = ex2(score_log2_feat_add<kCap>(cfg, slope, sv, dist0 - (float)i, -l2, th));
-              if (kMask) pe = col_visible(cm, i) ? pe : 0.f;
-              if (kCap) pe *= (1.f - th * th);
-              pf[i] = pe;
+            for (int i = 0; i < kHalfT; i += 2) {
+              const uint32_t* rr = i < 32 ? r0 : r1;
+              const float2 sv2 = make_float2(__uint_as_float(rr[i & 31]), __uint_as_float(rr[(i & 31) + 1]));
+              const float2 u2 = score_unit_feat2<kCap, kAbs>(fk, sv2, d2);
+              const float2 a2 = kCap ? f2fma(u2, cl2, nl2) : f2add(u2, nl2);
+              float2 pe = make_float2(ex2(a2.x), ex2(a2.y));
+              if (kMask) {
+                pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+              }
+              if (kCap) pe = f2mul(pe, f2fma(f2mul(u2, u2), none2, one2));   // times 1 - tanh^2
+              pf[i] = pe.x;
+              pf[i + 1] = pe.y;
+              d2 = f2add(d2, step2);
             }
           } else {
             const float2 c2 = make_float2(cfg.scale_log2, cfg.scale_log2), nl = make_float2(-l2, -l2);
@@ -1395,13 +1448,18 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         };
         const bool cap = kExtras && cfg.softcap > 0.f;
-        if (masked) {
-          if (cap) exp_body(std::true_type{}, std::true_type{});
-          else exp_body(std::true_type{}, std::false_type{});
-        } else {
-          if (cap) exp_body(std::false_type{}, std::true_type{});
-          else exp_body(std::false_type{}, std::false_type{});
-        }
+        const bool need_abs = kExtras && !cfg.causal;    // under the causal mask visible keys lie at distance >= 0
+        auto run_exp = [&](auto mask_tag) {
+          if (cap) {
+            if (need_abs) exp_body(mask_tag, std::true_type{}, std::true_type{});
+            else exp_body(mask_tag, std::true_type{}, std::false_type{});
+          } else {
+            if (need_abs) exp_body(mask_tag, std::false_type{}, std::true_type{});
+            else exp_body(mask_tag, std::false_type{}, std::false_type{});
+          }
+        };
+        if (masked) run_exp(std::true_type{});
+        else run_exp(std::false_type{});
 
         // ---- dS phase --------------------------------------------------------------------
         ok = bwait(&sh->dp_full, tg & 1, sh, 57);

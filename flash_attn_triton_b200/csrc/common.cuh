@@ -236,6 +236,30 @@ __device__ __forceinline__ float score_unit_feat(const ScoreCfg& c, float slope,
   th = tanh_approx(fmaf(-(slope * c.inv_softcap), fabsf(dist), dot * (c.scale * c.inv_softcap)));
   return th;
 }
+// The same for a pair of scores with packed arithmetic (half the instructions: the unrolled score
+// loops of the feature variants are what the instruction cache has to hold).  d2 = the pair's
+// (query position - key position); kAbs = false where every visible element has d >= 0 (causal).
+struct FeatK {
+  float2 ka, kb;
+};
+template <bool kCap> __device__ __forceinline__ FeatK feat_k(const ScoreCfg& c, float slope) {
+  const float ka = kCap ? -(slope * c.inv_softcap) : -(slope * FA_LOG2E);
+  const float kb = kCap ? c.scale * c.inv_softcap : c.scale_log2;
+  FeatK k;
+  k.ka = make_float2(ka, ka);
+  k.kb = make_float2(kb, kb);
+  return k;
+}
+template <bool kCap, bool kAbs>
+__device__ __forceinline__ float2 score_unit_feat2(const FeatK& k, float2 dot2, float2 d2) {
+  if (kAbs) {
+    d2.x = fabsf(d2.x);
+    d2.y = fabsf(d2.y);
+  }
+  const float2 y = f2fma(k.ka, d2, f2mul(dot2, k.kb));
+  if (!kCap) return y;
+  return make_float2(tanh_approx(y.x), tanh_approx(y.y));
+}
 // score in the log2 domain = score_unit_feat() * soft_cap_factor()
 template <bool kCap> __device__ __forceinline__ float soft_cap_factor(const ScoreCfg& c) {
   return kCap ? c.softcap * FA_LOG2E : 1.f;

@@ -472,33 +472,55 @@ fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // score pipeline and mask applied once, in place; values end up in the log2 domain.
         // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
         const float dist0 = (float)(qpos - k0);
-        auto score_tile = [&](auto mask_tag, auto cap_tag) {
+        auto score_tile = [&](auto mask_tag, auto cap_tag, auto abs_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
           constexpr bool kCap = decltype(cap_tag)::value;
+          constexpr bool kAbs = decltype(abs_tag)::value;
+          if (kExtras) {
+            // packed pairs; the distance of a pair's columns goes down by (2, 2)
+            const FeatK fk = feat_k<kCap>(cfg, slope);
+            const float2 step2 = make_float2(-2.f, -2.f);
+            float2 d2 = make_float2(dist0, dist0 - 1.f);
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < 4; ++cc) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float v = __uint_as_float(r[cc][i]);
-              if (kExtras) {
-                float th;
-                v = score_unit_feat<kCap>(cfg, slope, v, dist0 - (float)(cc * 32 + i), th);
-              } else {
-                v *= cfg.scale_log2;
+              for (int i = 0; i < 32; i += 2) {
+                float2 v = score_unit_feat2<kCap, kAbs>(
+                    fk, make_float2(__uint_as_float(r[cc][i]), __uint_as_float(r[cc][i + 1])), d2);
+                if (kMask) {
+                  v.x = col_visible(cm, cc * 32 + i) ? v.x : -INFINITY;
+                  v.y = col_visible(cm, cc * 32 + i + 1) ? v.y : -INFINITY;
+                }
+                r[cc][i] = __float_as_uint(v.x);
+                r[cc][i + 1] = __float_as_uint(v.y);
+                d2 = f2add(d2, step2);
               }
-              if (kMask) v = col_visible(cm, cc * 32 + i) ? v : -INFINITY;
-              r[cc][i] = __float_as_uint(v);
+            }
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float v = __uint_as_float(r[cc][i]) * cfg.scale_log2;
+                if (kMask) v = col_visible(cm, cc * 32 + i) ? v : -INFINITY;
+                r[cc][i] = __float_as_uint(v);
+              }
             }
           }
         };
         const bool cap = kExtras && cfg.softcap > 0.f;
-        if (masked) {
-          if (cap) score_tile(std::true_type{}, std::true_type{});
-          else score_tile(std::true_type{}, std::false_type{});
-        } else {
-          if (cap) score_tile(std::false_type{}, std::true_type{});
-          else score_tile(std::false_type{}, std::false_type{});
-        }
+        const bool need_abs = kExtras && !cfg.causal;    // under the causal mask visible keys lie at distance >= 0
+        auto run_score = [&](auto mask_tag) {
+          if (cap) {
+            if (need_abs) score_tile(mask_tag, std::true_type{}, std::true_type{});
+            else score_tile(mask_tag, std::true_type{}, std::false_type{});
+          } else {
+            if (need_abs) score_tile(mask_tag, std::false_type{}, std::true_type{});
+            else score_tile(mask_tag, std::false_type{}, std::false_type{});
+          }
+        };
+        if (masked) run_score(std::true_type{});
+        else run_score(std::false_type{});
       }
 
       // ---- packed batches: keep the next sequence's values out of P V ---------------------
