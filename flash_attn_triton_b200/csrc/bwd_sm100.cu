@@ -935,11 +935,12 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // columns (query rows) of this tile that see this thread's key
         const ColMask cm = make_col_mask(vq_lo - (q0 + off), vq_hi - (q0 + off));
         // One body, compiled per (masked tile, soft cap): no branch inside the unrolled loops.
+        uint32_t pkx[kExtras ? 32 : 1];                // feature variant: P as T pairs, packed inside the loop
         auto exp_body = [&](auto mask_tag, auto cap_tag, auto abs_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
           constexpr bool kCap = decltype(cap_tag)::value;
           constexpr bool kAbs = decltype(abs_tag)::value;
-          if (kExtras) {
+          if constexpr (kExtras) {
             // Packed pairs throughout (the loop body is what the instruction cache has to hold:
             // as 64 scalar chains this variant stalled more on instruction fetch than on anything
             // else).  The distance of a pair's columns advances by (2, 2); under the causal mask
@@ -962,17 +963,21 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const float2 th2 = make_float2(tanh_approx(y2.x), tanh_approx(y2.y));
                 const float2 a2 = f2fma(th2, cl2, st2);
                 pe = make_float2(ex2(a2.x), ex2(a2.y));
-                // the tanh factor of the soft cap is folded into the copy kept for dS
-                const float2 g2 = f2fma(f2mul(th2, th2), none2, one2);
-                st[i] = g2.x;
-                st[i + 1] = g2.y;
+                if (kMask) {
+                  pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                  pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+                }
+                pkx[i >> 1] = Elem<T>::pack(pe.x, pe.y);
+                // the tanh factor of the soft cap goes into the copy kept for dS
+                pe = f2mul(pe, f2fma(f2mul(th2, th2), none2, one2));
               } else {
                 const float2 a2 = f2fma(ka2, da, f2fma(sv2, kb2, st2));
                 pe = make_float2(ex2(a2.x), ex2(a2.y));
-              }
-              if (kMask) {
-                pe.x = col_visible(cm, i) ? pe.x : 0.f;
-                pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+                if (kMask) {
+                  pe.x = col_visible(cm, i) ? pe.x : 0.f;
+                  pe.y = col_visible(cm, i + 1) ? pe.y : 0.f;
+                }
+                pkx[i >> 1] = Elem<T>::pack(pe.x, pe.y);
               }
               pf[i] = pe.x;
               pf[i + 1] = pe.y;
@@ -1020,21 +1025,21 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           if (!ok) break;
           tc_fence_after();
         }
-        {
+        if constexpr (kExtras) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pkx[c * 16 + i];
+            tmem_st16(tXx + c * 16, pk);
+          }
+        } else {
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
             tmem_st16(tXx + c * 16, pk);
-          }
-        }
-        if (kExtras && cfg.softcap > 0.f) {
-#pragma unroll
-          for (int i = 0; i < kHalfT; i += 2) {
-            const float2 g = f2mul(make_float2(pf[i], pf[i + 1]), make_float2(st[i], st[i + 1]));
-            pf[i] = g.x;
-            pf[i + 1] = g.y;
           }
         }
         tmem_wait_st();
