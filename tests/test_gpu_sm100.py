@@ -25,6 +25,8 @@ FEATS = [
     dict(causal=False), dict(causal=True), dict(causal=True, wl=100, wr=0), dict(causal=False, wl=50, wr=70),
     dict(causal=True, softcap=10.0), dict(causal=True, alibi=True),
     dict(causal=True, wl=200, wr=0, softcap=30.0, alibi=True),
+    # keys on both sides of the diagonal: ALiBi needs |distance|
+    dict(causal=False, alibi=True), dict(causal=False, wl=300, wr=100, softcap=20.0, alibi=True),
 ]
 
 
