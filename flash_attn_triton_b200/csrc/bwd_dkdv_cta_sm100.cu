@@ -10,7 +10,8 @@
 //   GQA group) that can see them, on the TRANSPOSED tiles S^T = K Q^T, dP^T = V dO^T so that a TMEM
 //   lane is a key; P^T and dS^T go back to TMEM and feed dV += P^T dO, dK += dS^T Q as the A operand.
 //   Row statistics (-lse2, -delta) ride in the GEMMs through 16-column operand tiles.
-//   TMEM: R (128 fp32 columns: S^T, then dP^T) | X (64: P^T, then dS^T) | K (64) | dV (128) | dK (128).
+//   TMEM: R (128 fp32 columns: S^T, then dP^T) | P^T (64) | dS^T (64) | dV (128) | dK (128); K and V
+//   stay in shared memory.
 #include <cstddef>
 #include <type_traits>
 
@@ -43,12 +44,11 @@ static_assert((kRegsEw - 168) * 256 <= (168 - kRegsService) * 128, "register spl
 template <int D> struct BCfg {
   static constexpr int kTileBytes = kT * D * 2;
   static constexpr int kBoxes = D / 64;
-  // dK/dV kernel: V resident, a ring of Q tiles (one stage deeper than dO's: Q(i) lives from
-  // S(i) to dK(i), dO(i) only from dP(i) to dV(i)) whose last slot receives K first -- K moves to
-  // TMEM before the loop -- and a ring of dO tiles.
-  static constexpr int kStagesQ = (D == 128) ? 3 : 4;
+  // dK/dV kernel: V and K resident, a ring of Q tiles (Q(i) lives from S(i) to dK(i)) and a ring of
+  // dO tiles (dO(i) from dP(i) to dV(i)).
+  static constexpr int kStagesQ = (D == 128) ? 2 : 3;
   static constexpr int kStagesO = (D == 128) ? 2 : 4;
-  static constexpr int kSmemTiles = (1 + kStagesQ + kStagesO) * kTileBytes;
+  static constexpr int kSmemTiles = (2 + kStagesQ + kStagesO) * kTileBytes;
   // dK/dV kernel: 128 x 16 operand tiles that carry the row statistics into the GEMMs
   // (two constant ones on the key side, one per ring stage on the query side)
   static constexpr int kAugBytes = kT * 16 * 2;
@@ -80,7 +80,6 @@ struct BShared {
   uint64_t r_free;        // dK/dV kernel: scores, then dP, read out of their shared TMEM region (256 arrivals)
   uint64_t p_free;        // dK/dV kernel: dV MMA that read P finished
   uint64_t ds_free;       // dK/dV kernel: dK MMA that read dS finished
-  uint64_t k_copied;      // dK/dV kernel: K copied from its landing slot into TMEM (256 arrivals)
   uint64_t acc_done;      // every accumulation MMA finished
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -172,9 +171,8 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   BShared* sh = reinterpret_cast<BShared*>(tiles + C::kSmemTiles + C::kAugTotal);
-  const uint32_t sV = smem_u32(tiles);
-  const uint32_t sRingQ = sV + C::kTileBytes, sRingO = sRingQ + C::kStagesQ * C::kTileBytes;
-  const uint32_t sKland = sRingQ + (C::kStagesQ - 1) * C::kTileBytes;  // K lands in the last Q slot
+  const uint32_t sV = smem_u32(tiles), sK = sV + C::kTileBytes;
+  const uint32_t sRingQ = sK + C::kTileBytes, sRingO = sRingQ + C::kStagesQ * C::kTileBytes;
   // statistics operands: [0] key side of the score GEMM, [1] key side of the dP GEMM,
   // [2 + stage] query side (written per streamed query tile by the statistics warp)
   unsigned char* aug = tiles + C::kSmemTiles;
@@ -206,7 +204,6 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(smem_u32(&sh->p_free), 1);
     mbar_init(smem_u32(&sh->ds_free), 1);
     mbar_init(smem_u32(&sh->acc_done), 1);
-    mbar_init(smem_u32(&sh->k_copied), 256);
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&sh->full_a[i]), 2);   // the TMA load of Q and the statistics warp
       mbar_init(smem_u32(&sh->full_b[i]), 1);
@@ -245,8 +242,8 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
-  // TMEM: R (128 fp32 columns: S^T, then dP^T of a tile) | X (64: P^T, then dS^T) | K (64) | dV | dK
-  const uint32_t tR = tmem, tX = tmem + 128, tK = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
+  // TMEM: R (128 fp32 columns: S^T, then dP^T of a tile) | P^T (64) | dS^T (64) | dV | dK
+  const uint32_t tR = tmem, tXp = tmem + 128, tXs = tmem + 192, tdV = tmem + 256, tdK = tmem + 384;
 
   if (warp == 8) {
     // ------------------------------- TMA producer ---------------------------------------
@@ -259,15 +256,14 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       {
         const uint32_t bar = smem_u32(&sh->res_full);
         mbar_expect_tx(bar, 2 * C::kTileBytes);
-        load_tile<D>(sKland, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
+        load_tile<D>(sK, &tmK, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
         load_tile<D>(sV, &tmV, bar, (int)si.k_row0 + n0, hk, (int)si.k_boff);
       }
       for (int it = 0; it < total; ++it) {
         const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
         const int sq = it % C::kStagesQ, so = it % C::kStagesO;
-        // Q's slot frees after dK of the tile that held it; the last slot holds K at first
+        // Q's slot frees after dK of the tile that held it
         if (!bwait_relaxed(&sh->empty_a[sq], ((it / C::kStagesQ) & 1) ^ 1, sh, 41)) break;
-        if (it == C::kStagesQ - 1 && !bwait_relaxed(&sh->k_copied, 0, sh, 41)) break;
         {
           const uint32_t bar = smem_u32(&sh->full_a[sq]);
           mbar_expect_tx(bar, C::kTileBytes);
@@ -354,14 +350,14 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       const uint64_t dstat_s = make_smem_desc_noswizzle(sAug, 2048, 128);
       const uint64_t dstat_dp = make_smem_desc_noswizzle(sAug + C::kAugBytes, 2048, 128);
-      // S^T(i) = K Q(i)^T (K from TMEM) - lse2 / scale_log2; waits for Q(i) and its statistics
+      // S^T(i) = K Q(i)^T - lse2 / scale_log2; waits for Q(i) and its statistics
       auto issue_s = [&](int i) {
         const int st = i % C::kStagesQ;
         const uint32_t ph = (i / C::kStagesQ) & 1;
         wq(&sh->full_a[st], ph, 44);
         if (i > 0) wq(&sh->r_free, 1, 49);                                     // dP(i-1) read out
         if (!ok) return;
-        mma_kmajor_ts<D>(tR, tK, slotQ(i), idesc_s, leader);
+        mma_kmajor<D>(tR, sK, slotQ(i), idesc_s, leader);
         if (!kExtras) mma_f16_ss_lp(tR, dstat_s, stat_desc(i), idesc_s, 1u, leader);
         mma_commit_lp(smem_u32(&sh->s_full[0]), leader);
       };
@@ -370,7 +366,6 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // accumulating GEMMs dV(i), dK(i) that read P, dS from region X.  The exp2 phase of tile
       // i+1 runs under dK(i), dP(i+1); its dS phase under dV(i+1), S(i+2).
       wq(&sh->res_full, 0, 43);
-      wq(&sh->k_copied, 0, 43);
       issue_s(0);
       for (int i = 0; i < total && ok; ++i) {
         const int st = i % C::kStagesQ, so = i % C::kStagesO;
@@ -402,13 +397,15 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // dO(i) may land after P(i) is ready; Q(i) has been read by S(i) long before dS(i) exists
         wq(&sh->full_b[so], (i / C::kStagesO) & 1, 44);
         wq(&sh->p_ready, i & 1, 45);
-        if (!ok) break;
-        mma_from_tmem<D, 32>(tdV, tX, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader);  // dV += P(i)^T dO(i)
-        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
-        mma_commit_lp(smem_u32(&sh->p_free), leader);
+        // Both accumulations are issued once dS(i) is stored: S(i+1), which the other issuer queues as
+        // soon as dP(i) has been read, then runs ahead of dV(i), and the element-wise warps find
+        // their next scores ready (P and dS have regions of their own, so nothing waits for dV).
         wq(&sh->ds_ready, i & 1, 46);
         if (!ok) break;
-        mma_from_tmem<D, 32>(tdK, tX, sRingQ + st * C::kTileBytes, idesc_acc, i > 0, leader);  // dK += dS(i)^T Q(i)
+        mma_from_tmem<D, 32>(tdV, tXp, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader); // dV += P(i)^T dO(i)
+        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
+        mma_commit_lp(smem_u32(&sh->p_free), leader);
+        mma_from_tmem<D, 32>(tdK, tXs, sRingQ + st * C::kTileBytes, idesc_acc, i > 0, leader); // dK += dS(i)^T Q(i)
         mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
         mma_commit_lp(smem_u32(&sh->ds_free), leader);
       }
@@ -423,29 +420,9 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int key = n0 + lrow;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tRx = tR + lane_addr + x * kHalfT;            // fp32 scores / dP: this group's 64 columns
-    const uint32_t tXx = tX + lane_addr + x * (kHalfT / 2);      // P^T, then dS^T, as 16-bit pairs: 32 columns
+    const uint32_t tXpx = tXp + lane_addr + x * (kHalfT / 2);    // P^T as 16-bit pairs: 32 columns
+    const uint32_t tXsx = tXs + lane_addr + x * (kHalfT / 2);    // dS^T, a region of its own
     bool ok = true;
-    if (total > 0) {
-      // K: from its landing slot (which then joins the Q ring) into TMEM, where the score GEMM
-      // reads it as the A operand.  This thread copies its key row, group x the x-th half of it.
-      ok = bwait(&sh->res_full, 0, sh, 43);
-      if (ok) {
-        constexpr int kChunks = D / 16;              // 16-byte chunks per group
-        uint32_t kr[kChunks / 4][16];
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int g = x * kChunks + c;
-          const uint4 v = ld_shared_v4(sw128_addr(sKland + (g / 8) * (kT * 128), lrow, g % 8));
-          kr[c / 4][(c % 4) * 4] = v.x; kr[c / 4][(c % 4) * 4 + 1] = v.y;
-          kr[c / 4][(c % 4) * 4 + 2] = v.z; kr[c / 4][(c % 4) * 4 + 3] = v.w;
-        }
-#pragma unroll
-        for (int c = 0; c < kChunks / 4; ++c) tmem_st16(tK + lane_addr + x * (D / 4) + c * 16, kr[c]);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&sh->k_copied));
-      }
-    }
     for (int it = 0; it < total && ok; ++it) {
       const int stage = it % C::kStagesQ;
       const int hq = hk * G + it / ntiles, m = m_lo + it % ntiles;
@@ -517,9 +494,9 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       if (kExtras || masked) exp_body(std::true_type{});
       else exp_body(std::false_type{});
-      // X holds dS(it-1) until its dK MMA has finished (ds_free)
+      // the P region holds P(it-1) until its dV MMA has finished (p_free): long ago by now
       if (it > 0) {
-        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 50);
+        ok = bwait(&sh->p_free, (it - 1) & 1, sh, 51);
         if (!ok) break;
         tc_fence_after();
       }
@@ -529,7 +506,7 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = Elem<T>::pack(pf[c * 32 + 2 * i], pf[c * 32 + 2 * i + 1]);
-          tmem_st16(tXx + c * 16, pk);
+          tmem_st16(tXpx + c * 16, pk);
         }
       }
       if (kExtras && cfg.softcap > 0.f) {
@@ -559,12 +536,15 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (i < 16) pk0[i] = Elem<T>::pack(ds.x, ds.y);
         else pk1[i - 16] = Elem<T>::pack(ds.x, ds.y);
       }
-      // X holds P(it) until its dV MMA has finished (p_free)
-      ok = bwait(&sh->p_free, it & 1, sh, 51);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_st16(tXx, pk0);
-      tmem_st16(tXx + 16, pk1);
+      // the dS region holds dS(it-1) until its dK MMA has finished (ds_free): dS does not wait for
+      // the dV MMA of this tile, which still reads P from the other region
+      if (it > 0) {
+        ok = bwait(&sh->ds_free, (it - 1) & 1, sh, 50);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      tmem_st16(tXsx, pk0);
+      tmem_st16(tXsx + 16, pk1);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&sh->ds_ready));
