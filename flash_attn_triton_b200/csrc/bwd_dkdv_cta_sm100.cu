@@ -402,12 +402,14 @@ bwd_dkdv_cta_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // their next scores ready (P and dS have regions of their own, so nothing waits for dV).
         wq(&sh->ds_ready, i & 1, 46);
         if (!ok) break;
-        mma_from_tmem<D, 32>(tdV, tXp, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader); // dV += P(i)^T dO(i)
-        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
-        mma_commit_lp(smem_u32(&sh->p_free), leader);
+        // dK first: it releases the Q slot, and the two-stage Q ring needs that slot back for Q(i+2)
+        // well before S(i+2); dO(i)'s slot is not wanted before dP(i+2)
         mma_from_tmem<D, 32>(tdK, tXs, sRingQ + st * C::kTileBytes, idesc_acc, i > 0, leader); // dK += dS(i)^T Q(i)
         mma_commit_lp(smem_u32(&sh->empty_a[st]), leader);
         mma_commit_lp(smem_u32(&sh->ds_free), leader);
+        mma_from_tmem<D, 32>(tdV, tXp, sRingO + so * C::kTileBytes, idesc_acc, i > 0, leader); // dV += P(i)^T dO(i)
+        mma_commit_lp(smem_u32(&sh->empty_b[so]), leader);
+        mma_commit_lp(smem_u32(&sh->p_free), leader);
       }
       mma_commit_lp(smem_u32(&sh->acc_done), leader);
       __syncwarp();
