@@ -1,10 +1,9 @@
-// dK, dV with one CTA per block of 128 keys (grid = key blocks x kv heads x batch): the same roles,
-// tensor-memory layout and pipeline as the persistent kernel of bwd_sm100.cu, without its work
-// queue.  Measured on B200: when a key block meets few query tiles (a causal mask at moderate
-// sequence lengths: 16 tiles on average at 4096), handing the SM to a fresh CTA costs less than the
-// hand-over between items inside a persistent CTA, and this kernel is ~6 % faster; with long
-// items, packed batches and the ALiBi / soft-cap variants the persistent kernel wins.  The host
-// side of bwd_sm100.cu picks between the two.
+// dK, dV with one CTA per block of 128 keys (grid = key blocks x kv heads x batch): the roles of
+// the persistent kernel of bwd_sm100.cu without its work queue, and with K kept in shared memory so
+// that P^T and dS^T each have tensor-memory columns of their own.  Measured on B200 it is the
+// faster of the two on every plain dense shape (2-7 % without a mask, 10-15 % with the causal mask
+// or GQA); the host side of bwd_sm100.cu sends those here and packed batches and the ALiBi /
+// soft-cap variants to the persistent kernel.
 //
 //   CTA = 128 keys of one (batch, kv head); loops over the query tiles (and the query heads of the
 //   GQA group) that can see them, on the TRANSPOSED tiles S^T = K Q^T, dP^T = V dO^T so that a TMEM

@@ -44,6 +44,7 @@
 #include <cstddef>
 #include <type_traits>
 
+#include <cstdlib>
 #include "common.cuh"
 #define PROF_TAG bwd
 #include "prof.cuh"
@@ -1644,6 +1645,9 @@ int launch_dq(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
 
 int bwd_dkdv_cta_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st);
 
+#ifndef FA_DKDV_CTA_BELOW
+#define FA_DKDV_CTA_BELOW 1e9    // plain dense work items shorter than this many tiles go to the one-CTA-per-key-block kernel
+#endif
 // Average number of query tiles a block of 128 keys meets (times the GQA group): what one work
 // item of the dK/dV kernels amounts to.  Dense layout only (the lengths of a packed batch live
 // on the device).
@@ -1661,10 +1665,14 @@ static double dkdv_tiles_per_item(const fa_attn_args& a, const ScoreCfg& cfg) {
 }
 
 int bwd_dkdv_sm100(const fa_attn_args& a, const ScoreCfg& cfg, cudaStream_t st) {
-  // Two kernels (see bwd_dkdv_cta_sm100.cu): short work items of a plain dense problem go to the
-  // one-CTA-per-key-block kernel, everything else to the persistent one.
+  // Two kernels (see bwd_dkdv_cta_sm100.cu): a plain dense problem goes to the one-CTA-per-key-block
+  // kernel (since it keeps K in shared memory and P, dS apart it wins at every item length: 2-7 %
+  // without a mask, 10-15 % with the causal mask or GQA, measured at 16-66 tiles per item),
+  // packed batches and the feature variants to the persistent one.
   const bool features = cfg.has_alibi || cfg.softcap > 0.f || !(cfg.scale_log2 > 2e-5f);
-  if (!features && a.cu_seqlens_q == nullptr && dkdv_tiles_per_item(a, cfg) < 24.0)
+  double below = FA_DKDV_CTA_BELOW;
+  if (const char* e = getenv("FA_B200_DKDV_CTA_BELOW")) below = atof(e);   // tuning / tests: 0 = never
+  if (!features && a.cu_seqlens_q == nullptr && dkdv_tiles_per_item(a, cfg) < below)
     return bwd_dkdv_cta_sm100(a, cfg, st);
   if (a.head_dim == 128)
     return a.dtype == FA_BF16 ? launch_dkdv<__nv_bfloat16, 128>(a, cfg, st) : launch_dkdv<__half, 128>(a, cfg, st);
